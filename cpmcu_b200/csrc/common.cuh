@@ -1,0 +1,72 @@
+// Shared helpers of the sm_100a kernel library: element types, conversions,
+// reductions and the page geometry of the key-value cache.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <stdint.h>
+
+#define CPM_API extern "C" __attribute__((visibility("default")))
+
+// Element type codes shared with the Python side.
+enum : int { CPM_F32 = 0, CPM_BF16 = 1 };
+
+// Tokens per cache page.  A sequence's keys and values live in pages of this many
+// tokens; inside a page the layout is [kv_head][token_in_page][head_dim], so the
+// tile of one head is contiguous.
+constexpr int kPageTokens = 64;
+
+// Status codes returned by the launchers (0 = launched; the CUDA error otherwise).
+enum : int {
+    CPM_OK = 0,
+    CPM_BAD_ARGUMENT = -1,   // a size the kernel does not take
+};
+
+typedef __nv_bfloat16 bf16;
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<bf16>(bf16 v) { return __bfloat162float(v); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ bf16 from_f32<bf16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  The
+// order of additions depends only on the block size.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floats */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int n_warps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < n_warps ? scratch[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+// Address of the first element of (page, kv_head, token_in_page) in a cache lane.
+__device__ __forceinline__ int64_t page_row_offset(int page, int kv_head, int in_page, int n_kv, int d) {
+    return (((int64_t)page * n_kv + kv_head) * kPageTokens + in_page) * (int64_t)d;
+}
+
+static inline int launch_status() {
+    cudaError_t e = cudaPeekAtLastError();
+    return e == cudaSuccess ? CPM_OK : (int)e;
+}

@@ -1,0 +1,221 @@
+// Row-wise kernels of a step: embedding lookup, residual add + RMS norm, the gated
+// activation, and rotary position encoding fused with the store into the cache.
+// All arithmetic is fp32; only loads and stores touch the storage type.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------
+// Embedding rows times a scale, into the fp32 residual stream.
+// The reference gathers rows (src/model/embedding.cuh:7-20) and scales them in a
+// second kernel with the scale rounded to the storage type
+// (src/model/elementwise.cuh:34-41); here the product is formed once in fp32.
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_rows_kernel(const int* __restrict__ ids, const T* __restrict__ table,
+                                  float* __restrict__ out, int hidden, float scale) {
+    const int64_t row = ids[blockIdx.x];
+    const T* src = table + row * hidden;
+    float* dst = out + (int64_t)blockIdx.x * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = to_f32(src[c]) * scale;
+}
+
+CPM_API int cpm_embed_rows(const int* ids, const void* table, float* out, int n_tokens, int hidden,
+                           float scale, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return CPM_OK;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (dtype == CPM_BF16)
+        embed_rows_kernel<bf16><<<n_tokens, threads, 0, stream>>>(ids, (const bf16*)table, out, hidden, scale);
+    else
+        embed_rows_kernel<float><<<n_tokens, threads, 0, stream>>>(ids, (const float*)table, out, hidden, scale);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// x += alpha * delta (fp32 sum), y = x * rsqrt(mean(x^2) + eps) * w.
+// The reference adds in the storage type inside its norm kernel
+// (src/model/norm.cuh:53-99) after scaling the addend in a kernel of its own
+// (src/model/layer.cuh:48-50, 63); here the scale, the add and the norm are one
+// pass and the sum stays in fp32.
+// rows != nullptr: only the listed rows are normed, y is compact [n_rows, hidden]
+// and x is left as it is.
+// ---------------------------------------------------------------------------
+template <typename T, typename W>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, float alpha,
+                                   const W* __restrict__ w, T* __restrict__ y,
+                                   const int* __restrict__ rows, int hidden, float eps, int write_back) {
+    extern __shared__ float row_cache[];   // hidden floats + 33
+    float* scratch = row_cache + hidden;
+    const int64_t src_row = rows ? rows[blockIdx.x] : blockIdx.x;
+    float* xr = x + src_row * hidden;
+    const T* dr = delta ? delta + src_row * hidden : nullptr;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+        float v = xr[c];
+        if (dr) {
+            v = fmaf(alpha, to_f32(dr[c]), v);
+            if (write_back) xr[c] = v;
+        }
+        row_cache[c] = v;
+        ss = fmaf(v, v, ss);
+    }
+    const float total = block_sum(ss, scratch);
+    const float r = rsqrtf(total / (float)hidden + eps);
+    T* yr = y + (int64_t)blockIdx.x * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+        yr[c] = from_f32<T>(row_cache[c] * r * to_f32(w[c]));
+}
+
+template <typename T, typename W>
+static int launch_add_rmsnorm(float* x, const void* delta, float alpha, const void* w, void* y, const int* rows,
+                              int n_rows, int hidden, float eps, int write_back, cudaStream_t stream) {
+    const size_t smem = (size_t)(hidden + 33) * sizeof(float);
+    if (smem > 227 * 1024) return CPM_BAD_ARGUMENT;
+    auto kern = add_rmsnorm_kernel<T, W>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    kern<<<n_rows, threads, smem, stream>>>(x, (const T*)delta, alpha, (const W*)w, (T*)y, rows, hidden, eps, write_back);
+    return launch_status();
+}
+
+CPM_API int cpm_add_rmsnorm(float* x, const void* delta, float alpha, const void* w, int w_is_f32, void* y,
+                            const int* rows, int n_rows, int hidden, float eps, int write_back, int dtype,
+                            cudaStream_t stream) {
+    if (n_rows <= 0) return CPM_OK;
+    if (dtype == CPM_BF16) {
+        if (w_is_f32) return launch_add_rmsnorm<bf16, float>(x, delta, alpha, w, y, rows, n_rows, hidden, eps, write_back, stream);
+        return launch_add_rmsnorm<bf16, bf16>(x, delta, alpha, w, y, rows, n_rows, hidden, eps, write_back, stream);
+    }
+    if (!w_is_f32) return CPM_BAD_ARGUMENT;
+    return launch_add_rmsnorm<float, float>(x, delta, alpha, w, y, rows, n_rows, hidden, eps, write_back, stream);
+}
+
+// x += alpha * delta, for a residual that no norm follows.
+template <typename T>
+__global__ void residual_add_kernel(float* __restrict__ x, const T* __restrict__ delta, float alpha, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = fmaf(alpha, to_f32(delta[i]), x[i]);
+}
+
+CPM_API int cpm_residual_add(float* x, const void* delta, float alpha, int64_t n, int dtype, cudaStream_t stream) {
+    if (n <= 0) return CPM_OK;
+    const int threads = 256;
+    const unsigned blocks = (unsigned)((n + threads - 1) / threads);
+    if (dtype == CPM_BF16) residual_add_kernel<bf16><<<blocks, threads, 0, stream>>>(x, (const bf16*)delta, alpha, n);
+    else residual_add_kernel<float><<<blocks, threads, 0, stream>>>(x, (const float*)delta, alpha, n);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// h[t, c] = silu(gu[t, c]) * gu[t, inter + c]; a row of gu is [gate | up]
+// (src/model/activation.cuh:6-18, src/model/ffn.cuh:38-50).
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ h, int inter) {
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= inter) return;
+    const T* row = gu + (int64_t)blockIdx.x * 2 * inter;
+    const float g = to_f32(row[c]);
+    const float u = to_f32(row[inter + c]);
+    const float s = 1.0f / (1.0f + expf(-g));
+    h[(int64_t)blockIdx.x * inter + c] = from_f32<T>(g * s * u);
+}
+
+CPM_API int cpm_silu_mul(const void* gu, void* h, int n_tokens, int inter, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return CPM_OK;
+    dim3 grid(n_tokens, (inter + 255) / 256);
+    if (grid.y > 65535) return CPM_BAD_ARGUMENT;
+    if (dtype == CPM_BF16) silu_mul_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)gu, (bf16*)h, inter);
+    else silu_mul_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)h, inter);
+    return launch_status();
+}
+
+// ---------------------------------------------------------------------------
+// Rotary encoding of queries and keys, and the store of keys and values into
+// the paged cache.  Pairs are (c, c + rot_dim/2) inside the first rot_dim
+// dimensions of a head, angle = position * inv_freq[c] formed and evaluated in
+// fp32 with the accurate sincosf (src/model/rotary.cuh:6-34 uses the same pairing
+// but the fast-math cos/sin).  cos and sin are multiplied by ``magnitude`` (the
+// LongRoPE attention factor).  inv_freq == nullptr: no rotation.
+// qkv row: [heads*d | kv_heads*d | kv_heads*d].
+// ---------------------------------------------------------------------------
+template <typename T>
+__global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_out,
+                                  T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                  const int* __restrict__ positions, const int* __restrict__ token_seq,
+                                  const int* __restrict__ slots, const int* __restrict__ page_table,
+                                  int max_pages, const float* __restrict__ inv_freq, float magnitude,
+                                  int n_heads, int n_kv, int d, int rot_dim) {
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int half = rot_dim >> 1;
+    const int64_t row_stride = (int64_t)(n_heads + 2 * n_kv) * d;
+    const T* row = qkv + t * row_stride;
+
+    int64_t k_base = 0;
+    if (k_cache) {
+        const int slot = slots[token_seq[t]];
+        const int page = page_table[(int64_t)slot * max_pages + pos / kPageTokens];
+        k_base = page_row_offset(page, 0, pos % kPageTokens, n_kv, d);
+    }
+    const int64_t head_stride_in_page = (int64_t)kPageTokens * d;
+
+    // rotated pairs of q heads and k heads
+    const int n_rot_heads = n_heads + (k_cache ? n_kv : 0);
+    for (int i = threadIdx.x; i < n_rot_heads * half; i += blockDim.x) {
+        const int h = i / half, c = i - h * half;
+        float cs = 1.f, sn = 0.f;
+        if (inv_freq) {
+            const float angle = (float)pos * inv_freq[c];
+            sincosf(angle, &sn, &cs);
+            cs *= magnitude;
+            sn *= magnitude;
+        }
+        const T* src = row + (int64_t)h * d;
+        const float a = to_f32(src[c]);
+        const float b = to_f32(src[c + half]);
+        const float ra = a * cs - b * sn;
+        const float rb = a * sn + b * cs;
+        T* dst;
+        if (h < n_heads) dst = q_out + ((int64_t)t * n_heads + h) * d;
+        else dst = k_cache + k_base + (int64_t)(h - n_heads) * head_stride_in_page;
+        dst[c] = from_f32<T>(ra);
+        dst[c + half] = from_f32<T>(rb);
+    }
+    // dimensions beyond rot_dim pass through
+    const int rest = d - rot_dim;
+    if (rest > 0) {
+        for (int i = threadIdx.x; i < n_rot_heads * rest; i += blockDim.x) {
+            const int h = i / rest, c = rot_dim + (i - h * rest);
+            const T v = row[(int64_t)h * d + c];
+            if (h < n_heads) q_out[((int64_t)t * n_heads + h) * d + c] = v;
+            else k_cache[k_base + (int64_t)(h - n_heads) * head_stride_in_page + c] = v;
+        }
+    }
+    // values
+    if (v_cache) {
+        const T* vrow = row + (int64_t)(n_heads + n_kv) * d;
+        for (int i = threadIdx.x; i < n_kv * d; i += blockDim.x) {
+            const int h = i / d, c = i - h * d;
+            v_cache[k_base + (int64_t)h * head_stride_in_page + c] = vrow[i];
+        }
+    }
+}
+
+CPM_API int cpm_rope_store(const void* qkv, void* q_out, void* k_cache, void* v_cache, const int* positions,
+                           const int* token_seq, const int* slots, const int* page_table, int max_pages,
+                           const float* inv_freq, float magnitude, int n_tokens, int n_heads, int n_kv, int d,
+                           int rot_dim, int dtype, cudaStream_t stream) {
+    if (n_tokens <= 0) return CPM_OK;
+    if (rot_dim < 0 || rot_dim > d || (rot_dim & 1)) return CPM_BAD_ARGUMENT;
+    if ((k_cache == nullptr) != (v_cache == nullptr)) return CPM_BAD_ARGUMENT;
+    const int threads = 128;
+    if (dtype == CPM_BF16)
+        rope_store_kernel<bf16><<<n_tokens, threads, 0, stream>>>((const bf16*)qkv, (bf16*)q_out, (bf16*)k_cache,
+            (bf16*)v_cache, positions, token_seq, slots, page_table, max_pages, inv_freq, magnitude, n_heads, n_kv, d, rot_dim);
+    else
+        rope_store_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)qkv, (float*)q_out, (float*)k_cache,
+            (float*)v_cache, positions, token_seq, slots, page_table, max_pages, inv_freq, magnitude, n_heads, n_kv, d, rot_dim);
+    return launch_status();
+}

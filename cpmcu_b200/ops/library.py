@@ -1,0 +1,89 @@
+"""Loads the compiled kernel library and declares the C signatures of its entry points.
+
+There is no fallback: if the library cannot be built or loaded, or no CUDA device
+is present, the first use raises.  The reference binds its native code with
+pybind11 (src/entry.cu:599-625); these kernels take raw device pointers and a
+stream, so plain ``ctypes`` is enough and nothing has to be compiled against
+torch's headers.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from ctypes import c_float, c_int, c_int64, c_uint64, c_void_p
+from typing import Optional
+
+from . import build as _build
+
+
+class KernelLibraryError(RuntimeError):
+    pass
+
+
+_P = c_void_p
+_SIGNATURES = {
+    "cpm_embed_rows": [_P, _P, _P, c_int, c_int, c_float, c_int, _P],
+    "cpm_add_rmsnorm": [_P, _P, c_float, _P, c_int, _P, _P, c_int, c_int, c_float, c_int, c_int, _P],
+    "cpm_residual_add": [_P, _P, c_float, c_int64, c_int, _P],
+    "cpm_silu_mul": [_P, _P, c_int, c_int, c_int, _P],
+    "cpm_rope_store": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_float, c_int, c_int, c_int, c_int, c_int,
+                       c_int, _P],
+    "cpm_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int,
+                              c_int, c_int, c_float, c_int, _P],
+    "cpm_gemm_f32": [_P, _P, _P, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_float, _P],
+    "cpm_sample_rows": [_P, c_int64, c_int, c_int, _P, _P, _P, c_uint64, _P, _P, _P],
+}
+
+_lock = threading.Lock()
+_lib: Optional[ctypes.CDLL] = None
+_lib_path: Optional[str] = None
+
+
+def library_path() -> Optional[str]:
+    return _lib_path
+
+
+def load() -> ctypes.CDLL:
+    """The kernel library, built at the first call if needed."""
+    global _lib, _lib_path
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        try:
+            path = _build.build()
+        except _build.BuildError as e:
+            raise KernelLibraryError(f"the CUDA kernel library could not be built: {e}") from None
+        try:
+            lib = ctypes.CDLL(path)
+        except OSError as e:
+            raise KernelLibraryError(f"the CUDA kernel library {path} could not be loaded: {e}") from None
+        for name, argtypes in _SIGNATURES.items():
+            try:
+                fn = getattr(lib, name)
+            except AttributeError:
+                raise KernelLibraryError(f"{path} lacks the entry point {name}; rebuild it") from None
+            fn.argtypes = argtypes
+            fn.restype = c_int
+        _lib, _lib_path = lib, path
+        return lib
+
+
+def declare(name: str, argtypes) -> None:
+    """Adds an entry point's signature (used by kernels that register themselves)."""
+    _SIGNATURES[name] = list(argtypes)
+    if _lib is not None:
+        fn = getattr(_lib, name)
+        fn.argtypes = list(argtypes)
+        fn.restype = c_int
+
+
+def check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status == -1:
+        raise ValueError(f"{what}: the kernel does not take these sizes")
+    if status < 0:
+        raise KernelLibraryError(f"{what}: kernel library status {status}")
+    raise KernelLibraryError(f"{what}: CUDA error {status} at launch")

@@ -1,0 +1,204 @@
+"""The kernel library as Python calls, bound to one compute dtype.
+
+``Ops(torch.bfloat16)`` is the serving path: bf16 activations, weights and cache,
+fp32 residual stream, norms, softmax and logits.  ``Ops(torch.float32)`` is the
+true 32-bit path: every tensor fp32 and every matrix product done by this
+library's own fp32 FMA kernel, never by a library routine that may pick a
+reduced-precision mode.
+
+Matrix products of the bf16 path go to cuBLAS through torch, as the reference's
+do through ``cublasGemmEx`` (src/model/linear.cuh:8-37), unless a hand-written
+kernel of this library takes the shape.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional, Tuple
+
+import torch
+
+from . import library
+from .library import check
+
+F32, BF16 = 0, 1
+PAGE_TOKENS = 64
+
+
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+class Ops:
+    def __init__(self, dtype: torch.dtype, device: "torch.device | str" = "cuda:0"):
+        if dtype not in (torch.float32, torch.bfloat16):
+            raise ValueError(f"compute dtype must be float32 or bfloat16, got {dtype}")
+        self.dtype = dtype
+        self.code = F32 if dtype == torch.float32 else BF16
+        self.device = torch.device(device)
+        if self.device.type != "cuda":
+            raise library.KernelLibraryError("this library runs on a CUDA device only; there is no CPU path")
+        if not torch.cuda.is_available():
+            raise library.KernelLibraryError("no CUDA device is available; there is no CPU path")
+        self.lib = library.load()
+        self.element_size = 4 if dtype == torch.float32 else 2
+
+    # ---- checks ----
+    def _act(self, t: torch.Tensor, what: str) -> torch.Tensor:
+        if t.dtype != self.dtype or not t.is_cuda or not t.is_contiguous():
+            raise ValueError(f"{what}: needs a contiguous {self.dtype} CUDA tensor, got {t.dtype} "
+                             f"{'cuda' if t.is_cuda else 'cpu'} contiguous={t.is_contiguous()}")
+        return t
+
+    @staticmethod
+    def _i32(t: torch.Tensor, what: str) -> torch.Tensor:
+        if t.dtype != torch.int32 or not t.is_cuda or not t.is_contiguous():
+            raise ValueError(f"{what}: needs a contiguous int32 CUDA tensor")
+        return t
+
+    @staticmethod
+    def _f32(t: torch.Tensor, what: str) -> torch.Tensor:
+        if t.dtype != torch.float32 or not t.is_cuda or not t.is_contiguous():
+            raise ValueError(f"{what}: needs a contiguous float32 CUDA tensor")
+        return t
+
+    def empty(self, *shape, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        return torch.empty(*shape, dtype=dtype or self.dtype, device=self.device)
+
+    # ---- rows ----
+    def embed(self, ids: torch.Tensor, table: torch.Tensor, scale: float) -> torch.Tensor:
+        """ids int32 [tokens], table [vocab, hidden] -> fp32 [tokens, hidden] = table[ids] * scale."""
+        self._i32(ids, "embed ids")
+        self._act(table, "embedding table")
+        n, hidden = ids.numel(), table.shape[1]
+        out = self.empty(n, hidden, dtype=torch.float32)
+        check(self.lib.cpm_embed_rows(_ptr(ids), _ptr(table), _ptr(out), n, hidden, float(scale), self.code,
+                                      _stream()), "embed")
+        return out
+
+    def add_rmsnorm(self, x: torch.Tensor, delta: Optional[torch.Tensor], alpha: float, weight: torch.Tensor,
+                    eps: float, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """x fp32 [tokens, hidden] (+= alpha*delta, written back when rows is None) -> normed rows."""
+        self._f32(x, "residual stream")
+        hidden = x.shape[-1]
+        if delta is not None:
+            self._act(delta, "residual addend")
+            if delta.shape != x.shape:
+                raise ValueError(f"residual addend {tuple(delta.shape)} does not match the stream {tuple(x.shape)}")
+        if weight.dtype not in (torch.float32, self.dtype) or weight.numel() != hidden or not weight.is_cuda:
+            raise ValueError("norm weight: needs [hidden] in float32 or the compute dtype")
+        n_rows = x.shape[0] if rows is None else rows.numel()
+        if rows is not None:
+            self._i32(rows, "norm rows")
+        y = self.empty(n_rows, hidden)
+        check(self.lib.cpm_add_rmsnorm(_ptr(x), _ptr(delta), float(alpha), _ptr(weight),
+                                       1 if weight.dtype == torch.float32 else 0, _ptr(y), _ptr(rows), n_rows,
+                                       hidden, float(eps), 1 if rows is None else 0, self.code, _stream()),
+              f"rmsnorm (hidden {hidden})")
+        return y
+
+    def residual_add(self, x: torch.Tensor, delta: torch.Tensor, alpha: float) -> None:
+        self._f32(x, "residual stream")
+        self._act(delta, "residual addend")
+        if delta.shape != x.shape:
+            raise ValueError("residual addend does not match the stream")
+        check(self.lib.cpm_residual_add(_ptr(x), _ptr(delta), float(alpha), x.numel(), self.code, _stream()),
+              "residual add")
+
+    def silu_mul(self, gu: torch.Tensor) -> torch.Tensor:
+        """gu [tokens, 2*inter] with rows [gate | up] -> silu(gate) * up, [tokens, inter]."""
+        self._act(gu, "gate_up")
+        n, two_i = gu.shape
+        h = self.empty(n, two_i // 2)
+        check(self.lib.cpm_silu_mul(_ptr(gu), _ptr(h), n, two_i // 2, self.code, _stream()), "silu_mul")
+        return h
+
+    # ---- matrix products ----
+    def linear(self, a: torch.Tensor, w: torch.Tensor, alpha: float = 1.0,
+               out_f32: bool = False) -> torch.Tensor:
+        """alpha * a[M,K] @ w[N,K]^T -> [M,N] in the compute dtype, or fp32 when out_f32."""
+        self._act(a, "linear input")
+        self._act(w, "linear weight")
+        M, K = a.shape
+        N = w.shape[0]
+        if w.shape[1] != K:
+            raise ValueError(f"linear: input [*, {K}] against weight {tuple(w.shape)}")
+        if self.code == F32:
+            c = self.empty(M, N, dtype=torch.float32)
+            check(self.lib.cpm_gemm_f32(_ptr(a), _ptr(w), _ptr(c), M, N, K, K, K, N, float(alpha), _stream()),
+                  "fp32 matrix product")
+            return c
+        if out_f32:
+            c = torch.mm(a, w.t(), out_dtype=torch.float32)
+        else:
+            c = torch.mm(a, w.t())
+        if alpha != 1.0:
+            c.mul_(alpha)
+        return c
+
+    # ---- attention ----
+    def rope_store(self, qkv: torch.Tensor, n_heads: int, n_kv: int, d: int, positions: torch.Tensor,
+                   token_seq: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
+                   k_cache: Optional[torch.Tensor], v_cache: Optional[torch.Tensor],
+                   inv_freq: Optional[torch.Tensor], magnitude: float, rot_dim: int) -> torch.Tensor:
+        """Rotates q and k of qkv [tokens, (heads+2*kv)*d], stores k and v into the cache pages of
+        each token's sequence, and returns the rotated q [tokens, heads, d]."""
+        self._act(qkv, "qkv")
+        n = qkv.shape[0]
+        if qkv.shape[1] != (n_heads + 2 * n_kv) * d:
+            raise ValueError("qkv row size does not match the head counts")
+        if inv_freq is not None:
+            self._f32(inv_freq, "inv_freq")
+            if inv_freq.numel() != rot_dim // 2:
+                raise ValueError("inv_freq needs rot_dim/2 entries")
+        if k_cache is not None:
+            self._act(k_cache, "key cache")
+            self._act(v_cache, "value cache")
+        q = self.empty(n, n_heads, d)
+        check(self.lib.cpm_rope_store(_ptr(qkv), _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(positions),
+                                      _ptr(token_seq), _ptr(slots), _ptr(page_table), page_table.shape[1],
+                                      _ptr(inv_freq), float(magnitude), n, n_heads, n_kv, d, rot_dim, self.code,
+                                      _stream()), "rope_store")
+        return q
+
+    def attention_generic(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                          positions: torch.Tensor, token_seq: torch.Tensor, slots: torch.Tensor,
+                          page_table: torch.Tensor, n_kv: int, scale: float, window: int = 0,
+                          block_list: Optional[torch.Tensor] = None, block_size: int = 0) -> torch.Tensor:
+        """q [tokens, heads, d] against the cached keys of each token's sequence -> [tokens, heads*d]."""
+        self._act(q, "q")
+        n, n_heads, d = q.shape
+        out = self.empty(n, n_heads * d)
+        list_cap = 0
+        if block_list is not None:
+            self._i32(block_list, "block list")
+            list_cap = block_list.shape[-1]
+        check(self.lib.cpm_attention_generic(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(positions),
+                                             _ptr(token_seq), _ptr(slots), _ptr(page_table), page_table.shape[1],
+                                             _ptr(block_list), list_cap, block_size, window, n, n_heads, n_kv, d,
+                                             float(scale), self.code, _stream()),
+              f"attention (head_dim {d}, {n_heads} heads, {n_kv} kv heads)")
+        return out
+
+    # ---- sampling ----
+    def sample(self, logits: torch.Tensor, temperature: Optional[torch.Tensor] = None,
+               top_p: Optional[torch.Tensor] = None, seed: int = 0, seq_key: Optional[torch.Tensor] = None,
+               step_key: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """fp32 logits [rows, vocab] -> int32 [rows]; greedy where temperature is absent or 0."""
+        self._f32(logits, "logits")
+        rows, vocab = logits.shape
+        if out is None:
+            out = self.empty(rows, dtype=torch.int32)
+        check(self.lib.cpm_sample_rows(_ptr(logits), logits.stride(0), rows, vocab, _ptr(out), _ptr(temperature),
+                                       _ptr(top_p), ctypes.c_uint64(seed & 0xFFFFFFFFFFFFFFFF), _ptr(seq_key),
+                                       _ptr(step_key), _stream()), "sample")
+        return out
+
+    def attention(self, ctx, q: torch.Tensor, lane, n_kv: int, scale: float, window: int = 0,
+                  block_list: Optional[torch.Tensor] = None, block_size: int = 0) -> torch.Tensor:
+        """Attention of the step's queries over their sequences' cached keys; picks the kernel."""
+        return self.attention_generic(q, lane.k, lane.v, ctx.positions, ctx.token_seq, ctx.slot_dev,
+                                      lane.page_table, n_kv, scale, window, block_list, block_size)

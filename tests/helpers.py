@@ -1,0 +1,59 @@
+"""Shared by the tests: model folders with random weights, the plain implementation's
+logits for a folder, and error measures."""
+from __future__ import annotations
+
+import json
+import os
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from tests.plain import minicpm4_plain as plain
+
+# Largest allowed |engine - plain| relative to the largest |plain logit| of the compared rows.
+# float32: both sides are fp32 with different summation orders.  bfloat16: weights are the
+# same bf16 values on both sides; activations and the cache are rounded to bf16 in the engine.
+TOL = {"float32": 2e-5, "bfloat16": 2.5e-2}
+
+
+def make_folder(cfgd: dict, out_dir: str, seed: int, dtype: str, std: float = 0.02, norm_mean: float = 1.0) -> str:
+    from cpmcu_b200.models.model import Model
+    from cpmcu_b200.registry import architecture
+    from cpmcu_b200.weights import write_model_folder
+
+    arch = architecture(cfgd["architectures"][0])
+    cfg = arch.config_class.from_dict(cfgd)
+    specs = Model(arch.model_spec(cfg), None).weight_specs()
+    tdtype = {"float32": torch.float32, "bfloat16": torch.bfloat16}[dtype]
+    return write_model_folder(cfg, specs, out_dir, seed, tdtype, std, norm_mean)
+
+
+def read_folder(folder: str):
+    """(raw config dictionary, tensors by name) read without the package under test."""
+    from safetensors.torch import load_file
+
+    with open(os.path.join(folder, "config.json")) as f:
+        cfg = json.load(f)
+    return cfg, load_file(os.path.join(folder, "model.safetensors"))
+
+
+_plain_cache: Dict[tuple, torch.Tensor] = {}
+
+
+def plain_logits(folder: str, ids: Sequence[int], schedule=None) -> torch.Tensor:
+    key = (folder, tuple(ids), None if schedule is None else tuple(schedule))
+    if key not in _plain_cache:
+        cfg, w = read_folder(folder)
+        _plain_cache[key] = plain.forward(cfg, w, list(ids), schedule=schedule)
+    return _plain_cache[key]
+
+
+def rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
+    got, want = got.detach().float().cpu(), want.detach().float().cpu()
+    assert got.shape == want.shape, (got.shape, want.shape)
+    return float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
+
+
+def random_ids(vocab: int, n: int, seed: int) -> List[int]:
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()

@@ -1,0 +1,233 @@
+"""Each kernel alone against a plain PyTorch fp32 reference of the same operation, at
+sizes other than the models' (odd widths, group sizes 1/3/8, head sizes 16..256)."""
+import math
+
+import pytest
+import torch
+
+from tests.plain import minicpm4_plain as plain
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+# relative to the largest reference value; bf16 = one rounding of the output (2^-9) plus input rounding
+KTOL = {"float32": 1e-5, "bfloat16": 1e-2}
+
+
+def _ops(dtype):
+    from cpmcu_b200.ops.ops import Ops
+    return Ops(DT[dtype], "cuda:0")
+
+
+def _err(got, want):
+    got, want = got.float().cpu(), want.float().cpu()
+    return float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hidden", [24, 72, 1000, 4096])
+def test_embed(dtype, hidden):
+    ops = _ops(dtype)
+    g = torch.Generator().manual_seed(1)
+    table = torch.randn(333, hidden, generator=g).to(DT[dtype])
+    ids = torch.randint(0, 333, (17,), generator=g, dtype=torch.int32)
+    got = ops.embed(ids.cuda(), table.cuda(), 12.5)
+    want = table.float()[ids.long()] * 12.5
+    assert got.dtype == torch.float32
+    assert _err(got, want) < 1e-6
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hidden", [24, 72, 1000, 4096, 13000])
+def test_add_rmsnorm(dtype, hidden):
+    ops = _ops(dtype)
+    g = torch.Generator().manual_seed(2)
+    x = torch.randn(9, hidden, generator=g) * 3
+    delta = torch.randn(9, hidden, generator=g).to(DT[dtype])
+    w32 = 1 + 0.1 * torch.randn(hidden, generator=g)
+    for w in ([w32] if dtype == "float32" else [w32, w32.to(torch.bfloat16)]):
+        xd = x.clone().cuda()
+        y = ops.add_rmsnorm(xd, delta.cuda(), 0.37, w.cuda(), 1e-5)
+        xs = x + 0.37 * delta.float()
+        assert _err(xd, xs) < 1e-6
+        want = plain.rms_norm(xs, w.float(), 1e-5)
+        assert _err(y, want) < KTOL[dtype]
+        # rows mode: compact output, the stream stays as it is
+        rows = torch.tensor([7, 0, 3], dtype=torch.int32).cuda()
+        xd2 = x.clone().cuda()
+        y2 = ops.add_rmsnorm(xd2, delta.cuda(), 0.37, w.cuda(), 1e-5, rows)
+        assert torch.equal(xd2.cpu(), x)
+        assert _err(y2, want[rows.cpu().long()]) < KTOL[dtype]
+        # no addend
+        y3 = ops.add_rmsnorm(x.clone().cuda(), None, 0.0, w.cuda(), 1e-5)
+        assert _err(y3, plain.rms_norm(x, w.float(), 1e-5)) < KTOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_residual_add_and_silu_mul(dtype):
+    ops = _ops(dtype)
+    g = torch.Generator().manual_seed(3)
+    x = torch.randn(5, 100, generator=g)
+    d = torch.randn(5, 100, generator=g).to(DT[dtype])
+    xd = x.clone().cuda()
+    ops.residual_add(xd, d.cuda(), -0.5)
+    assert _err(xd, x - 0.5 * d.float()) < 1e-6
+    gu = (torch.randn(7, 2 * 333, generator=g) * 3).to(DT[dtype])
+    got = ops.silu_mul(gu.cuda())
+    gate, up = gu.float()[:, :333], gu.float()[:, 333:]
+    want = gate * (1 / (1 + torch.exp(-gate))) * up
+    assert _err(got, want) < KTOL[dtype]
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 1, 1), (3, 5, 7), (64, 64, 16), (65, 130, 33), (150, 1000, 72), (8, 777, 320)])
+def test_gemm_f32(M, N, K):
+    ops = _ops("float32")
+    g = torch.Generator().manual_seed(4)
+    a, w = torch.randn(M, K, generator=g), torch.randn(N, K, generator=g)
+    got = ops.linear(a.cuda(), w.cuda(), alpha=0.25)
+    want = (a.double() @ w.double().T * 0.25).float()
+    assert _err(got, want) < 1e-5
+    # a row's result does not depend on the other rows of the batch
+    one = ops.linear(a[:1].contiguous().cuda(), w.cuda(), alpha=0.25)
+    assert torch.equal(one[0], got[0])
+
+
+def test_linear_bf16():
+    ops = _ops("bfloat16")
+    g = torch.Generator().manual_seed(5)
+    a, w = torch.randn(37, 72, generator=g).bfloat16(), torch.randn(777, 72, generator=g).bfloat16()
+    want = a.float() @ w.float().T
+    assert _err(ops.linear(a.cuda(), w.cuda()), want) < KTOL["bfloat16"]
+    lg = ops.linear(a.cuda(), w.cuda(), alpha=0.5, out_f32=True)
+    assert lg.dtype == torch.float32
+    assert _err(lg, want * 0.5) < 1e-5
+
+
+def _paged_setup(ops, lens, n_kv, d, seed, dtype):
+    """Random rotated q/k/v for sequences of ``lens``, stored through rope_store into
+    pages handed out in a scrambled order."""
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.parts.base import CacheNeeds
+
+    cache = Cache([CacheNeeds(kv_heads=n_kv, head_dim=d)], max_tokens=64 * 40, dtype=DT[dtype], device="cuda:0")
+    # scramble the page order so that logical and physical pages differ
+    junk = cache.open_sequences(3)
+    for j, s in enumerate(junk):
+        cache.reserve(s, 64 * (j + 1))
+    slots = cache.open_sequences(len(lens))
+    cache.close_sequence(junk[1])
+    for s, n in zip(slots, lens):
+        cache.reserve(s, n)
+        cache.set_length(s, n)
+    cache.sync()
+    return cache, slots
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("n_heads,n_kv,d,rot", [(4, 2, 16, 16), (3, 3, 48, 48), (8, 1, 64, 32), (6, 2, 128, 128),
+                                                (2, 1, 256, 256), (5, 5, 32, 0)])
+def test_rope_store_and_attention(dtype, n_heads, n_kv, d, rot):
+    ops = _ops(dtype)
+    lens = [1, 70, 200, 64]
+    cache, slots = _paged_setup(ops, lens, n_kv, d, 0, dtype)
+    lane = cache.lane(0)
+    g = torch.Generator().manual_seed(6)
+    T = sum(lens)
+    qkv = torch.randn(T, (n_heads + 2 * n_kv) * d, generator=g).to(DT[dtype])
+    positions = torch.cat([torch.arange(n) for n in lens]).int()
+    token_seq = torch.cat([torch.full((n,), i) for i, n in enumerate(lens)]).int()
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, rot, 2).float() / max(rot, 1)))) if rot else None
+    mag = 1.3
+    q = ops.rope_store(qkv.cuda(), n_heads, n_kv, d, positions.cuda(), token_seq.cuda(),
+                       torch.tensor(slots, dtype=torch.int32).cuda(), lane.page_table, lane.k, lane.v,
+                       inv_freq.cuda() if rot else None, mag, rot)
+    rows = qkv.float().view(T, n_heads + 2 * n_kv, d)
+    q_ref, k_ref, v_ref = rows[:, :n_heads], rows[:, n_heads:n_heads + n_kv], rows[:, n_heads + n_kv:]
+    if rot:
+        def rot_part(u):
+            return torch.cat([plain.rotate(u[..., :rot], positions, inv_freq, mag), u[..., rot:]], dim=-1)
+        q_ref, k_ref = rot_part(q_ref), rot_part(k_ref)
+    assert _err(q, q_ref) < KTOL[dtype]
+    # read the cache back through the page table
+    table = lane.page_table.cpu()
+    o = 0
+    for s, n in zip(slots, lens):
+        for j in (0, n // 2, n - 1):
+            page = int(table[s, j // 64])
+            got_k = lane.k[page, :, j % 64].float().cpu()
+            got_v = lane.v[page, :, j % 64].float().cpu()
+            assert _err(got_k, k_ref[o + j]) < KTOL[dtype]
+            assert _err(got_v, v_ref[o + j]) < KTOL[dtype]
+        o += n
+    # attention of all tokens over their sequences
+    scale = 1 / math.sqrt(d)
+    out = ops.attention_generic(q, lane.k, lane.v, positions.cuda(), token_seq.cuda(),
+                                torch.tensor(slots, dtype=torch.int32).cuda(), lane.page_table, n_kv, scale)
+    qr = q.float().cpu() if dtype == "bfloat16" else q_ref
+    o = 0
+    for n in lens:
+        kk = k_ref[o:o + n].to(DT[dtype]).float()
+        vv = v_ref[o:o + n].to(DT[dtype]).float()
+        want = plain.dense_attention(qr[o:o + n], kk, vv, scale).reshape(n, -1)
+        assert _err(out[o:o + n], want) < KTOL[dtype], (n,)
+        o += n
+    # window
+    outw = ops.attention_generic(q, lane.k, lane.v, positions.cuda(), token_seq.cuda(),
+                                 torch.tensor(slots, dtype=torch.int32).cuda(), lane.page_table, n_kv, scale, window=37)
+    o = sum(lens[:2])
+    want = plain.dense_attention(qr[o:o + 200], k_ref[o:o + 200].to(DT[dtype]).float(),
+                                 v_ref[o:o + 200].to(DT[dtype]).float(), scale, window=37).reshape(200, -1)
+    assert _err(outw[o:o + 200], want) < KTOL[dtype]
+
+
+def test_attention_far_key_stands_out():
+    """One key far back is made to dominate: its value must come through whatever page it is in."""
+    ops = _ops("float32")
+    n_heads, n_kv, d, n = 2, 1, 32, 700
+    cache, slots = _paged_setup(ops, [n], n_kv, d, 0, "float32")
+    lane = cache.lane(0)
+    g = torch.Generator().manual_seed(7)
+    qkv = torch.randn(n, (n_heads + 2) * d, generator=g) * 0.1
+    rows = qkv.view(n, n_heads + 2, d)
+    far = 130
+    rows[far, n_heads] = 4.0                      # key
+    rows[n - 1, :n_heads] = 4.0                   # last query matches it
+    positions = torch.arange(n).int().cuda()
+    token_seq = torch.zeros(n, dtype=torch.int32).cuda()
+    sl = torch.tensor(slots, dtype=torch.int32).cuda()
+    q = ops.rope_store(qkv.cuda(), n_heads, n_kv, d, positions, token_seq, sl, lane.page_table, lane.k, lane.v,
+                       None, 1.0, 0)
+    out = ops.attention_generic(q, lane.k, lane.v, positions, token_seq, sl, lane.page_table, n_kv, 1 / math.sqrt(d))
+    v_far = rows[far, n_heads + 1]
+    assert _err(out[n - 1].view(n_heads, d)[0], v_far) < 1e-3
+
+
+@pytest.mark.parametrize("vocab", [5, 777, 73448])
+def test_sampling(vocab):
+    ops = _ops("float32")
+    g = torch.Generator().manual_seed(8)
+    logits = torch.randn(6, vocab, generator=g) * 3
+    logits[1, vocab // 2] = logits[1, 3] = 50.0        # a tie: the lower index wins
+    got = ops.sample(logits.cuda()).cpu()
+    for r in range(6):
+        assert int(got[r]) == plain.sample_token(logits[r], 0.0, 0.0)
+    assert int(got[1]) == 3
+    temps = torch.tensor([0.8, 0.0, 1.5, 0.3, 1.0, 2.0])
+    top_p = torch.tensor([1.0, 1.0, 0.9, 0.5, 0.05, 1.0])
+    seq_key = torch.arange(6, dtype=torch.int32)
+    for step in range(20):
+        step_key = torch.full((6,), step, dtype=torch.int32)
+        got = ops.sample(logits.cuda(), temps.cuda(), top_p.cuda(), 1234, seq_key.cuda(), step_key.cuda()).cpu()
+        for r in range(6):
+            tok = int(got[r])
+            if temps[r] == 0:
+                assert tok == plain.sample_token(logits[r], 0.0, 0.0)
+                continue
+            u = plain.philox_uniform(1234, r, step)
+            w = plain.sampling_weights(logits[r], float(temps[r]), float(top_p[r]))
+            assert w[tok] > 0, "a token outside the nucleus was drawn"
+            c = torch.cumsum(w, 0)
+            target = u * float(c[-1])
+            slack = 1e-5 * float(c[-1])
+            lo = float(c[tok - 1]) if tok > 0 else 0.0
+            assert lo - slack <= target <= float(c[tok]) + slack, (r, step, tok, lo, target, float(c[tok]))

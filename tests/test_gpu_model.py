@@ -1,0 +1,124 @@
+"""The engine against the plain implementation, through the step function: whole
+sequences, the last tokens one by one, chunked prompts, and batches of unequal lengths
+one after another so that slots and pages are used again.  float32 and bfloat16."""
+import pytest
+import torch
+
+from tests import configs, helpers
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    ("tiny_a", configs.tiny_a, 0),
+    ("tiny_b_dense", lambda: configs.tiny_b(sparse=False), 1),
+    ("tiny_c", configs.tiny_c, 5),
+]
+DTYPES = ["float32", "bfloat16"]
+
+
+def _stepper(folder, dtype, max_tokens=2048, chunk_tokens=2048):
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.engine import Stepper
+    from cpmcu_b200.loading import load_model
+
+    _, cfg, model = load_model(folder, dtype)
+    cache = Cache(model.cache_needs(), max_tokens=max_tokens, dtype=model.ops.dtype, device="cuda:0")
+    return cfg, Stepper(model, cache, chunk_tokens=chunk_tokens)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,make,seed", CASES)
+def test_whole_sequence(model_folders, name, make, seed, dtype):
+    from cpmcu_b200.engine import SequenceStep
+
+    folder = model_folders(name, make(), seed, dtype)
+    cfg, st = _stepper(folder, dtype)
+    for n in (1, 5, 70, 150):
+        ids = helpers.random_ids(cfg.vocab_size, n, seed + n)
+        slot = st.open(1)[0]
+        got = st.step([SequenceStep(slot, ids, list(range(n)))])
+        st.close(slot)
+        err = helpers.rel_err(got, helpers.plain_logits(folder, ids))
+        assert err < helpers.TOL[dtype], (name, dtype, n, err)
+    st.cache.check_consistent()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,make,seed", CASES)
+def test_last_tokens_one_by_one(model_folders, name, make, seed, dtype):
+    from cpmcu_b200.engine import SequenceStep
+
+    folder = model_folders(name, make(), seed, dtype)
+    cfg, st = _stepper(folder, dtype)
+    n, tail = 150, 32
+    ids = helpers.random_ids(cfg.vocab_size, n, seed + 100)
+    want = helpers.plain_logits(folder, ids)
+    slot = st.open(1)[0]
+    rows = [st.step([SequenceStep(slot, ids[:n - tail], list(range(n - tail)))])]
+    for i in range(n - tail, n):
+        rows.append(st.step([SequenceStep(slot, ids[i:i + 1], [0])]))
+    st.close(slot)
+    got = torch.cat(rows)
+    for lo, hi, what in ((0, n - tail, "prompt"), (n - tail, n - tail + 1, "first decoded"), (n - tail, n, "decoded")):
+        err = helpers.rel_err(got[lo:hi], want[lo:hi])
+        assert err < helpers.TOL[dtype], (name, dtype, what, err)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("chunk", [7, 64])
+def test_chunked_prompt(model_folders, dtype, chunk):
+    from cpmcu_b200.engine import SequenceStep
+
+    folder = model_folders("tiny_a", configs.tiny_a(), 0, dtype)
+    cfg, st = _stepper(folder, dtype, chunk_tokens=chunk)
+    lens = [33, 1, 130]
+    seqs = [helpers.random_ids(cfg.vocab_size, n, 40 + n) for n in lens]
+    slots = st.open(len(seqs))
+    got = st.step([SequenceStep(s, ids, [len(ids) - 1, 0]) for s, ids in zip(slots, seqs)])
+    k = 0
+    for ids in seqs:
+        want = helpers.plain_logits(folder, ids)
+        assert helpers.rel_err(got[k:k + 1], want[-1:]) < helpers.TOL[dtype]
+        assert helpers.rel_err(got[k + 1:k + 2], want[:1]) < helpers.TOL[dtype]
+        k += 2
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,make,seed", CASES)
+def test_unequal_batches_reuse_slots(model_folders, name, make, seed, dtype):
+    """Batches of unequal prompts decode together; shorter requests end earlier; the next
+    batch takes over their slots and pages with the old contents still in them."""
+    from cpmcu_b200.engine import SequenceStep
+
+    folder = model_folders(name, make(), seed, dtype)
+    cfg, st = _stepper(folder, dtype, max_tokens=64 * 12)
+    batches = [[(5, 3), (17, 20), (33, 9)], [(1, 24), (40, 2), (97, 11), (70, 16)], [(64, 5), (63, 70)]]
+    for b, batch in enumerate(batches):
+        seqs = [helpers.random_ids(cfg.vocab_size, p + d, 1000 * b + 10 * i + seed) for i, (p, d) in enumerate(batch)]
+        wants = [helpers.plain_logits(folder, ids) for ids in seqs]
+        slots = st.open(len(batch))
+        got = [[] for _ in batch]
+        out = st.step([SequenceStep(slots[i], seqs[i][:p], [p - 1]) for i, (p, d) in enumerate(batch)])
+        for i in range(len(batch)):
+            got[i].append(out[i])
+        live = list(range(len(batch)))
+        t = 0
+        while live:
+            live = [i for i in live if t < batch[i][1]]
+            for i in range(len(batch)):
+                if i not in live and slots[i] is not None and t >= batch[i][1]:
+                    st.close(slots[i])
+                    slots[i] = None
+            if not live:
+                break
+            out = st.step([SequenceStep(slots[i], [seqs[i][batch[i][0] + t]], [0]) for i in live])
+            for r, i in enumerate(live):
+                got[i].append(out[r])
+            t += 1
+        for i, (p, d) in enumerate(batch):
+            g = torch.stack(got[i])
+            w = wants[i][p - 1:p + d]
+            err = helpers.rel_err(g, w)
+            assert err < helpers.TOL[dtype], (name, dtype, b, i, err)
+        st.cache.check_consistent()
+    assert st.cache.tokens_held() == 0
