@@ -54,15 +54,16 @@ class CacheGroup:
                 if PAGE_TOKENS % needs.pooled_stride:
                     raise ValueError(f"pooled-key stride {needs.pooled_stride} must divide the page size {PAGE_TOKENS}")
                 per_page = PAGE_TOKENS // needs.pooled_stride
+                # pooled keys are kept in fp32 whatever the cache's type: block selection compares them
                 self.pooled = torch.empty((n, n_pages, needs.kv_heads, per_page, needs.head_dim),
-                                          dtype=dtype, device=device)
+                                          dtype=torch.float32, device=device)
 
     def bytes_per_token(self) -> int:
         if self.k is None:
             return 0
         per = 2 * self.needs.kv_heads * self.needs.head_dim * self.k.element_size() * len(self.lanes)
         if self.pooled is not None:
-            per += per // 2 // self.needs.pooled_stride
+            per += self.needs.kv_heads * self.needs.head_dim * 4 * len(self.lanes) // self.needs.pooled_stride
         return per
 
     def reserve(self, slot: int, n_tokens: int) -> None:

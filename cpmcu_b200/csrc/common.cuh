@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <cuda_bf16.h>
 #include <stdint.h>
+#include <math.h>
 
 #define CPM_API extern "C" __attribute__((visibility("default")))
 
@@ -55,6 +56,42 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
     if (warp == 0) {
         float t = lane < n_warps ? scratch[lane] : 0.f;
         t = warp_sum(t);
+        if (lane == 0) scratch[32] = t;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+// Largest value with the lowest index among equals, over a warp and over a block.
+struct ArgMax { float v; int i; };
+
+__device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
+    if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
+    return a;
+}
+
+__device__ __forceinline__ ArgMax block_argmax(ArgMax a, ArgMax* scratch /* 33 */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        ArgMax b;
+        b.v = __shfl_xor_sync(0xffffffffu, a.v, o);
+        b.i = __shfl_xor_sync(0xffffffffu, a.i, o);
+        a = better(a, b);
+    }
+    __syncthreads();
+    if (lane == 0) scratch[warp] = a;
+    __syncthreads();
+    if (warp == 0) {
+        const int n_warps = (blockDim.x + 31) >> 5;
+        ArgMax t = lane < n_warps ? scratch[lane] : ArgMax{-INFINITY, 0x7fffffff};
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            ArgMax b;
+            b.v = __shfl_xor_sync(0xffffffffu, t.v, o);
+            b.i = __shfl_xor_sync(0xffffffffu, t.i, o);
+            t = better(t, b);
+        }
         if (lane == 0) scratch[32] = t;
     }
     __syncthreads();

@@ -33,41 +33,6 @@ __device__ __forceinline__ float philox_uniform(uint64_t seed, uint32_t a, uint3
     return (float)(c0 >> 8) * (1.0f / 16777216.0f);
 }
 
-struct ArgMax { float v; int i; };
-
-__device__ __forceinline__ ArgMax better(ArgMax a, ArgMax b) {
-    if (b.v > a.v || (b.v == a.v && b.i < a.i)) return b;
-    return a;
-}
-
-__device__ ArgMax block_argmax(ArgMax a, ArgMax* scratch /* 33 */) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        ArgMax b;
-        b.v = __shfl_xor_sync(0xffffffffu, a.v, o);
-        b.i = __shfl_xor_sync(0xffffffffu, a.i, o);
-        a = better(a, b);
-    }
-    __syncthreads();
-    if (lane == 0) scratch[warp] = a;
-    __syncthreads();
-    if (warp == 0) {
-        const int n_warps = (blockDim.x + 31) >> 5;
-        ArgMax t = lane < n_warps ? scratch[lane] : ArgMax{-INFINITY, 0x7fffffff};
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            ArgMax b;
-            b.v = __shfl_xor_sync(0xffffffffu, t.v, o);
-            b.i = __shfl_xor_sync(0xffffffffu, t.i, o);
-            t = better(t, b);
-        }
-        if (lane == 0) scratch[32] = t;
-    }
-    __syncthreads();
-    return scratch[32];
-}
-
 __global__ void __launch_bounds__(kSampleThreads)
 sample_rows_kernel(const float* __restrict__ logits, int64_t ld, int vocab, int* __restrict__ out,
                    const float* __restrict__ temperature, const float* __restrict__ top_p,

@@ -31,6 +31,9 @@ _SIGNATURES = {
     "cpm_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int,
                               c_int, c_int, c_float, c_int, _P],
     "cpm_gemm_f32": [_P, _P, _P, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_float, _P],
+    "cpm_pool_keys": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "cpm_select_blocks": [_P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
+                          c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "cpm_sample_rows": [_P, c_int64, c_int, c_int, _P, _P, _P, c_uint64, _P, _P, _P],
 }
 

@@ -202,3 +202,27 @@ class Ops:
         """Attention of the step's queries over their sequences' cached keys; picks the kernel."""
         return self.attention_generic(q, lane.k, lane.v, ctx.positions, ctx.token_seq, ctx.slot_dev,
                                       lane.page_table, n_kv, scale, window, block_list, block_size)
+
+    # ---- block-sparse selection ----
+    def pool_keys(self, ctx, lane, n_kv: int, d: int, kernel: int, stride: int) -> None:
+        """Stores the mean-pooled keys whose windows this step's tokens complete."""
+        check(self.lib.cpm_pool_keys(_ptr(lane.k), _ptr(lane.pooled), _ptr(ctx.positions), _ptr(ctx.token_seq),
+                                     _ptr(ctx.slot_dev), _ptr(lane.page_table), lane.page_table.shape[1],
+                                     ctx.n_tokens, n_kv, d, kernel, stride, self.code, _stream()), "pool_keys")
+
+    def select_blocks(self, ctx, q: torch.Tensor, lane, n_kv: int, scale: float, sparse) -> Tuple[torch.Tensor, int]:
+        """(block list int32 [tokens, kv_heads, cap], block size) for the step's queries."""
+        n, n_heads, d = q.shape
+        bs, stride = sparse["block_size"], sparse["kernel_stride"]
+        local_blocks = sparse["window_size"] // bs
+        cap = sparse["topk"] + local_blocks + 2
+        longest = lane.page_table.shape[1] * PAGE_TOKENS if ctx.captured else ctx.max_kv_len
+        max_entries = max(1, longest // stride + 1)
+        lists = self.empty(n, n_kv, cap, dtype=torch.int32)
+        check(self.lib.cpm_select_blocks(_ptr(q), _ptr(lane.pooled), _ptr(ctx.positions), _ptr(ctx.token_seq),
+                                         _ptr(ctx.slot_dev), _ptr(lane.page_table), lane.page_table.shape[1],
+                                         _ptr(lists), cap, n, n_heads, n_kv, d, float(scale), sparse["kernel_size"],
+                                         stride, bs, sparse.get("init_blocks", 1), sparse["topk"], local_blocks,
+                                         sparse.get("dense_len", 0), max_entries, self.code, _stream()),
+              f"select_blocks ({max_entries} pooled keys)")
+        return lists, bs

@@ -82,12 +82,9 @@ class GroupedQueryAttention(Mixer):
                            inv_freq, magnitude, rot_dim)
         block_list, block_size = None, 0
         if self.sparse is not None:
-            block_list, block_size = self._select_blocks(ctx, q, lane, writes_cache)
+            if writes_cache:
+                ops.pool_keys(ctx, lane, self.n_kv, self.d, self.sparse["kernel_size"], self.sparse["kernel_stride"])
+            if ctx.captured or ctx.max_kv_len > self.sparse.get("dense_len", 0):
+                block_list, block_size = ops.select_blocks(ctx, q, lane, self.n_kv, self.scale, self.sparse)
         out = ops.attention(ctx, q, lane, self.n_kv, self.scale, self.window, block_list, block_size)
         return ops.linear(out, self.w_o)
-
-    def _select_blocks(self, ctx, q, lane, writes_cache: bool):
-        sp = self.sparse
-        if not ctx.captured and ctx.max_kv_len <= sp["dense_len"]:
-            return None, 0          # every query of this step is below the switch: dense
-        return self.ops.sparse_select(ctx, q, lane, self.n_kv, self.scale, sp, writes_cache)

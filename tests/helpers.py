@@ -51,7 +51,12 @@ def plain_logits(folder: str, ids: Sequence[int], schedule=None) -> torch.Tensor
 def rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
     got, want = got.detach().float().cpu(), want.detach().float().cpu()
     assert got.shape == want.shape, (got.shape, want.shape)
-    return float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
+    err = float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
+    log = os.environ.get("CPMCU_TEST_ERRLOG")
+    if log:
+        with open(log, "a") as f:
+            f.write(f"{os.environ.get('PYTEST_CURRENT_TEST', '?')} {err:.3e}\n")
+    return err
 
 
 def random_ids(vocab: int, n: int, seed: int) -> List[int]:

@@ -207,7 +207,7 @@ def test_sampling(vocab):
     ops = _ops("float32")
     g = torch.Generator().manual_seed(8)
     logits = torch.randn(6, vocab, generator=g) * 3
-    logits[1, vocab // 2] = logits[1, 3] = 50.0        # a tie: the lower index wins
+    logits[1, vocab - 1] = logits[1, 3] = 50.0         # a tie: the lower index wins
     got = ops.sample(logits.cuda()).cpu()
     for r in range(6):
         assert int(got[r]) == plain.sample_token(logits[r], 0.0, 0.0)

@@ -11,6 +11,7 @@ pytestmark = pytest.mark.gpu
 CASES = [
     ("tiny_a", configs.tiny_a, 0),
     ("tiny_b_dense", lambda: configs.tiny_b(sparse=False), 1),
+    ("tiny_b", configs.tiny_b, 1),
     ("tiny_c", configs.tiny_c, 5),
 ]
 DTYPES = ["float32", "bfloat16"]
