@@ -219,3 +219,28 @@ CPM_API int cpm_rope_store(const void* qkv, void* q_out, void* k_cache, void* v_
             (float*)v_cache, positions, token_seq, slots, page_table, max_pages, inv_freq, magnitude, n_heads, n_kv, d, rot_dim);
     return launch_status();
 }
+
+// ---------------------------------------------------------------------------
+// Between two decode steps that run without the host: the sampled token becomes the
+// next input, and the position, key count and draw counter of every live sequence
+// go up by one.  Entries that only pad the batch (live == 0) stay where they are.
+// ---------------------------------------------------------------------------
+__global__ void advance_decode_kernel(int* __restrict__ ids, int* __restrict__ positions, int* __restrict__ kv_len,
+                                      int* __restrict__ step_key, const int* __restrict__ sampled,
+                                      const int* __restrict__ live, int n) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    if (live[i]) {
+        ids[i] = sampled[i];
+        positions[i] += 1;
+        kv_len[i] += 1;
+        step_key[i] += 1;
+    }
+}
+
+CPM_API int cpm_advance_decode(int* ids, int* positions, int* kv_len, int* step_key, const int* sampled,
+                               const int* live, int n, cudaStream_t stream) {
+    if (n <= 0) return CPM_OK;
+    advance_decode_kernel<<<(n + 127) / 128, 128, 0, stream>>>(ids, positions, kv_len, step_key, sampled, live, n);
+    return launch_status();
+}

@@ -1,0 +1,166 @@
+"""Decode steps that run without the host in between: one token per live sequence,
+sampled on the device and fed back as the next input, optionally as a CUDA graph.
+
+The batch lives in fixed device buffers (ids, positions, key counts, slots, random
+keys); a step reads them, runs the model on one token per entry, samples, and
+advances the buffers.  The buffers have a bucket size (a power of two); entries
+beyond the live sequences are padding that points at a scratch sequence and never
+advances, so padding changes no result.  One graph is captured per bucket size and
+replayed whatever the sequences' lengths are, because every kernel reads lengths and
+pages from device memory.  The reference captures its decode graph anew whenever the
+padded length or the token count changes (src/entry.cu:562-584) and returns to the host
+for every token (cpmcu/llm.py:361-373).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import torch
+
+from ..parts.base import StepContext
+from ..sampling import SamplingParams
+from .step import Stepper
+
+
+def bucket_size(n: int) -> int:
+    b = 1
+    while b < n:
+        b *= 2
+    return b
+
+
+class _Bucket:
+    def __init__(self, size: int, device: torch.device):
+        i32 = dict(dtype=torch.int32, device=device)
+        self.size = size
+        self.ids = torch.zeros(size, **i32)
+        self.positions = torch.zeros(size, **i32)
+        self.kv_len = torch.ones(size, **i32)
+        self.slot = torch.zeros(size, **i32)
+        self.token_seq = torch.arange(size, **i32)
+        self.cu_q = torch.arange(size + 1, **i32)
+        self.want_rows = torch.arange(size, **i32)
+        self.live = torch.zeros(size, **i32)
+        self.seq_key = torch.zeros(size, **i32)
+        self.step_key = torch.zeros(size, **i32)
+        self.temperature = torch.zeros(size, dtype=torch.float32, device=device)
+        self.top_p = torch.ones(size, dtype=torch.float32, device=device)
+        self.sampled = torch.zeros(size, **i32)
+        self.logits: Optional[torch.Tensor] = None
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.warm = False
+
+
+class DecodeRunner:
+    def __init__(self, stepper: Stepper, use_graph: bool = True, seed: int = 0):
+        self.stepper = stepper
+        self.model = stepper.model
+        self.cache = stepper.cache
+        self.ops = stepper.ops
+        self.use_graph = bool(use_graph)
+        self.seed = int(seed)
+        self.buckets: Dict[int, _Bucket] = {}
+        self.pad_slot = self.cache.open_sequence()       # scratch sequence the padding entries use
+        self.cache.reserve(self.pad_slot, 1)
+        self.cache.set_length(self.pad_slot, 1)
+        self.cache.sync()
+        self.current: Optional[_Bucket] = None
+        self.slots: List[int] = []
+        self.pinned = None
+        self.launches_per_step = 0
+
+    # ---- one step's work on the device ----
+    def _body(self, b: _Bucket, captured: bool) -> None:
+        capacity = self.cache.max_pages_per_seq * 64
+        ctx = StepContext(
+            n_tokens=b.size, n_seqs=b.size, is_decode=True, captured=captured,
+            q_lens=[1] * b.size, kv_lens=[], slots=[], max_q_len=1, max_kv_len=capacity,
+            token_ids=b.ids, positions=b.positions, token_seq=b.token_seq, cu_q=b.cu_q,
+            kv_len_dev=b.kv_len, slot_dev=b.slot, cache=self.cache,
+        )
+        b.logits = self.model.forward(ctx, b.want_rows)
+        self.ops.sample(b.logits, b.temperature, b.top_p, self.seed, b.seq_key, b.step_key, out=b.sampled)
+        self.ops.advance_decode(b.ids, b.positions, b.kv_len, b.step_key, b.sampled, b.live)
+
+    def _bucket(self, n: int) -> _Bucket:
+        size = bucket_size(n)
+        b = self.buckets.get(size)
+        if b is None:
+            b = _Bucket(size, self.ops.device)
+            b.slot.fill_(self.pad_slot)
+            self.buckets[size] = b
+        return b
+
+    def _prepare(self, b: _Bucket) -> None:
+        """Warm-up and capture happen on padding only, so they touch no sequence."""
+        if b.warm:
+            return
+        b.slot.fill_(self.pad_slot)
+        b.live.zero_()
+        b.positions.zero_()
+        b.kv_len.fill_(1)
+        b.ids.zero_()
+        b.temperature.zero_()
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self._body(b, captured=self.use_graph)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+        if self.use_graph:
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                self._body(b, captured=True)
+            b.graph = g
+        b.warm = True
+
+    # ---- batches ----
+    def start(self, slots: Sequence[int], last_tokens: Sequence[int], seq_keys: Sequence[int],
+              step_keys: Sequence[int], sampling: Sequence[SamplingParams]) -> None:
+        """Sets the batch: ``last_tokens`` are the tokens to feed next; every sequence's
+        position is its current length in the cache."""
+        n = len(slots)
+        b = self._bucket(n)
+        self._prepare(b)
+        pad = b.size - n
+        lengths = [self.cache.length(s) for s in slots]
+        host = torch.tensor(
+            list(last_tokens) + [0] * pad + lengths + [0] * pad + [l + 1 for l in lengths] + [1] * pad
+            + list(slots) + [self.pad_slot] * pad + [1] * n + [0] * pad + list(seq_keys) + [0] * pad
+            + list(step_keys) + [0] * pad, dtype=torch.int32).view(7, b.size).to(self.ops.device)
+        b.ids.copy_(host[0]); b.positions.copy_(host[1]); b.kv_len.copy_(host[2]); b.slot.copy_(host[3])
+        b.live.copy_(host[4]); b.seq_key.copy_(host[5]); b.step_key.copy_(host[6])
+        fl = torch.tensor([p.temperature for p in sampling] + [0.0] * pad + [p.top_p for p in sampling] + [1.0] * pad,
+                          dtype=torch.float32).view(2, b.size).to(self.ops.device)
+        b.temperature.copy_(fl[0]); b.top_p.copy_(fl[1])
+        self.current = b
+        self.slots = list(slots)
+
+    def step(self) -> torch.Tensor:
+        """Runs one decode step of the current batch; returns the sampled tokens (device,
+        int32, one per live sequence; valid until the next step)."""
+        b = self.current
+        for s in self.slots:
+            self.cache.reserve(s, self.cache.length(s) + 1)
+        self.cache.sync()
+        if b.graph is not None:
+            b.graph.replay()
+        else:
+            self._body(b, captured=False)
+        for s in self.slots:
+            self.cache.set_length(s, self.cache.length(s) + 1)
+        return b.sampled[:len(self.slots)]
+
+    def logits(self) -> torch.Tensor:
+        """fp32 logits of the last step, one row per live sequence."""
+        return self.current.logits[:len(self.slots)]
+
+    def read_tokens(self) -> List[int]:
+        """The last step's sampled tokens on the host (waits for the step)."""
+        n = len(self.slots)
+        if self.pinned is None or self.pinned.numel() < self.current.size:
+            self.pinned = torch.empty(max(64, self.current.size), dtype=torch.int32).pin_memory()
+        self.pinned[:n].copy_(self.current.sampled[:n], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self.pinned[:n].tolist()

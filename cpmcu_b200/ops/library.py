@@ -34,6 +34,7 @@ _SIGNATURES = {
     "cpm_pool_keys": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "cpm_select_blocks": [_P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+    "cpm_advance_decode": [_P, _P, _P, _P, _P, _P, c_int, _P],
     "cpm_sample_rows": [_P, c_int64, c_int, c_int, _P, _P, _P, c_uint64, _P, _P, _P],
 }
 

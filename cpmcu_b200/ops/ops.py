@@ -226,3 +226,7 @@ class Ops:
                                          sparse.get("dense_len", 0), max_entries, self.code, _stream()),
               f"select_blocks ({max_entries} pooled keys)")
         return lists, bs
+
+    def advance_decode(self, ids, positions, kv_len, step_key, sampled, live) -> None:
+        check(self.lib.cpm_advance_decode(_ptr(ids), _ptr(positions), _ptr(kv_len), _ptr(step_key), _ptr(sampled),
+                                          _ptr(live), ids.numel(), _stream()), "advance_decode")

@@ -34,7 +34,8 @@ def read_folder(folder: str):
 
     with open(os.path.join(folder, "config.json")) as f:
         cfg = json.load(f)
-    return cfg, load_file(os.path.join(folder, "model.safetensors"))
+    # cloned: the reader's tensors are views of the file, which a test may rewrite
+    return cfg, {k: v.clone() for k, v in load_file(os.path.join(folder, "model.safetensors")).items()}
 
 
 _plain_cache: Dict[tuple, torch.Tensor] = {}

@@ -1,0 +1,164 @@
+"""Generation through the Python entry point and the command line, against the plain
+implementation generating greedily token by token."""
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+from tests import configs, helpers
+from tests.plain import minicpm4_plain as plain
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def plain_greedy(folder, prompt, n_new, stop=()):
+    cfg, w = helpers.read_folder(folder)
+    ids, out, rows = list(prompt), [], []
+    for _ in range(n_new):
+        logits = plain.forward(cfg, w, ids)[-1]
+        tok = plain.sample_token(logits, 0.0, 0.0)
+        rows.append(logits)
+        out.append(tok)
+        ids.append(tok)
+        if tok in stop:
+            break
+    return out, rows
+
+
+def check_greedy(folder, prompt, got, dtype, n_new, stop=()):
+    """fp32: the very tokens of the plain implementation.  bf16: every chosen token is
+    within the rounding margin of the plain implementation's best logit, given the
+    engine's own history."""
+    if dtype == "float32":
+        want, _ = plain_greedy(folder, prompt, n_new, stop)
+        assert got == want
+        return
+    cfg, w = helpers.read_folder(folder)
+    ids = list(prompt)
+    for tok in got:
+        logits = plain.forward(cfg, w, ids)[-1]
+        margin = helpers.TOL["bfloat16"] * float(logits.abs().max())
+        assert float(logits[tok]) >= float(logits.max()) - 2 * margin, (len(ids), tok)
+        ids.append(tok)
+
+
+@pytest.mark.parametrize("graph", [False, True])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_batch_tiny_a(model_folders, dtype, graph):
+    """Tiny A's workload: batch 3 with prompts of 5/17/33 tokens, 16 greedy steps."""
+    from cpmcu_b200 import LLM
+
+    folder = model_folders("tiny_a", configs.tiny_a(), 0, dtype)
+    llm = LLM(folder, dtype=dtype, cuda_graph=graph, max_tokens=64 * 16, chunk_length=64)
+    prompts = [helpers.random_ids(512, n, 7 + n) for n in (5, 17, 33)]
+    res = llm.generate_batch(prompts, generation_length=16)
+    for p, r in zip(prompts, res):
+        assert len(r.tokens) == 16 and r.reason == "length"
+        check_greedy(folder, p, r.tokens, dtype, 16)
+    # the same requests one at a time give the same tokens
+    if dtype == "float32":
+        for p, r in zip(prompts, res):
+            toks, _, _ = llm.generate(p, generation_length=16)
+            assert toks == r.tokens
+    llm.cache.check_consistent()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_tiny_b_sampling_batch(model_folders, dtype):
+    """Tiny B's workload: batch 4 with prompts of 1/40/97/150 tokens, 24 steps at temperature
+    0.8 with a fixed seed.  A sequence's draws do not depend on its batch: each request run
+    alone gives the same tokens."""
+    from cpmcu_b200 import LLM
+
+    folder = model_folders("tiny_b", configs.tiny_b(), 1, dtype)
+    prompts = [helpers.random_ids(1000, n, 3 + n) for n in (1, 40, 97, 150)]
+    llm = LLM(folder, dtype=dtype, cuda_graph=True, temperature=0.8, random_seed=11, max_tokens=64 * 24)
+    res = llm.generate_batch(prompts, generation_length=24)
+    again = llm.generate_batch(prompts, generation_length=24)
+    assert [r.tokens for r in res] == [r.tokens for r in again]
+    assert all(len(r.tokens) == 24 for r in res)
+    if dtype == "float32":
+        # every drawn token is what the plain implementation draws from its own logits with the same random number
+        cfg, w = helpers.read_folder(folder)
+        for i in (0, 2):
+            ids = list(prompts[i])
+            for n, tok in enumerate(res[i].tokens[:6]):
+                logits = plain.forward(cfg, w, ids)[-1]
+                u = plain.philox_uniform(11, i, n)
+                wts = plain.sampling_weights(logits, 0.8)
+                c = torch.cumsum(wts, 0)
+                lo = float(c[tok - 1]) if tok > 0 else 0.0
+                slack = 1e-4 * float(c[-1])
+                assert lo - slack <= u * float(c[-1]) <= float(c[tok]) + slack
+                ids.append(tok)
+
+
+def test_stop_tokens_and_lengths(model_folders):
+    from cpmcu_b200 import LLM
+
+    folder = model_folders("tiny_a", configs.tiny_a(), 0, "float32")
+    llm = LLM(folder, dtype="float32", cuda_graph=True, max_tokens=64 * 8, max_batch=2)
+    prompts = [helpers.random_ids(512, n, 70 + n) for n in (9, 30, 4, 12, 21)]
+    free = llm.generate_batch(prompts, generation_length=12)
+    stop = free[1].tokens[3]
+    res = llm.generate_batch(prompts, generation_length=12, terminators=[stop])
+    for p, r, f in zip(prompts, res, free):
+        if stop in f.tokens:
+            cut = f.tokens.index(stop) + 1
+            assert r.tokens == f.tokens[:cut] and r.reason == "stop"      # the stop token is kept
+        else:
+            assert r.tokens == f.tokens and r.reason == "length"
+    assert llm.last_stats.batches == 3                                      # five requests, two at a time
+    llm.cache.check_consistent()
+    assert llm.cache.slots.n_held == 1                                      # only the decode runner's scratch sequence
+
+
+def test_stream_and_cli(model_folders):
+    from cpmcu_b200 import LLM
+
+    folder = model_folders("tiny_c", configs.tiny_c(), 5, "bfloat16")
+    llm = LLM(folder, max_tokens=64 * 4)
+    prompt = helpers.random_ids(777, 11, 1)
+    toks, decode_time, prefill_time = llm.generate(prompt, generation_length=8)
+    items = list(llm.generate(prompt, generation_length=8, use_stream=True))
+    assert [it["token"] for it in items] == toks
+    assert items[-1]["is_finished"] and not items[0]["is_finished"]
+    out = subprocess.run([sys.executable, "-m", "cpmcu_b200.cli", "--model-path", folder, "--prompt-ids",
+                          ",".join(map(str, prompt)), "--num-generate", "8", "--use-stream", "false",
+                          "--max-tokens", "256"], cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    assert out.stdout.strip() == "[0] " + " ".join(map(str, toks))
+
+
+def test_trace_run_program(model_folders, tmp_path):
+    """bin/trace_run end to end: two requests start together, the shorter ends first."""
+    import json
+    import numpy as np
+
+    folder = model_folders("tiny_a", configs.tiny_a(), 0, "float32")
+    a, b = helpers.random_ids(512, 40, 1), helpers.random_ids(512, 75, 2)
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": a[:30], "want": [29, 0]},
+                                     {"id": "b", "tokens": b[:70], "want": []}], "end": []}]
+    for t in range(10):
+        entries = [{"id": "a", "tokens": [a[30 + t]], "want": [0]}]
+        if t < 5:
+            entries.append({"id": "b", "tokens": [b[70 + t]], "want": [0]})
+        steps.append({"step": t + 1, "entries": entries, "end": (["b"] if t == 4 else []) + (["a"] if t == 9 else [])})
+    out_dir = tmp_path / "out"
+    env = dict(os.environ)
+    p = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", "float32",
+                        "--out", str(out_dir), "--max-tokens", "256"],
+                       input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True,
+                       timeout=600, env=env)
+    assert p.returncode == 0, p.stderr
+    assert p.stdout.split() == [x for s in steps for x in ("done", str(s["step"]))]
+    wa, wb = helpers.plain_logits(folder, a), helpers.plain_logits(folder, b)
+    got0 = torch.from_numpy(np.fromfile(out_dir / "0.f32", dtype="<f4").reshape(2, 512))
+    assert helpers.rel_err(got0, wa[[29, 0]]) < helpers.TOL["float32"]
+    for t in range(10):
+        got = torch.from_numpy(np.fromfile(out_dir / f"{t + 1}.f32", dtype="<f4").reshape(-1, 512))
+        want = [wa[30 + t]] + ([wb[70 + t]] if t < 5 else [])
+        assert helpers.rel_err(got, torch.stack(want)) < helpers.TOL["float32"]
