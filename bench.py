@@ -1,0 +1,316 @@
+#!/usr/bin/env python3
+"""Benchmark: decode tokens/s (batch 1, 8, 64) and prefill tokens/s (2,048 tokens) of a
+MiniCPM4-8B-sized model with random bf16 weights on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A "step" is one decode step of the whole batch.  The default run is batch 8 with the
+sequences ending at the context length of 4,096 tokens.  One JSON line is printed.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# MiniCPM4-8B layer sizes; random weights N(0, 0.02), seed 2; bf16.
+MODEL = {
+    "architectures": ["MiniCPMForCausalLM"], "model_type": "minicpm",
+    "num_hidden_layers": 32, "hidden_size": 4096, "num_attention_heads": 32, "num_key_value_heads": 2,
+    "head_dim": 128, "intermediate_size": 16384, "vocab_size": 73448,
+    "rope_theta": 10000.0, "max_position_embeddings": 65536, "rms_norm_eps": 1e-6,
+    "scale_emb": 12, "dim_model_base": 256, "scale_depth": 1.4, "tie_word_embeddings": False,
+    "hidden_act": "silu", "torch_dtype": "bfloat16",
+}
+FULL_LAYERS = 32
+CONTEXT = 4096
+PREFILL_TOKENS = 2048
+SEED = 2
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def long_factors(n: int) -> list:
+    import torch
+    g = torch.Generator().manual_seed(SEED)
+    return sorted((1.0 + 39.0 * torch.rand(n, generator=g)).tolist())
+
+
+def peaks() -> dict:
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    out = dict(FALLBACK_PEAKS, source="fallback")
+    try:
+        with open(path) as f:
+            data = json.load(f)
+        if "hbm_gbs" in data and "bf16_tflops" in data:
+            out = {"hbm_gbs": float(data["hbm_gbs"]), "bf16_tflops": float(data["bf16_tflops"]), "source": "measured"}
+    except (OSError, ValueError):
+        pass
+    return out
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples, self.proc, self.thread = [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) >= 6:
+                self.samples.append(parts)
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, reasons, mx = [], set(), None
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for p in self.samples:
+            try:
+                sm.append(float(p[0]))
+                mx = float(p[1])
+            except ValueError:
+                continue
+            for name, v in zip(names, p[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def reference_arm() -> int:
+    """The reference cannot be installed offline here: its attention sources include
+    cute/tensor.hpp from the cutlass submodule, which is empty in the mounted tree."""
+    print(json.dumps({"impl": "reference",
+                      "unavailable": "pip install of the reference fails offline: src/cutlass submodule is empty "
+                                     "(flash_fwd_kernel.h:7: cute/tensor.hpp: No such file or directory)"}))
+    return 0
+
+
+def build_engine(n_layers: int, max_tokens: int, max_batch: int):
+    import torch
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.engine import Stepper
+    from cpmcu_b200.loading import build_model
+    from cpmcu_b200.registry import architecture
+    from cpmcu_b200.weights import random_tensors
+
+    cfgd = dict(MODEL, num_hidden_layers=n_layers)
+    cfgd["rope_scaling"] = {"rope_type": "longrope", "long_factor": long_factors(64), "short_factor": [1.0] * 64,
+                            "original_max_position_embeddings": 32768}
+    arch = architecture("MiniCPMForCausalLM")
+    cfg = arch.config_class.from_dict(cfgd)
+    # the residual scale of the full depth, whatever number of layers is built
+    model = build_model(arch, cfg, torch.bfloat16, "cuda:0")
+    specs = model.weight_specs()
+    model.load_weights(random_tensors(specs, SEED, torch.bfloat16, std=0.02, norm_mean=1.0, device="cuda:0"))
+    cache = Cache(model.cache_needs(), max_tokens=max_tokens, dtype=torch.bfloat16, device="cuda:0",
+                  n_slots=max_batch + 2, max_seq_tokens=CONTEXT + 64)
+    return cfg, model, cache, Stepper(model, cache, chunk_tokens=PREFILL_TOKENS)
+
+
+def random_prompt(vocab: int, n: int, seed: int) -> list:
+    import torch
+    g = torch.Generator().manual_seed(seed)
+    return torch.randint(0, vocab, (n,), generator=g).tolist()
+
+
+def time_decode(stepper, batch: int, steps: int, warmup: int, vocab: int, sample_clocks: bool = False):
+    """Sequences are prefilled so that the timed steps end at the context length; returns
+    (ms per step, clocks, launches in the timed region, bytes of cache read per step)."""
+    import torch
+    from cpmcu_b200.engine import SequenceStep
+    from cpmcu_b200.engine.decode import DecodeRunner
+    from cpmcu_b200.ops import library
+    from cpmcu_b200.sampling import SamplingParams
+
+    start_len = CONTEXT - steps - warmup - 1
+    slots = stepper.open(batch)
+    first = []
+    for i, s in enumerate(slots):                       # one prompt per step keeps the workspace small
+        out = stepper.step([SequenceStep(s, random_prompt(vocab, start_len, 100 + i), [start_len - 1])])
+        first.append(int(out.argmax(dim=-1)[0]))
+    runner = DecodeRunner(stepper, use_graph=True, seed=SEED)
+    runner.start(slots, first, list(range(batch)), [1] * batch, [SamplingParams()] * batch)
+    runner.step()
+    for _ in range(max(0, warmup - 1)):
+        runner.step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler()
+    if sample_clocks:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        runner.step()
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    clocks = sampler.stop() if sample_clocks else None
+    mean_ctx = CONTEXT - 1 - steps / 2
+    cache_bytes = sum(stepper.model.blocks[e.layer].mixer.cache_bytes_read(int(mean_ctx)) for e in stepper.model.schedule) * batch
+    launches = runner.launches_per_graph * steps
+    for s in slots:
+        stepper.close(s)
+    stepper.close(runner.pad_slot)
+    return ms, clocks, launches, cache_bytes
+
+
+def time_prefill(stepper, cfg, reps: int = 3):
+    import torch
+    from cpmcu_b200.engine import SequenceStep
+
+    times = []
+    for r in range(reps + 1):
+        ids = random_prompt(cfg.vocab_size, PREFILL_TOKENS, 500 + r)
+        slot = stepper.open(1)[0]
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        stepper.step([SequenceStep(slot, ids, [PREFILL_TOKENS - 1])])
+        e1.record()
+        torch.cuda.synchronize()
+        if r > 0:
+            times.append(e0.elapsed_time(e1))
+        stepper.close(slot)
+    return statistics.median(times)
+
+
+def prefill_flops(cfg, n_layers: int, tokens: int) -> float:
+    h, d = cfg.hidden_size, cfg.head_dim
+    per_layer = (cfg.num_attention_heads + 2 * cfg.num_key_value_heads) * d * h + cfg.num_attention_heads * d * h \
+        + 3 * cfg.intermediate_size * h
+    gemm = 2.0 * tokens * per_layer * n_layers + 2.0 * cfg.vocab_size * h
+    attn = 4.0 * cfg.num_attention_heads * d * tokens * tokens / 2 * n_layers
+    return gemm + attn
+
+
+def time_e2e(cfg, model, steps: int, batch: int):
+    """The same decode metric through the Python entry point: host token lists in,
+    host token lists out, one device-to-host read of the sampled tokens per step."""
+    import torch
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.engine import Stepper
+    from cpmcu_b200.engine.backend import EngineBackend
+    from cpmcu_b200.engine.generate import Request, run_requests
+    from cpmcu_b200.sampling import SamplingParams
+
+    cache = Cache(model.cache_needs(), max_tokens=batch * (CONTEXT + 64) + 64, dtype=torch.bfloat16, device="cuda:0",
+                  n_slots=batch + 2, max_seq_tokens=CONTEXT + 64)
+    stepper = Stepper(model, cache, chunk_tokens=PREFILL_TOKENS)
+    backend = EngineBackend(stepper, max_batch=batch, use_graph=True, seed=SEED)
+    n_new = steps + 1
+    prompts = [random_prompt(cfg.vocab_size, CONTEXT - n_new, 900 + i) for i in range(batch)]
+    reqs = [Request(p, n_new, SamplingParams(), (), key=i) for i, p in enumerate(prompts)]
+    run_requests(backend, [Request(p[:64], 4, SamplingParams(), (), key=i) for i, p in enumerate(prompts)],
+                 sync=torch.cuda.synchronize)                       # warm-up: graph capture
+    h0, d0 = backend.h2d_bytes, backend.d2h_bytes
+    results, stats = run_requests(backend, reqs, sync=torch.cuda.synchronize)
+    assert all(len(r.tokens) == n_new for r in results)
+    decode_steps = max(1, stats.decode_steps)
+    prompt_bytes = 4 * sum(len(p) for p in prompts)
+    return {
+        "value": batch * decode_steps / stats.decode_time, "unit": "tokens/s",
+        "h2d_bytes_per_step": (backend.h2d_bytes - h0 - prompt_bytes) / decode_steps,
+        "d2h_bytes_per_step": (backend.d2h_bytes - d0) / (decode_steps + 1),
+        "prefill_tokens_per_s": stats.prompt_tokens / stats.prefill_time,
+    }
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="layers built (the full model has 32)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the e2e run")
+    a = ap.parse_args()
+    if a.impl == "reference":
+        return reference_arm()
+    if a.gpus != 1:
+        print("bench.py: this library runs on one GPU; --gpus must be 1")
+        return 2
+    a.warmup = max(3, a.warmup)
+    import torch
+    from cpmcu_b200.ops import library
+
+    pk = peaks()
+    max_batch = a.batch if a.no_points else max(64, a.batch)
+    cfg, model, cache, stepper = build_engine(a.layers, max_batch * (CONTEXT + 64) + 128, max_batch)
+    weight_bytes = model.weight_bytes_per_step()
+
+    ms, clocks, launches, cache_bytes = time_decode(stepper, a.batch, a.steps, a.warmup, cfg.vocab_size, True)
+    value = a.batch * 1000.0 / ms
+    achieved = (weight_bytes + cache_bytes) / (ms * 1e-3) / 1e9
+
+    pre_ms = time_prefill(stepper, cfg)
+    flops = prefill_flops(cfg, a.layers, PREFILL_TOKENS)
+    prefill = {"value": PREFILL_TOKENS / (pre_ms * 1e-3), "tokens": PREFILL_TOKENS, "ms": pre_ms,
+               "frac": flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)}
+
+    points, e2e = {}, None
+    if not a.no_points:
+        for b in (1, 64):
+            pms, _, _, _ = time_decode(stepper, b, min(a.steps, 64), a.warmup, cfg.vocab_size)
+            points[f"decode_b{b}"] = b * 1000.0 / pms
+        del stepper, cache
+        torch.cuda.empty_cache()
+        e2e = time_e2e(cfg, model, a.steps, a.batch)
+
+    line = {
+        "metric": "decode tokens/s (MiniCPM4-8B sizes, bf16, batch 8, context 4096)",
+        "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": a.steps, "warmup": a.warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: uniform-random token ids, random weights N(0,0.02) seed 2",
+        "impl": "ours",
+        "config": {
+            "model": "MiniCPM4-8B sizes", "layers": a.layers, "layers_full": FULL_LAYERS, "hidden": cfg.hidden_size,
+            "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+            "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "global_batch": a.batch,
+            "seq_len": CONTEXT, "prefill_tokens": PREFILL_TOKENS, "parallelism": "single GPU",
+            "rope": "longrope", "attention": "dense", "l2": "inputs larger than L2 (weights read per step)",
+            "peaks": pk["source"], "cuda_graph": True,
+        },
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"]},
+        "points": points,
+        "clocks": clocks,
+        "gpu_launches": launches,
+    }
+    if e2e is not None:
+        line["e2e"] = e2e
+    print(json.dumps(line))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

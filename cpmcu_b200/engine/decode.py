@@ -49,6 +49,7 @@ class _Bucket:
         self.logits: Optional[torch.Tensor] = None
         self.graph: Optional[torch.cuda.CUDAGraph] = None
         self.warm = False
+        self.launches = 0           # kernels of this library in one step
 
 
 class DecodeRunner:
@@ -67,7 +68,6 @@ class DecodeRunner:
         self.current: Optional[_Bucket] = None
         self.slots: List[int] = []
         self.pinned = None
-        self.launches_per_step = 0
 
     # ---- one step's work on the device ----
     def _body(self, b: _Bucket, captured: bool) -> None:
@@ -102,10 +102,13 @@ class DecodeRunner:
         b.ids.zero_()
         b.temperature.zero_()
         torch.cuda.synchronize()
+        from ..ops import library
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
+        before = library.LAUNCHES[0]
         with torch.cuda.stream(side):
             self._body(b, captured=self.use_graph)
+        b.launches = library.LAUNCHES[0] - before
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
         if self.use_graph:
@@ -151,6 +154,10 @@ class DecodeRunner:
         for s in self.slots:
             self.cache.set_length(s, self.cache.length(s) + 1)
         return b.sampled[:len(self.slots)]
+
+    @property
+    def launches_per_graph(self) -> int:
+        return self.current.launches if self.current is not None else 0
 
     def logits(self) -> torch.Tensor:
         """fp32 logits of the last step, one row per live sequence."""

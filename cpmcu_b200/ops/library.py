@@ -83,8 +83,12 @@ def declare(name: str, argtypes) -> None:
         fn.restype = c_int
 
 
+LAUNCHES = [0]      # kernels of this library launched (or recorded into a graph) so far
+
+
 def check(status: int, what: str) -> None:
     if status == 0:
+        LAUNCHES[0] += 1
         return
     if status == -1:
         raise ValueError(f"{what}: the kernel does not take these sizes")
