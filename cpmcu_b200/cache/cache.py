@@ -5,8 +5,8 @@ uses (its keys and values for every sequence, its pooled keys, its state).  Lane
 with the same needs form a *group* that shares one storage tensor, one pool of
 pages and one page table; lanes with other needs (another head count, a window
 instead of all keys, pooled keys) form a group of their own.  A sequence's tokens
-live in pages of 64 tokens; inside a page the layout is
-[kv_head][token_in_page][head_dim].  Pages and slots go back to the free lists when
+live in pages of 64 tokens; a key page is [kv_head][token_in_page][head_dim], a value
+page is its transpose [kv_head][head_dim][token_in_page].  Pages and slots go back to the free lists when
 a sequence ends and are used again as they are: only a slot's state is cleared, its
 pages never are.
 
@@ -47,9 +47,10 @@ class CacheGroup:
         n = len(lanes)
         self.k = self.v = self.pooled = None
         if needs.kv_heads > 0:
-            shape = (n, n_pages, needs.kv_heads, PAGE_TOKENS, needs.head_dim)
-            self.k = torch.empty(shape, dtype=dtype, device=device)
-            self.v = torch.empty(shape, dtype=dtype, device=device)
+            # zeros, not empty: a kernel may multiply a masked weight of 0 with whatever a page
+            # holds beyond the sequence's end, and that has to be a finite number
+            self.k = torch.zeros((n, n_pages, needs.kv_heads, PAGE_TOKENS, needs.head_dim), dtype=dtype, device=device)
+            self.v = torch.zeros((n, n_pages, needs.kv_heads, needs.head_dim, PAGE_TOKENS), dtype=dtype, device=device)
             if needs.pooled_stride > 0:
                 if PAGE_TOKENS % needs.pooled_stride:
                     raise ValueError(f"pooled-key stride {needs.pooled_stride} must divide the page size {PAGE_TOKENS}")

@@ -1,0 +1,350 @@
+// bf16 attention over the paged cache on the tensor cores, for decode (one query token
+// per sequence, split over the keys) and for prefill (many query tokens per sequence).
+//
+// One warp owns a tile of 16 query rows and walks over key pages.  Keys are read
+// straight from global memory into mma fragments with 16-byte loads along head_dim, and
+// values likewise along the token axis of the transposed value pages, so there is no
+// shared-memory staging and no barrier: the sums over head_dim and over keys do not
+// care about order, which lets a thread's 8 consecutive elements stand for the k-slots
+// of two m16n8k16 instructions as long as both operands use the same assignment.
+//
+// Decode: the 16 rows are the query heads that share one key-value head (grouped-query
+// attention), every warp takes a share of the sequence's pages and writes an unnormalised
+// partial result; a second kernel combines the shares.  The reference runs its flash
+// kernel with 16 fixed splits and a combine kernel (src/flash_attn/flash_api.hpp:385-391,
+// src/flash_attn/src/flash_fwd_kernel.h:2320-2501).  Prefill: the 16 rows are consecutive
+// tokens of one head; the causal rule is per row (src/flash_attn/src/mask.h:185-211).
+// Softmax statistics, scores and output accumulators are fp32; probabilities are rounded
+// to bf16 for the second product, as in the reference (src/flash_attn/src/flash_fwd_kernel.h:1560-1616).
+#include "common.cuh"
+
+__device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                          uint32_t b0, uint32_t b1) {
+    asm volatile(
+        "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+__device__ __forceinline__ uint4 ldg16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+
+// State of a 16-row tile in one warp: thread (g = lane / 4, j = lane % 4) holds rows g and
+// g + 8; o[nt] are output dims 8*nt + 2j, 2j+1 of both rows.
+template <int D>
+struct TileState {
+    float o[D / 8][4];
+    float m[2];      // running maximum of the scaled scores (log2 domain)
+    float l[2];      // this thread's share of the running sum
+    __device__ __forceinline__ void init() {
+#pragma unroll
+        for (int i = 0; i < D / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+        m[0] = m[1] = -INFINITY;
+        l[0] = l[1] = 0.f;
+    }
+};
+
+// One page of 64 keys.  q[r][w]: 8 consecutive dims 32w + 8j .. of row g (r = 0) and g + 8
+// (r = 1).  Keys with index > limit[r] (index inside the sequence) are masked for row r.
+// Column n = 2j' + e of score tile t in the 32-key half u stands for key
+// 32u + 8j' + 2t + e, so that thread j ends up with the probabilities of 8 consecutive
+// keys, which is what the 16-byte value loads along the token axis need.
+template <int D>
+__device__ __forceinline__ void attend_page(TileState<D>& st, const uint4 (&q)[2][D / 32], const bf16* __restrict__ kpage,
+                                            const bf16* __restrict__ vpage, int key0, int limit0, int limit1,
+                                            float scale_log2, int lane) {
+    const int j = lane & 3, n = lane >> 2;
+    float s[2][4][4];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            s[u][t][0] = s[u][t][1] = s[u][t][2] = s[u][t][3] = 0.f;
+            const int krow = 32 * u + 8 * (n >> 1) + 2 * t + (n & 1);
+            const bf16* kp = kpage + krow * D + 8 * j;
+#pragma unroll
+            for (int w = 0; w < D / 32; ++w) {
+                const uint4 kv = ldg16(kp + 32 * w);
+                mma_16816(s[u][t], q[0][w].x, q[1][w].x, q[0][w].y, q[1][w].y, kv.x, kv.y);
+                mma_16816(s[u][t], q[0][w].z, q[1][w].z, q[0][w].w, q[1][w].w, kv.z, kv.w);
+            }
+        }
+    }
+    // scale, mask, row maxima
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = key0 + 32 * u + 8 * j + 2 * t + e;
+                const float a = key <= limit0 ? s[u][t][e] * scale_log2 : -INFINITY;
+                const float b = key <= limit1 ? s[u][t][2 + e] * scale_log2 : -INFINITY;
+                s[u][t][e] = a;
+                s[u][t][2 + e] = b;
+                mx0 = fmaxf(mx0, a);
+                mx1 = fmaxf(mx1, b);
+            }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(st.m[0], mx0), mn1 = fmaxf(st.m[1], mx1);
+    const float use0 = mn0 == -INFINITY ? 0.f : mn0, use1 = mn1 == -INFINITY ? 0.f : mn1;
+    const float corr0 = exp2f(st.m[0] - use0), corr1 = exp2f(st.m[1] - use1);
+    st.m[0] = mn0;
+    st.m[1] = mn1;
+    float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const float a = exp2f(s[u][t][e] - use0), b = exp2f(s[u][t][2 + e] - use1);
+                s[u][t][e] = a;
+                s[u][t][2 + e] = b;
+                sum0 += a;
+                sum1 += b;
+            }
+    st.l[0] = st.l[0] * corr0 + sum0;
+    st.l[1] = st.l[1] * corr1 + sum1;
+#pragma unroll
+    for (int nt = 0; nt < D / 8; ++nt) {
+        st.o[nt][0] *= corr0;
+        st.o[nt][1] *= corr0;
+        st.o[nt][2] *= corr1;
+        st.o[nt][3] *= corr1;
+    }
+    // weighted sum of values
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const uint32_t a0 = pack_bf16(s[u][0][0], s[u][0][1]), a1 = pack_bf16(s[u][0][2], s[u][0][3]);
+        const uint32_t a2 = pack_bf16(s[u][1][0], s[u][1][1]), a3 = pack_bf16(s[u][1][2], s[u][1][3]);
+        const uint32_t c0 = pack_bf16(s[u][2][0], s[u][2][1]), c1 = pack_bf16(s[u][2][2], s[u][2][3]);
+        const uint32_t c2 = pack_bf16(s[u][3][0], s[u][3][1]), c3 = pack_bf16(s[u][3][2], s[u][3][3]);
+        const bf16* vp = vpage + n * kPageTokens + 32 * u + 8 * j;
+#pragma unroll
+        for (int nt = 0; nt < D / 8; ++nt) {
+            const uint4 vv = ldg16(vp + nt * 8 * kPageTokens);
+            mma_16816(st.o[nt], a0, a1, a2, a3, vv.x, vv.y);
+            mma_16816(st.o[nt], c0, c1, c2, c3, vv.z, vv.w);
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------
+// decode
+// ---------------------------------------------------------------------------
+template <int D>
+__global__ void __launch_bounds__(128)
+decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                        const int* __restrict__ kv_len, const int* __restrict__ slots,
+                        const int* __restrict__ page_table, int max_pages, float* __restrict__ part_o,
+                        float* __restrict__ part_ml, int n_heads, int n_kv, int m_tiles, int n_splits,
+                        float scale_log2) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int split = blockIdx.x * 4 + warp;
+    if (split >= n_splits) return;
+    const int kvh = blockIdx.y / m_tiles, mt = blockIdx.y % m_tiles, b = blockIdx.z;
+    const int group = n_heads / n_kv;
+    const int j = lane & 3, g = lane >> 2;
+    const int len = kv_len[b];
+    const int n_pages = (len + kPageTokens - 1) / kPageTokens;
+    const int per = (n_pages + n_splits - 1) / n_splits;
+    const int p0 = split * per, p1 = min(n_pages, p0 + per);
+
+    TileState<D> st;
+    st.init();
+    if (p0 < p1) {
+        uint4 qf[2][D / 32];
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int local = mt * 16 + g + 8 * r;
+            const bool valid = local < group;
+            const bf16* qrow = q + ((int64_t)b * n_heads + kvh * group + (valid ? local : 0)) * D + 8 * j;
+#pragma unroll
+            for (int w = 0; w < D / 32; ++w) qf[r][w] = valid ? ldg16(qrow + 32 * w) : make_uint4(0, 0, 0, 0);
+        }
+        const int* pages = page_table + (int64_t)slots[b] * max_pages;
+        for (int p = p0; p < p1; ++p) {
+            const int page = pages[p];
+            const bf16* kpage = k_cache + ((int64_t)page * n_kv + kvh) * kPageTokens * D;
+            const bf16* vpage = v_cache + ((int64_t)page * n_kv + kvh) * D * kPageTokens;
+            attend_page<D>(st, qf, kpage, vpage, p * kPageTokens, len - 1, len - 1, scale_log2, lane);
+        }
+    }
+    // this thread's shares of the row sums -> whole rows
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
+        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+    }
+    const int64_t unit = (((int64_t)b * n_kv + kvh) * m_tiles + mt) * n_splits + split;
+    float* po = part_o + unit * 16 * D;
+#pragma unroll
+    for (int nt = 0; nt < D / 8; ++nt) {
+        *reinterpret_cast<float2*>(po + g * D + 8 * nt + 2 * j) = make_float2(st.o[nt][0], st.o[nt][1]);
+        *reinterpret_cast<float2*>(po + (g + 8) * D + 8 * nt + 2 * j) = make_float2(st.o[nt][2], st.o[nt][3]);
+    }
+    if (j == 0) {
+        float* pm = part_ml + unit * 32;
+        pm[2 * g] = st.m[0];
+        pm[2 * g + 1] = st.l[0];
+        pm[2 * (g + 8)] = st.m[1];
+        pm[2 * (g + 8) + 1] = st.l[1];
+    }
+}
+
+// out[b, h, :] = sum_s o_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M)
+__global__ void combine_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                      bf16* __restrict__ out, int n_heads, int n_kv, int m_tiles, int n_splits,
+                                      int D) {
+    const int h = blockIdx.x, b = blockIdx.y;
+    const int group = n_heads / n_kv;
+    const int kvh = h / group, local = h % group;
+    const int mt = local / 16, row = local % 16;
+    const int64_t unit0 = (((int64_t)b * n_kv + kvh) * m_tiles + mt) * n_splits;
+    float mx = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, part_ml[(unit0 + s) * 32 + 2 * row]);
+    float denom = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float m = part_ml[(unit0 + s) * 32 + 2 * row];
+        if (m != -INFINITY) denom += part_ml[(unit0 + s) * 32 + 2 * row + 1] * exp2f(m - mx);
+    }
+    const float inv = denom > 0.f ? 1.f / denom : 0.f;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float m = part_ml[(unit0 + s) * 32 + 2 * row];
+            if (m != -INFINITY) acc += part_o[((unit0 + s) * 16 + row) * D + c] * exp2f(m - mx);
+        }
+        out[((int64_t)b * n_heads + h) * D + c] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
+// Floats of scratch the decode kernels need for these sizes.
+CPM_API int64_t cpm_decode_attention_scratch_floats(int n_seqs, int n_heads, int n_kv, int d, int n_splits) {
+    const int m_tiles = (n_heads / n_kv + 15) / 16;
+    return (int64_t)n_seqs * n_kv * m_tiles * n_splits * (16 * d + 32);
+}
+
+template <int D>
+static int launch_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int* kv_len,
+                         const int* slots, const int* page_table, int max_pages, float* scratch, int n_seqs,
+                         int n_heads, int n_kv, int n_splits, float scale, cudaStream_t stream) {
+    const int m_tiles = (n_heads / n_kv + 15) / 16;
+    float* part_o = scratch;
+    float* part_ml = scratch + (int64_t)n_seqs * n_kv * m_tiles * n_splits * 16 * D;
+    dim3 grid((n_splits + 3) / 4, n_kv * m_tiles, n_seqs);
+    decode_attention_kernel<D><<<grid, 128, 0, stream>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
+        kv_len, slots, page_table, max_pages, part_o, part_ml, n_heads, n_kv, m_tiles, n_splits,
+        scale * 1.4426950408889634f);
+    combine_splits_kernel<<<dim3(n_heads, n_seqs), D >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, (bf16*)out, n_heads,
+                                                                               n_kv, m_tiles, n_splits, D);
+    return launch_status();
+}
+
+// q [n_seqs, heads, d] bf16, one token per sequence; out [n_seqs, heads, d] bf16.
+CPM_API int cpm_decode_attention_bf16(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                      const int* kv_len, const int* slots, const int* page_table, int max_pages,
+                                      float* scratch, int n_seqs, int n_heads, int n_kv, int d, int n_splits,
+                                      float scale, cudaStream_t stream) {
+    if (n_seqs <= 0) return CPM_OK;
+    if (n_kv <= 0 || n_heads % n_kv || n_splits < 1 || n_seqs > 65535 || !scratch) return CPM_BAD_ARGUMENT;
+    switch (d) {
+        case 32: return launch_decode<32>(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream);
+        case 64: return launch_decode<64>(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream);
+        case 96: return launch_decode<96>(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream);
+        case 128: return launch_decode<128>(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream);
+        default: return CPM_BAD_ARGUMENT;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// prefill
+// ---------------------------------------------------------------------------
+// A block of 4 warps takes 64 consecutive query tokens of one sequence and one head;
+// tile_seq/tile_row name the sequence (index in the batch) and the first of the 64
+// tokens (offset inside this step's tokens of the sequence) of every block.
+template <int D>
+__global__ void __launch_bounds__(128)
+prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                         bf16* __restrict__ out, const int* __restrict__ tile_seq, const int* __restrict__ tile_row,
+                         const int* __restrict__ cu_q, const int* __restrict__ kv_len, const int* __restrict__ slots,
+                         const int* __restrict__ page_table, int max_pages, int n_heads, int n_kv, float scale_log2) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int j = lane & 3, g = lane >> 2;
+    const int seq = tile_seq[blockIdx.x], h = blockIdx.y;
+    const int kvh = h / (n_heads / n_kv);
+    const int q_begin = cu_q[seq], q_len = cu_q[seq + 1] - q_begin;
+    const int row0 = tile_row[blockIdx.x] + 16 * warp;           // first of this warp's 16 tokens
+    if (row0 >= q_len) return;
+    const int history = kv_len[seq] - q_len;                     // keys cached before this step's tokens
+
+    uint4 qf[2][D / 32];
+    int limit[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = row0 + g + 8 * r;
+        const bool valid = row < q_len;
+        limit[r] = valid ? history + row : -1;
+        const bf16* qrow = q + ((int64_t)(q_begin + (valid ? row : 0)) * n_heads + h) * D + 8 * j;
+#pragma unroll
+        for (int w = 0; w < D / 32; ++w) qf[r][w] = valid ? ldg16(qrow + 32 * w) : make_uint4(0, 0, 0, 0);
+    }
+    TileState<D> st;
+    st.init();
+    const int last_key = history + min(row0 + 15, q_len - 1);
+    const int* pages = page_table + (int64_t)slots[seq] * max_pages;
+    for (int p = 0; p <= last_key / kPageTokens; ++p) {
+        const int page = pages[p];
+        const bf16* kpage = k_cache + ((int64_t)page * n_kv + kvh) * kPageTokens * D;
+        const bf16* vpage = v_cache + ((int64_t)page * n_kv + kvh) * D * kPageTokens;
+        attend_page<D>(st, qf, kpage, vpage, p * kPageTokens, limit[0], limit[1], scale_log2, lane);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
+        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+        const int row = row0 + g + 8 * r;
+        if (row >= q_len) continue;
+        const float inv = st.l[r] > 0.f ? 1.f / st.l[r] : 0.f;
+        bf16* orow = out + ((int64_t)(q_begin + row) * n_heads + h) * D + 2 * j;
+#pragma unroll
+        for (int nt = 0; nt < D / 8; ++nt)
+            *reinterpret_cast<uint32_t*>(orow + 8 * nt) = pack_bf16(st.o[nt][2 * r] * inv, st.o[nt][2 * r + 1] * inv);
+    }
+}
+
+template <int D>
+static int launch_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq,
+                          const int* tile_row, int n_tiles, const int* cu_q, const int* kv_len, const int* slots,
+                          const int* page_table, int max_pages, int n_heads, int n_kv, float scale,
+                          cudaStream_t stream) {
+    prefill_attention_kernel<D><<<dim3(n_tiles, n_heads), 128, 0, stream>>>((const bf16*)q, (const bf16*)k_cache,
+        (const bf16*)v_cache, (bf16*)out, tile_seq, tile_row, cu_q, kv_len, slots, page_table, max_pages, n_heads, n_kv,
+        scale * 1.4426950408889634f);
+    return launch_status();
+}
+
+// q, out [tokens, heads, d] bf16, tokens packed by sequence (cu_q); the cache already holds this step's keys.
+CPM_API int cpm_prefill_attention_bf16(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                       const int* tile_seq, const int* tile_row, int n_tiles, const int* cu_q,
+                                       const int* kv_len, const int* slots, const int* page_table, int max_pages,
+                                       int n_heads, int n_kv, int d, float scale, cudaStream_t stream) {
+    if (n_tiles <= 0) return CPM_OK;
+    if (n_kv <= 0 || n_heads % n_kv || n_heads > 65535) return CPM_BAD_ARGUMENT;
+    switch (d) {
+        case 32: return launch_prefill<32>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table, max_pages, n_heads, n_kv, scale, stream);
+        case 64: return launch_prefill<64>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table, max_pages, n_heads, n_kv, scale, stream);
+        case 96: return launch_prefill<96>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table, max_pages, n_heads, n_kv, scale, stream);
+        case 128: return launch_prefill<128>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table, max_pages, n_heads, n_kv, scale, stream);
+        default: return CPM_BAD_ARGUMENT;
+    }
+}

@@ -84,11 +84,11 @@ __global__ void attention_generic_kernel(
                 const float pj = __shfl_sync(0xffffffffu, pr, jj);
                 const int key = j0 + jj;
                 const int page = pages[key / kPageTokens];
-                const T* vrow = v_cache + page_row_offset(page, kvh, key % kPageTokens, n_kv, d);
+                const T* vcol = v_cache + value_offset(page, kvh, 0, key % kPageTokens, n_kv, d);
 #pragma unroll
                 for (int i = 0; i < kMaxDimsPerLane; ++i) {
                     const int c = lane + 32 * i;
-                    if (c < d) acc[i] = fmaf(pj, to_f32(vrow[c]), acc[i]);
+                    if (c < d) acc[i] = fmaf(pj, to_f32(vcol[(int64_t)c * kPageTokens]), acc[i]);
                 }
             }
         }

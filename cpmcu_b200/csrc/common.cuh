@@ -12,8 +12,10 @@
 enum : int { CPM_F32 = 0, CPM_BF16 = 1 };
 
 // Tokens per cache page.  A sequence's keys and values live in pages of this many
-// tokens; inside a page the layout is [kv_head][token_in_page][head_dim], so the
-// tile of one head is contiguous.
+// tokens.  A key page is [kv_head][token_in_page][head_dim]; a value page is stored
+// transposed, [kv_head][head_dim][token_in_page].  The tile of one head is contiguous
+// in both, and both can feed tensor-core fragments with 16-byte loads along the
+// contiguous axis (head_dim for the scores, tokens for the weighted sum).
 constexpr int kPageTokens = 64;
 
 // Status codes returned by the launchers (0 = launched; the CUDA error otherwise).
@@ -101,6 +103,11 @@ __device__ __forceinline__ ArgMax block_argmax(ArgMax a, ArgMax* scratch /* 33 *
 // Address of the first element of (page, kv_head, token_in_page) in a cache lane.
 __device__ __forceinline__ int64_t page_row_offset(int page, int kv_head, int in_page, int n_kv, int d) {
     return (((int64_t)page * n_kv + kv_head) * kPageTokens + in_page) * (int64_t)d;
+}
+
+// Address of value element (page, kv_head, dim, token_in_page) in a cache lane.
+__device__ __forceinline__ int64_t value_offset(int page, int kv_head, int dim, int in_page, int n_kv, int d) {
+    return (((int64_t)page * n_kv + kv_head) * d + dim) * (int64_t)kPageTokens + in_page;
 }
 
 static inline int launch_status() {

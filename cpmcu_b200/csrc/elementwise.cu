@@ -153,11 +153,12 @@ __global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
     const int64_t row_stride = (int64_t)(n_heads + 2 * n_kv) * d;
     const T* row = qkv + t * row_stride;
 
-    int64_t k_base = 0;
+    int64_t k_base = 0, v_base = 0;
     if (k_cache) {
         const int slot = slots[token_seq[t]];
         const int page = page_table[(int64_t)slot * max_pages + pos / kPageTokens];
         k_base = page_row_offset(page, 0, pos % kPageTokens, n_kv, d);
+        v_base = value_offset(page, 0, 0, pos % kPageTokens, n_kv, d);
     }
     const int64_t head_stride_in_page = (int64_t)kPageTokens * d;
 
@@ -198,7 +199,7 @@ __global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
         const T* vrow = row + (int64_t)(n_heads + n_kv) * d;
         for (int i = threadIdx.x; i < n_kv * d; i += blockDim.x) {
             const int h = i / d, c = i - h * d;
-            v_cache[k_base + (int64_t)h * head_stride_in_page + c] = vrow[i];
+            v_cache[v_base + ((int64_t)h * d + c) * kPageTokens] = vrow[i];
         }
     }
 }

@@ -148,7 +148,11 @@ class Stepper:
             q_lens.append(count)
             slots.append(s.slot)
         n_tok, n_seq = len(ids), len(slots)
-        packed = torch.tensor(ids + positions + token_seq + cu_q + kv_lens + slots + want_rows, dtype=torch.int32)
+        # 64-token query tiles of the prefill attention kernel: (sequence, first token of the tile)
+        tile_seq = [j for j, n in enumerate(q_lens) for _ in range(0, n, 64)]
+        tile_row = [r for n in q_lens for r in range(0, n, 64)]
+        packed = torch.tensor(ids + positions + token_seq + cu_q + kv_lens + slots + want_rows + tile_seq + tile_row,
+                              dtype=torch.int32)
         dev = packed.to(self.ops.device)
         o = 0
 
@@ -165,4 +169,5 @@ class Stepper:
             kv_len_dev=cut(n_seq), slot_dev=cut(n_seq), cache=self.cache,
         )
         rows = cut(len(want_rows)) if want_rows else None
+        ctx.extras["q_tiles"] = (cut(len(tile_seq)), cut(len(tile_row)), len(tile_seq))
         return self.model.forward(ctx, rows)

@@ -35,6 +35,9 @@ _SIGNATURES = {
     "cpm_select_blocks": [_P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "cpm_advance_decode": [_P, _P, _P, _P, _P, _P, c_int, _P],
+    "cpm_decode_attention_bf16": [_P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, c_float, _P],
+    "cpm_prefill_attention_bf16": [_P, _P, _P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float,
+                                   _P],
     "cpm_sample_rows": [_P, c_int64, c_int, c_int, _P, _P, _P, c_uint64, _P, _P, _P],
 }
 
@@ -63,6 +66,8 @@ def load() -> ctypes.CDLL:
             lib = ctypes.CDLL(path)
         except OSError as e:
             raise KernelLibraryError(f"the CUDA kernel library {path} could not be loaded: {e}") from None
+        lib.cpm_decode_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int, c_int]
+        lib.cpm_decode_attention_scratch_floats.restype = c_int64
         for name, argtypes in _SIGNATURES.items():
             try:
                 fn = getattr(lib, name)

@@ -22,6 +22,8 @@ from .library import check
 
 F32, BF16 = 0, 1
 PAGE_TOKENS = 64
+FAST_HEAD_DIMS = (32, 64, 96, 128)       # head sizes the tensor-core attention kernels are built for
+SM_COUNT_TARGET_WARPS = 148 * 8          # warps the split-key decode attention aims to have in flight
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -200,6 +202,15 @@ class Ops:
     def attention(self, ctx, q: torch.Tensor, lane, n_kv: int, scale: float, window: int = 0,
                   block_list: Optional[torch.Tensor] = None, block_size: int = 0) -> torch.Tensor:
         """Attention of the step's queries over their sequences' cached keys; picks the kernel."""
+        n, n_heads, d = q.shape
+        if self.code == BF16 and block_list is None and not window and d in FAST_HEAD_DIMS:
+            if ctx.is_decode:
+                return self.decode_attention(q, lane.k, lane.v, ctx.kv_len_dev, ctx.slot_dev, lane.page_table,
+                                             n_kv, scale)
+            tiles = ctx.extras.get("q_tiles")
+            if tiles is not None:
+                return self.prefill_attention(q, lane.k, lane.v, tiles, ctx.cu_q, ctx.kv_len_dev, ctx.slot_dev,
+                                              lane.page_table, n_kv, scale)
         return self.attention_generic(q, lane.k, lane.v, ctx.positions, ctx.token_seq, ctx.slot_dev,
                                       lane.page_table, n_kv, scale, window, block_list, block_size)
 
@@ -230,3 +241,47 @@ class Ops:
     def advance_decode(self, ids, positions, kv_len, step_key, sampled, live) -> None:
         check(self.lib.cpm_advance_decode(_ptr(ids), _ptr(positions), _ptr(kv_len), _ptr(step_key), _ptr(sampled),
                                           _ptr(live), ids.numel(), _stream()), "advance_decode")
+
+    # ---- bf16 tensor-core attention ----
+    @staticmethod
+    def decode_splits(n_seqs: int, n_heads: int, n_kv: int) -> int:
+        """How many shares a sequence's pages are cut into: enough warps to fill the GPU."""
+        m_tiles = (n_heads // n_kv + 15) // 16
+        units = max(1, n_seqs * n_kv * m_tiles)
+        return max(1, min(64, -(-SM_COUNT_TARGET_WARPS // units)))
+
+    def decode_attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kv_len: torch.Tensor,
+                         slots: torch.Tensor, page_table: torch.Tensor, n_kv: int, scale: float,
+                         n_splits: Optional[int] = None) -> torch.Tensor:
+        """One query token per sequence: q [seqs, heads, d] -> [seqs, heads*d]."""
+        self._act(q, "q")
+        n, n_heads, d = q.shape
+        if n_splits is None:
+            n_splits = self.decode_splits(n, n_heads, n_kv)
+        floats = self.lib.cpm_decode_attention_scratch_floats(n, n_heads, n_kv, d, n_splits)
+        scratch = self.empty(floats, dtype=torch.float32)
+        out = self.empty(n, n_heads * d)
+        check(self.lib.cpm_decode_attention_bf16(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(kv_len),
+                                                 _ptr(slots), _ptr(page_table), page_table.shape[1], _ptr(scratch),
+                                                 n, n_heads, n_kv, d, n_splits, float(scale), _stream()),
+              f"decode attention (head_dim {d})")
+        LAUNCHES_EXTRA[0] += 1           # the launcher starts two kernels
+        return out
+
+    def prefill_attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tiles,
+                          cu_q: torch.Tensor, kv_len: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
+                          n_kv: int, scale: float) -> torch.Tensor:
+        """q [tokens, heads, d] packed by sequence -> [tokens, heads*d]; tiles = (tile_seq, tile_row, count)
+        lists the 64-token query tiles."""
+        self._act(q, "q")
+        n, n_heads, d = q.shape
+        tile_seq, tile_row, n_tiles = tiles
+        out = self.empty(n, n_heads * d)
+        check(self.lib.cpm_prefill_attention_bf16(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(tile_seq),
+                                                  _ptr(tile_row), n_tiles, _ptr(cu_q), _ptr(kv_len), _ptr(slots),
+                                                  _ptr(page_table), page_table.shape[1], n_heads, n_kv, d,
+                                                  float(scale), _stream()), f"prefill attention (head_dim {d})")
+        return out
+
+
+LAUNCHES_EXTRA = library.LAUNCHES

@@ -38,6 +38,7 @@ def test_groups_have_their_own_storage():
     g0 = c.lane(0).group
     assert c.lane(1).group is g0 and c.lane(2).group is not g0
     assert c.lane(0).k.shape == (10, 2, 64, 16) and c.lane(2).k.shape == (10, 1, 64, 32)
+    assert c.lane(0).v.shape == (10, 2, 16, 64)
     assert c.lane(3).k is None and c.lane(3).state["acc"].shape == (c.n_slots, 8)
     assert c.lane(0).k.data_ptr() != c.lane(1).k.data_ptr()
 

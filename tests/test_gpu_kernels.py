@@ -155,7 +155,7 @@ def test_rope_store_and_attention(dtype, n_heads, n_kv, d, rot):
         for j in (0, n // 2, n - 1):
             page = int(table[s, j // 64])
             got_k = lane.k[page, :, j % 64].float().cpu()
-            got_v = lane.v[page, :, j % 64].float().cpu()
+            got_v = lane.v[page, :, :, j % 64].float().cpu()
             assert _err(got_k, k_ref[o + j]) < KTOL[dtype]
             assert _err(got_v, v_ref[o + j]) < KTOL[dtype]
         o += n
@@ -231,3 +231,48 @@ def test_sampling(vocab):
             slack = 1e-5 * float(c[-1])
             lo = float(c[tok - 1]) if tok > 0 else 0.0
             assert lo - slack <= target <= float(c[tok]) + slack, (r, step, tok, lo, target, float(c[tok]))
+
+
+@pytest.mark.parametrize("n_heads,n_kv,d", [(4, 1, 32), (6, 2, 64), (16, 16, 96), (32, 2, 128), (20, 1, 64), (3, 3, 128)])
+def test_tensor_core_attention_against_generic_and_plain(n_heads, n_kv, d):
+    """The bf16 tensor-core kernels (prefill tiles, split-key decode) on sequences that end inside a
+    page, at a page boundary and just after it; with history (chunked prompt) and without."""
+    ops = _ops("bfloat16")
+    lens = [1, 64, 65, 130, 333]
+    cache, slots = _paged_setup(ops, lens, n_kv, d, 0, "bfloat16")
+    lane = cache.lane(0)
+    g = torch.Generator().manual_seed(9)
+    T = sum(lens)
+    qkv = torch.randn(T, (n_heads + 2 * n_kv) * d, generator=g).bfloat16()
+    positions = torch.cat([torch.arange(n) for n in lens]).int().cuda()
+    token_seq = torch.cat([torch.full((n,), i) for i, n in enumerate(lens)]).int().cuda()
+    sl = torch.tensor(slots, dtype=torch.int32).cuda()
+    q = ops.rope_store(qkv.cuda(), n_heads, n_kv, d, positions, token_seq, sl, lane.page_table, lane.k, lane.v,
+                       None, 1.0, 0)
+    scale = 1 / math.sqrt(d)
+    rows = qkv.float().view(T, n_heads + 2 * n_kv, d)
+    want = torch.cat([plain.dense_attention(rows[o:o + n, :n_heads], rows[o:o + n, n_heads:n_heads + n_kv],
+                                            rows[o:o + n, n_heads + n_kv:], scale).reshape(n, -1)
+                      for o, n in zip([0, 1, 65, 130, 260], lens)])
+    cu = torch.tensor([0, 1, 65, 130, 260, 593], dtype=torch.int32).cuda()
+    kv_len = torch.tensor(lens, dtype=torch.int32).cuda()
+    tile_seq = [j for j, n in enumerate(lens) for _ in range(0, n, 64)]
+    tile_row = [r for n in lens for r in range(0, n, 64)]
+    tiles = (torch.tensor(tile_seq, dtype=torch.int32).cuda(), torch.tensor(tile_row, dtype=torch.int32).cuda(), len(tile_seq))
+    got = ops.prefill_attention(q, lane.k, lane.v, tiles, cu, kv_len, sl, lane.page_table, n_kv, scale)
+    assert _err(got, want) < KTOL["bfloat16"]
+    generic = ops.attention_generic(q, lane.k, lane.v, positions, token_seq, sl, lane.page_table, n_kv, scale)
+    assert _err(got, generic) < KTOL["bfloat16"]
+    # the last 40 tokens of the longest sequence as a step of their own: the earlier ones are history
+    o, n = 260, 333
+    cu2 = torch.tensor([0, 40], dtype=torch.int32).cuda()
+    tiles2 = (torch.zeros(1, dtype=torch.int32).cuda(), torch.zeros(1, dtype=torch.int32).cuda(), 1)
+    got2 = ops.prefill_attention(q[o + n - 40:o + n].contiguous(), lane.k, lane.v, tiles2, cu2, kv_len[4:5].contiguous(),
+                                 sl[4:5].contiguous(), lane.page_table, n_kv, scale)
+    assert _err(got2, want[o + n - 40:o + n]) < KTOL["bfloat16"]
+    # decode: the last token of every sequence, with few and with many shares
+    last = torch.tensor([0, 64, 129, 259, 592])
+    ql = q[last.cuda()].contiguous()
+    for splits in (1, 3, 64, None):
+        dec = ops.decode_attention(ql, lane.k, lane.v, kv_len, sl, lane.page_table, n_kv, scale, n_splits=splits)
+        assert _err(dec, want[last]) < KTOL["bfloat16"], splits
