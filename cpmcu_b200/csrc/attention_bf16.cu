@@ -348,3 +348,72 @@ CPM_API int cpm_prefill_attention_bf16(const void* q, const void* k_cache, const
         default: return CPM_BAD_ARGUMENT;
     }
 }
+
+// ---------------------------------------------------------------------------
+// The decode attention with scratch memory of its own (see cpm_no_alloc.h).
+// ---------------------------------------------------------------------------
+#include "cpm_no_alloc.h"
+#include <mutex>
+#include <stdio.h>
+
+// Partial results of the split-key decode kernel.  In host code this name is only a
+// stand-in for the symbol, never a device address: the address each device gives it is
+// looked up below and that pointer is what the kernels get.
+static __device__ __align__(256) float g_static_scratch[CPM_STATIC_SCRATCH_FLOATS];
+
+static constexpr int kMaxDevices = 64;
+static float* g_static_scratch_ptr[kMaxDevices] = {nullptr};
+static std::mutex g_static_scratch_mutex;
+
+// Device address of g_static_scratch on the current device, looked up once per device.
+static int static_scratch_for_current_device(float** out, char* error_text, int error_text_len) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        if (error_text && error_text_len > 0)
+            snprintf(error_text, error_text_len, "cannot tell the current device (cudaGetDevice: %s, device %d)",
+                     cudaGetErrorString(e), dev);
+        return CPM_STATIC_SETUP_FAILED;
+    }
+    std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+    if (g_static_scratch_ptr[dev] == nullptr) {
+        float* p = nullptr;
+        e = cudaGetSymbolAddress((void**)&p, g_static_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            if (error_text && error_text_len > 0)
+                snprintf(error_text, error_text_len, "cudaGetSymbolAddress of the static scratch failed on device %d: %s",
+                         dev, cudaGetErrorString(e));
+            return CPM_STATIC_SETUP_FAILED;
+        }
+        g_static_scratch_ptr[dev] = p;
+    }
+    *out = g_static_scratch_ptr[dev];
+    return CPM_OK;
+}
+
+int cpm_decode_attention_bf16_static(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                     const int* kv_len, const int* slots, const int* page_table, int max_pages,
+                                     int n_seqs, int n_heads, int n_kv, int d, int n_splits, float scale,
+                                     cudaStream_t stream, char* error_text, int error_text_len) {
+    if (error_text && error_text_len > 0) error_text[0] = 0;
+    if (n_seqs <= 0) return CPM_OK;
+    if (n_kv <= 0 || n_heads <= 0 || n_heads % n_kv || n_splits < 1 || (d != 32 && d != 64 && d != 96 && d != 128)) {
+        if (error_text && error_text_len > 0)
+            snprintf(error_text, error_text_len, "sizes not taken: heads %d, kv heads %d, head_dim %d (32/64/96/128), "
+                     "splits %d", n_heads, n_kv, d, n_splits);
+        return CPM_BAD_ARGUMENT;
+    }
+    const int64_t need = cpm_decode_attention_scratch_floats(n_seqs, n_heads, n_kv, d, n_splits);
+    if (need > (int64_t)CPM_STATIC_SCRATCH_FLOATS) {
+        if (error_text && error_text_len > 0)
+            snprintf(error_text, error_text_len, "these sizes need %lld floats of scratch, the static scratch holds %d: "
+                     "use fewer splits or sequences, or cpm_decode_attention_bf16 with scratch of your own",
+                     (long long)need, (int)CPM_STATIC_SCRATCH_FLOATS);
+        return CPM_STATIC_TOO_LARGE;
+    }
+    float* scratch = nullptr;
+    const int status = static_scratch_for_current_device(&scratch, error_text, error_text_len);
+    if (status != CPM_OK) return status;
+    return cpm_decode_attention_bf16(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs,
+                                     n_heads, n_kv, d, n_splits, scale, stream);
+}
