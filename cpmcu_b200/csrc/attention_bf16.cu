@@ -20,7 +20,7 @@
 
 __device__ __forceinline__ void mma_16816(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                           uint32_t b0, uint32_t b1) {
-    asm volatile(
+    asm(
         "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
         : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -148,9 +148,12 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
                         const int* __restrict__ page_table, int max_pages, float* __restrict__ part_o,
                         float* __restrict__ part_ml, int n_heads, int n_kv, int m_tiles, int n_splits,
                         float scale_log2) {
+    // A block takes one share of a sequence's pages; its 4 warps take every fourth page of
+    // the share and merge their results in shared memory before anything is written.
+    __shared__ float sm_o[4][16][D + 4];
+    __shared__ float sm_m[4][16], sm_l[4][16];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int split = blockIdx.x * 4 + warp;
-    if (split >= n_splits) return;
+    const int split = blockIdx.x;
     const int kvh = blockIdx.y / m_tiles, mt = blockIdx.y % m_tiles, b = blockIdx.z;
     const int group = n_heads / n_kv;
     const int j = lane & 3, g = lane >> 2;
@@ -161,7 +164,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
 
     TileState<D> st;
     st.init();
-    if (p0 < p1) {
+    if (p0 + warp < p1) {
         uint4 qf[2][D / 32];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
@@ -172,7 +175,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
             for (int w = 0; w < D / 32; ++w) qf[r][w] = valid ? ldg16(qrow + 32 * w) : make_uint4(0, 0, 0, 0);
         }
         const int* pages = page_table + (int64_t)slots[b] * max_pages;
-        for (int p = p0; p < p1; ++p) {
+        for (int p = p0 + warp; p < p1; p += 4) {
             const int page = pages[p];
             const bf16* kpage = k_cache + ((int64_t)page * n_kv + kvh) * kPageTokens * D;
             const bf16* vpage = v_cache + ((int64_t)page * n_kv + kvh) * D * kPageTokens;
@@ -185,19 +188,34 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
         st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
         st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
     }
-    const int64_t unit = (((int64_t)b * n_kv + kvh) * m_tiles + mt) * n_splits + split;
-    float* po = part_o + unit * 16 * D;
 #pragma unroll
     for (int nt = 0; nt < D / 8; ++nt) {
-        *reinterpret_cast<float2*>(po + g * D + 8 * nt + 2 * j) = make_float2(st.o[nt][0], st.o[nt][1]);
-        *reinterpret_cast<float2*>(po + (g + 8) * D + 8 * nt + 2 * j) = make_float2(st.o[nt][2], st.o[nt][3]);
+        *reinterpret_cast<float2*>(&sm_o[warp][g][8 * nt + 2 * j]) = make_float2(st.o[nt][0], st.o[nt][1]);
+        *reinterpret_cast<float2*>(&sm_o[warp][g + 8][8 * nt + 2 * j]) = make_float2(st.o[nt][2], st.o[nt][3]);
     }
     if (j == 0) {
-        float* pm = part_ml + unit * 32;
-        pm[2 * g] = st.m[0];
-        pm[2 * g + 1] = st.l[0];
-        pm[2 * (g + 8)] = st.m[1];
-        pm[2 * (g + 8) + 1] = st.l[1];
+        sm_m[warp][g] = st.m[0];
+        sm_l[warp][g] = st.l[0];
+        sm_m[warp][g + 8] = st.m[1];
+        sm_l[warp][g + 8] = st.l[1];
+    }
+    __syncthreads();
+    const int64_t unit = (((int64_t)b * n_kv + kvh) * m_tiles + mt) * n_splits + split;
+    float* po = part_o + unit * 16 * D;
+    for (int i = threadIdx.x; i < 16 * D; i += 128) {
+        const int row = i / D, c = i - row * D;
+        const float m0 = sm_m[0][row], m1 = sm_m[1][row], m2 = sm_m[2][row], m3 = sm_m[3][row];
+        const float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+        const float use = mx == -INFINITY ? 0.f : mx;
+        const float o = sm_o[0][row][c] * exp2f(m0 - use) + sm_o[1][row][c] * exp2f(m1 - use)
+                      + sm_o[2][row][c] * exp2f(m2 - use) + sm_o[3][row][c] * exp2f(m3 - use);
+        po[i] = o;
+        if (c == 0) {
+            const float l = sm_l[0][row] * exp2f(m0 - use) + sm_l[1][row] * exp2f(m1 - use)
+                          + sm_l[2][row] * exp2f(m2 - use) + sm_l[3][row] * exp2f(m3 - use);
+            part_ml[unit * 32 + 2 * row] = mx;
+            part_ml[unit * 32 + 2 * row + 1] = l;
+        }
     }
 }
 
@@ -241,7 +259,7 @@ static int launch_decode(const void* q, const void* k_cache, const void* v_cache
     const int m_tiles = (n_heads / n_kv + 15) / 16;
     float* part_o = scratch;
     float* part_ml = scratch + (int64_t)n_seqs * n_kv * m_tiles * n_splits * 16 * D;
-    dim3 grid((n_splits + 3) / 4, n_kv * m_tiles, n_seqs);
+    dim3 grid(n_splits, n_kv * m_tiles, n_seqs);
     decode_attention_kernel<D><<<grid, 128, 0, stream>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
         kv_len, slots, page_table, max_pages, part_o, part_ml, n_heads, n_kv, m_tiles, n_splits,
         scale * 1.4426950408889634f);

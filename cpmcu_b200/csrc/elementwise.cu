@@ -48,20 +48,46 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
     float* xr = x + src_row * hidden;
     const T* dr = delta ? delta + src_row * hidden : nullptr;
     float ss = 0.f;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
-        float v = xr[c];
-        if (dr) {
-            v = fmaf(alpha, to_f32(dr[c]), v);
-            if (write_back) xr[c] = v;
+    if ((hidden & 3) == 0) {
+        // four elements per thread and step: 16-byte loads of the fp32 stream
+        for (int c = 4 * threadIdx.x; c < hidden; c += 4 * blockDim.x) {
+            float4 v = *reinterpret_cast<const float4*>(xr + c);
+            if (dr) {
+                v.x = fmaf(alpha, to_f32(dr[c]), v.x);
+                v.y = fmaf(alpha, to_f32(dr[c + 1]), v.y);
+                v.z = fmaf(alpha, to_f32(dr[c + 2]), v.z);
+                v.w = fmaf(alpha, to_f32(dr[c + 3]), v.w);
+                if (write_back) *reinterpret_cast<float4*>(xr + c) = v;
+            }
+            *reinterpret_cast<float4*>(row_cache + c) = v;
+            ss = fmaf(v.x, v.x, fmaf(v.y, v.y, fmaf(v.z, v.z, fmaf(v.w, v.w, ss))));
         }
-        row_cache[c] = v;
-        ss = fmaf(v, v, ss);
+    } else {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+            float v = xr[c];
+            if (dr) {
+                v = fmaf(alpha, to_f32(dr[c]), v);
+                if (write_back) xr[c] = v;
+            }
+            row_cache[c] = v;
+            ss = fmaf(v, v, ss);
+        }
     }
     const float total = block_sum(ss, scratch);
     const float r = rsqrtf(total / (float)hidden + eps);
     T* yr = y + (int64_t)blockIdx.x * hidden;
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x)
-        yr[c] = from_f32<T>(row_cache[c] * r * to_f32(w[c]));
+    if ((hidden & 3) == 0) {
+        for (int c = 4 * threadIdx.x; c < hidden; c += 4 * blockDim.x) {
+            const float4 v = *reinterpret_cast<const float4*>(row_cache + c);
+            yr[c] = from_f32<T>(v.x * r * to_f32(w[c]));
+            yr[c + 1] = from_f32<T>(v.y * r * to_f32(w[c + 1]));
+            yr[c + 2] = from_f32<T>(v.z * r * to_f32(w[c + 2]));
+            yr[c + 3] = from_f32<T>(v.w * r * to_f32(w[c + 3]));
+        }
+    } else {
+        for (int c = threadIdx.x; c < hidden; c += blockDim.x)
+            yr[c] = from_f32<T>(row_cache[c] * r * to_f32(w[c]));
+    }
 }
 
 template <typename T, typename W>
@@ -74,7 +100,7 @@ static int launch_add_rmsnorm(float* x, const void* delta, float alpha, const vo
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    const int threads = hidden >= 2048 ? 512 : (hidden >= 512 ? 256 : 128);
+    const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
     kern<<<n_rows, threads, smem, stream>>>(x, (const T*)delta, alpha, (const W*)w, (T*)y, rows, hidden, eps, write_back);
     return launch_status();
 }
@@ -111,23 +137,36 @@ CPM_API int cpm_residual_add(float* x, const void* delta, float alpha, int64_t n
 // h[t, c] = silu(gu[t, c]) * gu[t, inter + c]; a row of gu is [gate | up]
 // (src/model/activation.cuh:6-18, src/model/ffn.cuh:38-50).
 // ---------------------------------------------------------------------------
+// interleave == 0: a row is [gate(inter) | up(inter)].  interleave == 8: a row is made of blocks of
+// 16, the 8 gate values of 8 features followed by their 8 up values (the layout the fused
+// decode product wants).  Two features per thread.
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ h, int inter) {
-    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+__global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ h, int inter, int interleave) {
+    const int c = 2 * (blockIdx.y * blockDim.x + threadIdx.x);
     if (c >= inter) return;
     const T* row = gu + (int64_t)blockIdx.x * 2 * inter;
-    const float g = to_f32(row[c]);
-    const float u = to_f32(row[inter + c]);
-    const float s = 1.0f / (1.0f + expf(-g));
-    h[(int64_t)blockIdx.x * inter + c] = from_f32<T>(g * s * u);
+    T* out = h + (int64_t)blockIdx.x * inter;
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+        const int f = c + e;
+        if (f >= inter) break;
+        const int gi = interleave ? (f / interleave) * 2 * interleave + f % interleave : f;
+        const int ui = interleave ? gi + interleave : inter + f;
+        const float g = to_f32(row[gi]);
+        const float u = to_f32(row[ui]);
+        const float s = 1.0f / (1.0f + expf(-g));
+        out[f] = from_f32<T>(g * s * u);
+    }
 }
 
-CPM_API int cpm_silu_mul(const void* gu, void* h, int n_tokens, int inter, int dtype, cudaStream_t stream) {
+CPM_API int cpm_silu_mul(const void* gu, void* h, int n_tokens, int inter, int interleave, int dtype,
+                         cudaStream_t stream) {
     if (n_tokens <= 0) return CPM_OK;
-    dim3 grid(n_tokens, (inter + 255) / 256);
+    if (interleave != 0 && (interleave != 8 || inter % 8 != 0)) return CPM_BAD_ARGUMENT;
+    dim3 grid(n_tokens, (inter + 511) / 512);
     if (grid.y > 65535) return CPM_BAD_ARGUMENT;
-    if (dtype == CPM_BF16) silu_mul_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)gu, (bf16*)h, inter);
-    else silu_mul_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)h, inter);
+    if (dtype == CPM_BF16) silu_mul_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)gu, (bf16*)h, inter, interleave);
+    else silu_mul_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)h, inter, interleave);
     return launch_status();
 }
 
@@ -140,6 +179,8 @@ CPM_API int cpm_silu_mul(const void* gu, void* h, int n_tokens, int inter, int d
 // LongRoPE attention factor).  inv_freq == nullptr: no rotation.
 // qkv row: [heads*d | kv_heads*d | kv_heads*d].
 // ---------------------------------------------------------------------------
+constexpr int kRopeHeadsPerBlock = 4;
+
 template <typename T>
 __global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_out,
                                   T* __restrict__ k_cache, T* __restrict__ v_cache,
@@ -147,11 +188,29 @@ __global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
                                   const int* __restrict__ slots, const int* __restrict__ page_table,
                                   int max_pages, const float* __restrict__ inv_freq, float magnitude,
                                   int n_heads, int n_kv, int d, int rot_dim) {
+    extern __shared__ float cs_table[];       // cos[half], sin[half] of this token
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int half = rot_dim >> 1;
     const int64_t row_stride = (int64_t)(n_heads + 2 * n_kv) * d;
     const T* row = qkv + t * row_stride;
+    const int n_all = n_heads + (k_cache ? 2 * n_kv : 0);       // q heads, then k heads, then v heads
+    const int h_begin = blockIdx.y * kRopeHeadsPerBlock;
+    const int h_end = min(n_all, h_begin + kRopeHeadsPerBlock);
+    if (h_begin >= h_end) return;
+
+    for (int c = threadIdx.x; c < half; c += blockDim.x) {
+        float cs = 1.f, sn = 0.f;
+        if (inv_freq) {
+            const float angle = (float)pos * inv_freq[c];
+            sincosf(angle, &sn, &cs);
+            cs *= magnitude;
+            sn *= magnitude;
+        }
+        cs_table[c] = cs;
+        cs_table[half + c] = sn;
+    }
+    __syncthreads();
 
     int64_t k_base = 0, v_base = 0;
     if (k_cache) {
@@ -161,46 +220,24 @@ __global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
         v_base = value_offset(page, 0, 0, pos % kPageTokens, n_kv, d);
     }
     const int64_t head_stride_in_page = (int64_t)kPageTokens * d;
-
-    // rotated pairs of q heads and k heads
-    const int n_rot_heads = n_heads + (k_cache ? n_kv : 0);
-    for (int i = threadIdx.x; i < n_rot_heads * half; i += blockDim.x) {
-        const int h = i / half, c = i - h * half;
-        float cs = 1.f, sn = 0.f;
-        if (inv_freq) {
-            const float angle = (float)pos * inv_freq[c];
-            sincosf(angle, &sn, &cs);
-            cs *= magnitude;
-            sn *= magnitude;
-        }
+    for (int h = h_begin; h < h_end; ++h) {
         const T* src = row + (int64_t)h * d;
-        const float a = to_f32(src[c]);
-        const float b = to_f32(src[c + half]);
-        const float ra = a * cs - b * sn;
-        const float rb = a * sn + b * cs;
-        T* dst;
-        if (h < n_heads) dst = q_out + ((int64_t)t * n_heads + h) * d;
-        else dst = k_cache + k_base + (int64_t)(h - n_heads) * head_stride_in_page;
-        dst[c] = from_f32<T>(ra);
-        dst[c + half] = from_f32<T>(rb);
-    }
-    // dimensions beyond rot_dim pass through
-    const int rest = d - rot_dim;
-    if (rest > 0) {
-        for (int i = threadIdx.x; i < n_rot_heads * rest; i += blockDim.x) {
-            const int h = i / rest, c = rot_dim + (i - h * rest);
-            const T v = row[(int64_t)h * d + c];
-            if (h < n_heads) q_out[((int64_t)t * n_heads + h) * d + c] = v;
-            else k_cache[k_base + (int64_t)(h - n_heads) * head_stride_in_page + c] = v;
+        if (h >= n_heads + n_kv) {                               // a value head: transposed store
+            const int kvh = h - n_heads - n_kv;
+            for (int c = threadIdx.x; c < d; c += blockDim.x)
+                v_cache[v_base + ((int64_t)kvh * d + c) * kPageTokens] = src[c];
+            continue;
         }
-    }
-    // values
-    if (v_cache) {
-        const T* vrow = row + (int64_t)(n_heads + n_kv) * d;
-        for (int i = threadIdx.x; i < n_kv * d; i += blockDim.x) {
-            const int h = i / d, c = i - h * d;
-            v_cache[v_base + ((int64_t)h * d + c) * kPageTokens] = vrow[i];
+        T* dst = h < n_heads ? q_out + ((int64_t)t * n_heads + h) * d
+                             : k_cache + k_base + (int64_t)(h - n_heads) * head_stride_in_page;
+        for (int c = threadIdx.x; c < half; c += blockDim.x) {
+            const float cs = cs_table[c], sn = cs_table[half + c];
+            const float a = to_f32(src[c]);
+            const float b = to_f32(src[c + half]);
+            dst[c] = from_f32<T>(a * cs - b * sn);
+            dst[c + half] = from_f32<T>(a * sn + b * cs);
         }
+        for (int c = rot_dim + threadIdx.x; c < d; c += blockDim.x) dst[c] = src[c];
     }
 }
 
@@ -211,12 +248,16 @@ CPM_API int cpm_rope_store(const void* qkv, void* q_out, void* k_cache, void* v_
     if (n_tokens <= 0) return CPM_OK;
     if (rot_dim < 0 || rot_dim > d || (rot_dim & 1)) return CPM_BAD_ARGUMENT;
     if ((k_cache == nullptr) != (v_cache == nullptr)) return CPM_BAD_ARGUMENT;
-    const int threads = 128;
+    const int n_all = n_heads + (k_cache ? 2 * n_kv : 0);
+    dim3 grid(n_tokens, (n_all + kRopeHeadsPerBlock - 1) / kRopeHeadsPerBlock);
+    if (grid.y > 65535) return CPM_BAD_ARGUMENT;
+    const int threads = d >= 128 ? 64 : 32;
+    const size_t smem = (size_t)(rot_dim > 0 ? rot_dim : 2) * sizeof(float);
     if (dtype == CPM_BF16)
-        rope_store_kernel<bf16><<<n_tokens, threads, 0, stream>>>((const bf16*)qkv, (bf16*)q_out, (bf16*)k_cache,
+        rope_store_kernel<bf16><<<grid, threads, smem, stream>>>((const bf16*)qkv, (bf16*)q_out, (bf16*)k_cache,
             (bf16*)v_cache, positions, token_seq, slots, page_table, max_pages, inv_freq, magnitude, n_heads, n_kv, d, rot_dim);
     else
-        rope_store_kernel<float><<<n_tokens, threads, 0, stream>>>((const float*)qkv, (float*)q_out, (float*)k_cache,
+        rope_store_kernel<float><<<grid, threads, smem, stream>>>((const float*)qkv, (float*)q_out, (float*)k_cache,
             (float*)v_cache, positions, token_seq, slots, page_table, max_pages, inv_freq, magnitude, n_heads, n_kv, d, rot_dim);
     return launch_status();
 }

@@ -25,7 +25,8 @@ _SIGNATURES = {
     "cpm_embed_rows": [_P, _P, _P, c_int, c_int, c_float, c_int, _P],
     "cpm_add_rmsnorm": [_P, _P, c_float, _P, c_int, _P, _P, c_int, c_int, c_float, c_int, c_int, _P],
     "cpm_residual_add": [_P, _P, c_float, c_int64, c_int, _P],
-    "cpm_silu_mul": [_P, _P, c_int, c_int, c_int, _P],
+    "cpm_silu_mul": [_P, _P, c_int, c_int, c_int, c_int, _P],
+    "cpm_gemm_skinny_bf16": [_P, _P, _P, c_int, c_int, c_int, c_float, c_int, _P],
     "cpm_rope_store": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_float, c_int, c_int, c_int, c_int, c_int,
                        c_int, _P],
     "cpm_attention_generic": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int,

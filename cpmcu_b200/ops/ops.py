@@ -23,7 +23,7 @@ from .library import check
 F32, BF16 = 0, 1
 PAGE_TOKENS = 64
 FAST_HEAD_DIMS = (32, 64, 96, 128)       # head sizes the tensor-core attention kernels are built for
-SM_COUNT_TARGET_WARPS = 148 * 8          # warps the split-key decode attention aims to have in flight
+DECODE_TARGET_BLOCKS = 148 * 3           # blocks (of 4 warps) the split-key decode attention aims for
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -110,15 +110,21 @@ class Ops:
         check(self.lib.cpm_residual_add(_ptr(x), _ptr(delta), float(alpha), x.numel(), self.code, _stream()),
               "residual add")
 
-    def silu_mul(self, gu: torch.Tensor) -> torch.Tensor:
-        """gu [tokens, 2*inter] with rows [gate | up] -> silu(gate) * up, [tokens, inter]."""
+    def silu_mul(self, gu: torch.Tensor, interleave: int = 0) -> torch.Tensor:
+        """gu [tokens, 2*inter] -> silu(gate) * up, [tokens, inter].  interleave 0: rows are
+        [gate | up]; 8: blocks of 8 gate values followed by the 8 up values of the same features."""
         self._act(gu, "gate_up")
         n, two_i = gu.shape
         h = self.empty(n, two_i // 2)
-        check(self.lib.cpm_silu_mul(_ptr(gu), _ptr(h), n, two_i // 2, self.code, _stream()), "silu_mul")
+        check(self.lib.cpm_silu_mul(_ptr(gu), _ptr(h), n, two_i // 2, interleave, self.code, _stream()), "silu_mul")
         return h
 
     # ---- matrix products ----
+    SKINNY_MAX_ROWS = 16
+
+    def _skinny_ok(self, M: int, K: int) -> bool:
+        return self.code == BF16 and M <= self.SKINNY_MAX_ROWS and K % 32 == 0
+
     def linear(self, a: torch.Tensor, w: torch.Tensor, alpha: float = 1.0,
                out_f32: bool = False) -> torch.Tensor:
         """alpha * a[M,K] @ w[N,K]^T -> [M,N] in the compute dtype, or fp32 when out_f32."""
@@ -133,6 +139,11 @@ class Ops:
             check(self.lib.cpm_gemm_f32(_ptr(a), _ptr(w), _ptr(c), M, N, K, K, K, N, float(alpha), _stream()),
                   "fp32 matrix product")
             return c
+        if self._skinny_ok(M, K):
+            c = self.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype)
+            check(self.lib.cpm_gemm_skinny_bf16(_ptr(w), _ptr(a), _ptr(c), M, N, K, float(alpha), 1 if out_f32 else 0,
+                                                _stream()), "skinny matrix product")
+            return c
         if out_f32:
             c = torch.mm(a, w.t(), out_dtype=torch.float32)
         else:
@@ -140,6 +151,18 @@ class Ops:
         if alpha != 1.0:
             c.mul_(alpha)
         return c
+
+    def gated_linear(self, a: torch.Tensor, w_gate_up: torch.Tensor, interleave: int) -> torch.Tensor:
+        """silu(a @ gate^T) * (a @ up^T) for a gate_up matrix [2*inter, K] laid out as ``interleave`` says."""
+        M, K = a.shape
+        if interleave == 8 and self._skinny_ok(M, K) and w_gate_up.shape[0] % 16 == 0:
+            self._act(a, "linear input")
+            self._act(w_gate_up, "gate_up weight")
+            h = self.empty(M, w_gate_up.shape[0] // 2)
+            check(self.lib.cpm_gemm_skinny_bf16(_ptr(w_gate_up), _ptr(a), _ptr(h), M, w_gate_up.shape[0], K, 1.0, 2,
+                                                _stream()), "gated skinny matrix product")
+            return h
+        return self.silu_mul(self.linear(a, w_gate_up), interleave)
 
     # ---- attention ----
     def rope_store(self, qkv: torch.Tensor, n_heads: int, n_kv: int, d: int, positions: torch.Tensor,
@@ -248,7 +271,7 @@ class Ops:
         """How many shares a sequence's pages are cut into: enough warps to fill the GPU."""
         m_tiles = (n_heads // n_kv + 15) // 16
         units = max(1, n_seqs * n_kv * m_tiles)
-        return max(1, min(64, -(-SM_COUNT_TARGET_WARPS // units)))
+        return max(1, min(16, -(-DECODE_TARGET_BLOCKS // units)))
 
     def decode_attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kv_len: torch.Tensor,
                          slots: torch.Tensor, page_table: torch.Tensor, n_kv: int, scale: float,

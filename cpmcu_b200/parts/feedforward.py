@@ -1,7 +1,8 @@
 """Gated feed-forward: down( act(gate(y)) * up(y) ) (src/model/ffn.cuh:18-89).
 
-gate and up are kept as one [2*inter, hidden] matrix so that one product gives a row
-[gate | up] (src/model/ffn.cuh:47-48); the activation is SiLU in fp32
+gate and up are kept as one [2*inter, hidden] matrix so that one product gives both
+(src/model/ffn.cuh:47-48 keeps them as [gate | up]; here their rows are interleaved in
+blocks of 8 when the size allows); the activation is SiLU in fp32
 (src/model/activation.cuh:6-18)."""
 from __future__ import annotations
 
@@ -20,6 +21,7 @@ class GatedFeedForward(FeedForward):
             raise ValueError(f"gated_ffn: activation '{activation}' is not built; known: ['silu']")
         self.hidden_size = int(hidden_size)
         self.intermediate_size = int(intermediate_size)
+        self.interleave = 0
         self.w_gate_up: Optional[torch.Tensor] = None
         self.w_down: Optional[torch.Tensor] = None
 
@@ -32,13 +34,21 @@ class GatedFeedForward(FeedForward):
         }
 
     def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.w_gate_up = torch.cat([tensors["gate_proj.weight"], tensors["up_proj.weight"]], dim=0).contiguous()
+        gate, up = tensors["gate_proj.weight"], tensors["up_proj.weight"]
+        i, h = self.intermediate_size, self.hidden_size
+        if i % 8 == 0:
+            # blocks of 8 gate rows followed by the 8 up rows of the same features: gate and up of a
+            # feature then fall into one tile of the product, which can apply the activation itself
+            self.interleave = 8
+            self.w_gate_up = torch.stack([gate.view(i // 8, 8, h), up.view(i // 8, 8, h)], dim=1).reshape(2 * i, h).contiguous()
+        else:
+            self.interleave = 0
+            self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.w_down = tensors["down_proj.weight"].contiguous()
 
     def weight_bytes(self) -> int:
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_gate_up.element_size()
 
     def forward(self, ctx, y: torch.Tensor) -> torch.Tensor:
-        gu = self.ops.linear(y, self.w_gate_up)
-        h = self.ops.silu_mul(gu)
+        h = self.ops.gated_linear(y, self.w_gate_up, self.interleave)
         return self.ops.linear(h, self.w_down)

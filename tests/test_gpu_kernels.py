@@ -276,3 +276,40 @@ def test_tensor_core_attention_against_generic_and_plain(n_heads, n_kv, d):
     for splits in (1, 3, 64, None):
         dec = ops.decode_attention(ql, lane.k, lane.v, kv_len, sl, lane.page_table, n_kv, scale, n_splits=splits)
         assert _err(dec, want[last]) < KTOL["bfloat16"], splits
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_silu_mul_interleaved(dtype):
+    ops = _ops(dtype)
+    g = torch.Generator().manual_seed(10)
+    inter = 88
+    gate, up = torch.randn(5, inter, generator=g) * 2, torch.randn(5, inter, generator=g)
+    gu = torch.stack([gate.view(5, inter // 8, 8), up.view(5, inter // 8, 8)], dim=2).reshape(5, 2 * inter).to(DT[dtype])
+    got = ops.silu_mul(gu.cuda(), interleave=8)
+    gf, uf = gate.to(DT[dtype]).float(), up.to(DT[dtype]).float()
+    assert _err(got, gf * (1 / (1 + torch.exp(-gf))) * uf) < KTOL[dtype]
+
+
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(16, 32), (48, 64), (1000, 128), (777, 96), (4608, 4096), (73448, 256)])
+def test_skinny_gemm(M, N, K):
+    """The weight-streaming product of the decode path against fp32 torch, all epilogues."""
+    ops = _ops("bfloat16")
+    g = torch.Generator().manual_seed(11)
+    a = torch.randn(M, K, generator=g).bfloat16()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16()
+    want = a.float() @ w.float().T
+    got = ops.linear(a.cuda(), w.cuda())
+    assert got.dtype == torch.bfloat16 and _err(got, want) < KTOL["bfloat16"]
+    got32 = ops.linear(a.cuda(), w.cuda(), alpha=0.125, out_f32=True)
+    assert got32.dtype == torch.float32 and _err(got32, want * 0.125) < 2e-5
+    if N % 16 == 0:
+        inter = N // 2
+        gate, up = w[:inter].float(), w[inter:].float()
+        wi = torch.stack([w[:inter].view(inter // 8, 8, K), w[inter:].view(inter // 8, 8, K)], dim=1).reshape(N, K)
+        gg, uu = a.float() @ gate.T, a.float() @ up.T
+        h = ops.gated_linear(a.cuda(), wi.contiguous().cuda(), 8)
+        assert _err(h, gg * (1 / (1 + torch.exp(-gg))) * uu) < KTOL["bfloat16"]
+    # a row's result does not depend on the other rows
+    one = ops.linear(a[:1].contiguous().cuda(), w.cuda(), out_f32=True, alpha=0.125)
+    assert torch.equal(one[0], got32[0])
