@@ -31,7 +31,13 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__device__ __forceinline__ uint4 ldg16(const void* p) { return __ldg(reinterpret_cast<const uint4*>(p)); }
+// Keys and values are read once by one warp: keep them out of L1.
+__device__ __forceinline__ uint4 ldg16(const void* p) {
+    uint4 v;
+    asm("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+        : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
 
 // State of a 16-row tile in one warp: thread (g = lane / 4, j = lane % 4) holds rows g and
 // g + 8; o[nt] are output dims 8*nt + 2j, 2j+1 of both rows.
@@ -141,17 +147,151 @@ __device__ __forceinline__ void attend_page(TileState<D>& st, const uint4 (&q)[2
 // ---------------------------------------------------------------------------
 // decode
 // ---------------------------------------------------------------------------
+// Asynchronous copies (cp.async, 16 bytes per thread) bring a warp's next pages into its own
+// shared-memory buffers while it works on the current one, so the bytes in flight do not
+// depend on how the compiler orders loads.  The 16-byte chunks of odd rows are stored
+// shifted by four chunks where rows are a multiple of 128 bytes apart, which keeps the
+// fragment reads free of bank conflicts.
+__device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void* gmem) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" :: "r"(smem_addr), "l"(gmem) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" :: "n"(N) : "memory"); }
+__device__ __forceinline__ uint4 lds16(uint32_t smem_addr) {
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(smem_addr));
+    return v;
+}
+
+constexpr int kDecodeWarps = 3;
+constexpr int kDecodeStages = 2;
+
 template <int D>
-__global__ void __launch_bounds__(128)
+struct DecodeSmem {
+    static constexpr int kChunksPerKeyRow = D / 8;                         // 16-byte chunks in a key row
+    static constexpr bool kSwizzleKeys = (kChunksPerKeyRow % 8) == 0;
+    static constexpr int kKeyBytes = kPageTokens * D * 2;
+    static constexpr int kStageBytes = 2 * kKeyBytes;                      // a key page and a value page
+    static constexpr int kTotal = kDecodeWarps * kDecodeStages * kStageBytes;
+};
+
+// Copies one key page and one value page (both contiguous in global memory) into a stage.
+template <int D>
+__device__ __forceinline__ void copy_page_async(uint32_t stage, const bf16* __restrict__ kpage,
+                                                const bf16* __restrict__ vpage, int lane) {
+    using S = DecodeSmem<D>;
+    constexpr int kChunks = S::kKeyBytes / 16;
+#pragma unroll 8
+    for (int c = lane; c < kChunks; c += 32) {
+        const int row = c / S::kChunksPerKeyRow, col = c % S::kChunksPerKeyRow;
+        const int pcol = S::kSwizzleKeys ? (col ^ ((row & 1) << 2)) : col;
+        cp_async16(stage + (row * S::kChunksPerKeyRow + pcol) * 16, kpage + c * 8);
+    }
+#pragma unroll 8
+    for (int c = lane; c < kChunks; c += 32) {
+        const int row = c >> 3, col = c & 7;                               // value rows hold 64 tokens = 8 chunks
+        cp_async16(stage + S::kKeyBytes + (row * 8 + (col ^ ((row & 1) << 2))) * 16, vpage + c * 8);
+    }
+}
+
+// attend_page with both pages in shared memory (same fragment assignment).
+template <int D>
+__device__ __forceinline__ void attend_page_smem(TileState<D>& st, const uint4 (&q)[2][D / 32], uint32_t stage, int key0,
+                                                 int limit, float scale_log2, int lane) {
+    using S = DecodeSmem<D>;
+    const int j = lane & 3, n = lane >> 2;
+    float s[2][4][4];
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            s[u][t][0] = s[u][t][1] = s[u][t][2] = s[u][t][3] = 0.f;
+            const int krow = 32 * u + 8 * (n >> 1) + 2 * t + (n & 1);
+            const int swz = S::kSwizzleKeys ? ((krow & 1) << 2) : 0;
+#pragma unroll
+            for (int w = 0; w < D / 32; ++w) {
+                const uint4 kv = lds16(stage + (krow * S::kChunksPerKeyRow + ((4 * w + j) ^ swz)) * 16);
+                mma_16816(s[u][t], q[0][w].x, q[1][w].x, q[0][w].y, q[1][w].y, kv.x, kv.y);
+                mma_16816(s[u][t], q[0][w].z, q[1][w].z, q[0][w].w, q[1][w].w, kv.z, kv.w);
+            }
+        }
+    }
+    float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const int key = key0 + 32 * u + 8 * j + 2 * t + e;
+                const float a = key <= limit ? s[u][t][e] * scale_log2 : -INFINITY;
+                const float b = key <= limit ? s[u][t][2 + e] * scale_log2 : -INFINITY;
+                s[u][t][e] = a;
+                s[u][t][2 + e] = b;
+                mx0 = fmaxf(mx0, a);
+                mx1 = fmaxf(mx1, b);
+            }
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+    const float mn0 = fmaxf(st.m[0], mx0), mn1 = fmaxf(st.m[1], mx1);
+    const float use0 = mn0 == -INFINITY ? 0.f : mn0, use1 = mn1 == -INFINITY ? 0.f : mn1;
+    const float corr0 = exp2f(st.m[0] - use0), corr1 = exp2f(st.m[1] - use1);
+    st.m[0] = mn0;
+    st.m[1] = mn1;
+    float sum0 = 0.f, sum1 = 0.f;
+#pragma unroll
+    for (int u = 0; u < 2; ++u)
+#pragma unroll
+        for (int t = 0; t < 4; ++t)
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+                const float a = exp2f(s[u][t][e] - use0), b = exp2f(s[u][t][2 + e] - use1);
+                s[u][t][e] = a;
+                s[u][t][2 + e] = b;
+                sum0 += a;
+                sum1 += b;
+            }
+    st.l[0] = st.l[0] * corr0 + sum0;
+    st.l[1] = st.l[1] * corr1 + sum1;
+#pragma unroll
+    for (int nt = 0; nt < D / 8; ++nt) {
+        st.o[nt][0] *= corr0;
+        st.o[nt][1] *= corr0;
+        st.o[nt][2] *= corr1;
+        st.o[nt][3] *= corr1;
+    }
+    const uint32_t vbase = stage + S::kKeyBytes;
+#pragma unroll
+    for (int u = 0; u < 2; ++u) {
+        const uint32_t a0 = pack_bf16(s[u][0][0], s[u][0][1]), a1 = pack_bf16(s[u][0][2], s[u][0][3]);
+        const uint32_t a2 = pack_bf16(s[u][1][0], s[u][1][1]), a3 = pack_bf16(s[u][1][2], s[u][1][3]);
+        const uint32_t c0 = pack_bf16(s[u][2][0], s[u][2][1]), c1 = pack_bf16(s[u][2][2], s[u][2][3]);
+        const uint32_t c2 = pack_bf16(s[u][3][0], s[u][3][1]), c3 = pack_bf16(s[u][3][2], s[u][3][3]);
+#pragma unroll
+        for (int nt = 0; nt < D / 8; ++nt) {
+            const int row = 8 * nt + n;
+            const uint4 vv = lds16(vbase + (row * 8 + ((4 * u + j) ^ ((row & 1) << 2))) * 16);
+            mma_16816(st.o[nt], a0, a1, a2, a3, vv.x, vv.y);
+            mma_16816(st.o[nt], c0, c1, c2, c3, vv.z, vv.w);
+        }
+    }
+}
+
+template <int D>
+__global__ void __launch_bounds__(kDecodeWarps * 32)
 decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                         const int* __restrict__ kv_len, const int* __restrict__ slots,
                         const int* __restrict__ page_table, int max_pages, float* __restrict__ part_o,
                         float* __restrict__ part_ml, int n_heads, int n_kv, int m_tiles, int n_splits,
                         float scale_log2) {
-    // A block takes one share of a sequence's pages; its 4 warps take every fourth page of
-    // the share and merge their results in shared memory before anything is written.
-    __shared__ float sm_o[4][16][D + 4];
-    __shared__ float sm_m[4][16], sm_l[4][16];
+    // A block takes one share of a sequence's pages; its warps take every third page of the
+    // share and merge their results in shared memory before anything is written.
+    using S = DecodeSmem<D>;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ float sm_m[kDecodeWarps][16], sm_l[kDecodeWarps][16];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int split = blockIdx.x;
     const int kvh = blockIdx.y / m_tiles, mt = blockIdx.y % m_tiles, b = blockIdx.z;
@@ -161,37 +301,53 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
     const int n_pages = (len + kPageTokens - 1) / kPageTokens;
     const int per = (n_pages + n_splits - 1) / n_splits;
     const int p0 = split * per, p1 = min(n_pages, p0 + per);
+    const int* pages = page_table + (int64_t)slots[b] * max_pages;
+    const uint32_t my_stages = (uint32_t)__cvta_generic_to_shared(smem_raw) + warp * kDecodeStages * S::kStageBytes;
+    const int64_t page_elems = (int64_t)n_kv * kPageTokens * D;
+
+    auto issue = [&](int k) {           // the warp's k-th page into stage k % kDecodeStages
+        const int p = p0 + warp + k * kDecodeWarps;
+        if (p < p1) {
+            const int64_t base = (int64_t)pages[p] * page_elems + (int64_t)kvh * kPageTokens * D;
+            copy_page_async<D>(my_stages + (k % kDecodeStages) * S::kStageBytes, k_cache + base, v_cache + base, lane);
+        }
+        cp_async_commit();
+    };
+    issue(0);
+    issue(1);
 
     TileState<D> st;
     st.init();
-    if (p0 + warp < p1) {
-        uint4 qf[2][D / 32];
+    uint4 qf[2][D / 32];
 #pragma unroll
-        for (int r = 0; r < 2; ++r) {
-            const int local = mt * 16 + g + 8 * r;
-            const bool valid = local < group;
-            const bf16* qrow = q + ((int64_t)b * n_heads + kvh * group + (valid ? local : 0)) * D + 8 * j;
+    for (int r = 0; r < 2; ++r) {
+        const int local = min(mt * 16 + g + 8 * r, group - 1);      // rows beyond the group repeat a valid head; never stored
+        const bf16* qrow = q + ((int64_t)b * n_heads + kvh * group + local) * D + 8 * j;
 #pragma unroll
-            for (int w = 0; w < D / 32; ++w) qf[r][w] = valid ? ldg16(qrow + 32 * w) : make_uint4(0, 0, 0, 0);
-        }
-        const int* pages = page_table + (int64_t)slots[b] * max_pages;
-        for (int p = p0 + warp; p < p1; p += 4) {
-            const int page = pages[p];
-            const bf16* kpage = k_cache + ((int64_t)page * n_kv + kvh) * kPageTokens * D;
-            const bf16* vpage = v_cache + ((int64_t)page * n_kv + kvh) * D * kPageTokens;
-            attend_page<D>(st, qf, kpage, vpage, p * kPageTokens, len - 1, len - 1, scale_log2, lane);
-        }
+        for (int w = 0; w < D / 32; ++w) qf[r][w] = __ldg(reinterpret_cast<const uint4*>(qrow + 32 * w));
     }
-    // this thread's shares of the row sums -> whole rows
+    for (int k = 0; p0 + warp + k * kDecodeWarps < p1; ++k) {
+        cp_async_wait<kDecodeStages - 1>();
+        __syncwarp();
+        const int p = p0 + warp + k * kDecodeWarps;
+        attend_page_smem<D>(st, qf, my_stages + (k % kDecodeStages) * S::kStageBytes, p * kPageTokens, len - 1,
+                            scale_log2, lane);
+        __syncwarp();
+        issue(k + kDecodeStages);
+    }
+    cp_async_wait<0>();
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
         st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
     }
+    __syncthreads();                                       // every warp is done with its stages: reuse them
+    float* sm_o = reinterpret_cast<float*>(smem_raw);      // [warps][16][D + 4]
+    constexpr int kLd = D + 4;
 #pragma unroll
     for (int nt = 0; nt < D / 8; ++nt) {
-        *reinterpret_cast<float2*>(&sm_o[warp][g][8 * nt + 2 * j]) = make_float2(st.o[nt][0], st.o[nt][1]);
-        *reinterpret_cast<float2*>(&sm_o[warp][g + 8][8 * nt + 2 * j]) = make_float2(st.o[nt][2], st.o[nt][3]);
+        *reinterpret_cast<float2*>(&sm_o[(warp * 16 + g) * kLd + 8 * nt + 2 * j]) = make_float2(st.o[nt][0], st.o[nt][1]);
+        *reinterpret_cast<float2*>(&sm_o[(warp * 16 + g + 8) * kLd + 8 * nt + 2 * j]) = make_float2(st.o[nt][2], st.o[nt][3]);
     }
     if (j == 0) {
         sm_m[warp][g] = st.m[0];
@@ -202,17 +358,21 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
     __syncthreads();
     const int64_t unit = (((int64_t)b * n_kv + kvh) * m_tiles + mt) * n_splits + split;
     float* po = part_o + unit * 16 * D;
-    for (int i = threadIdx.x; i < 16 * D; i += 128) {
+    for (int i = threadIdx.x; i < 16 * D; i += kDecodeWarps * 32) {
         const int row = i / D, c = i - row * D;
-        const float m0 = sm_m[0][row], m1 = sm_m[1][row], m2 = sm_m[2][row], m3 = sm_m[3][row];
-        const float mx = fmaxf(fmaxf(m0, m1), fmaxf(m2, m3));
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kDecodeWarps; ++w) mx = fmaxf(mx, sm_m[w][row]);
         const float use = mx == -INFINITY ? 0.f : mx;
-        const float o = sm_o[0][row][c] * exp2f(m0 - use) + sm_o[1][row][c] * exp2f(m1 - use)
-                      + sm_o[2][row][c] * exp2f(m2 - use) + sm_o[3][row][c] * exp2f(m3 - use);
+        float o = 0.f, l = 0.f;
+#pragma unroll
+        for (int w = 0; w < kDecodeWarps; ++w) {
+            const float f = exp2f(sm_m[w][row] - use);
+            o += sm_o[(w * 16 + row) * kLd + c] * f;
+            l += sm_l[w][row] * f;
+        }
         po[i] = o;
         if (c == 0) {
-            const float l = sm_l[0][row] * exp2f(m0 - use) + sm_l[1][row] * exp2f(m1 - use)
-                          + sm_l[2][row] * exp2f(m2 - use) + sm_l[3][row] * exp2f(m3 - use);
             part_ml[unit * 32 + 2 * row] = mx;
             part_ml[unit * 32 + 2 * row + 1] = l;
         }
@@ -260,7 +420,15 @@ static int launch_decode(const void* q, const void* k_cache, const void* v_cache
     float* part_o = scratch;
     float* part_ml = scratch + (int64_t)n_seqs * n_kv * m_tiles * n_splits * 16 * D;
     dim3 grid(n_splits, n_kv * m_tiles, n_seqs);
-    decode_attention_kernel<D><<<grid, 128, 0, stream>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
+    auto kern = decode_attention_kernel<D>;
+    constexpr int smem = DecodeSmem<D>::kTotal;
+    static bool configured = false;      // per function and per process; setting it again would be harmless
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    kern<<<grid, kDecodeWarps * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
         kv_len, slots, page_table, max_pages, part_o, part_ml, n_heads, n_kv, m_tiles, n_splits,
         scale * 1.4426950408889634f);
     combine_splits_kernel<<<dim3(n_heads, n_seqs), D >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, (bf16*)out, n_heads,

@@ -4,7 +4,7 @@
 // come from the caches.
 //
 // A block owns 16 weight rows (one m16 tile of mma.sync m16n8k16, the weight as the A
-// operand, the tokens as the n8 columns) and its 8 warps take interleaved 32-element
+// operand, the tokens as the n8 columns) and its 8 or 16 warps take interleaved 32-element
 // slices of K, so that together they walk each row contiguously; the warps' partial sums
 // meet in shared memory.  A thread's 8 consecutive K elements stand for the k-slots of two
 // mma instructions; the sum over K does not care about the order as long as both operands
@@ -35,9 +35,7 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
     return v;
 }
 
-constexpr int kSkinnyWarps = 8;
-
-template <int NT, int EPI>
+template <int NT, int EPI, int kSkinnyWarps>
 __global__ void __launch_bounds__(kSkinnyWarps * 32)
 skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, void* __restrict__ out, int M, int N, int K,
                    float alpha) {
@@ -46,29 +44,25 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, void*
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, j = lane & 3;
     const int n0 = blockIdx.x * 16;
-    const bool row_ok0 = n0 + g < N, row_ok1 = n0 + g + 8 < N;
-    const bf16* w0 = W + (int64_t)(row_ok0 ? n0 + g : 0) * K + 8 * j;
-    const bf16* w1 = W + (int64_t)(row_ok1 ? n0 + g + 8 : 0) * K + 8 * j;
+    // Rows beyond N and token columns beyond M read a valid row instead and their results are never
+    // stored: rows of the product are independent, so no load needs a predicate.
+    const bf16* w0 = W + (int64_t)min(n0 + g, N - 1) * K + 8 * j;
+    const bf16* w1 = W + (int64_t)min(n0 + g + 8, N - 1) * K + 8 * j;
     const bf16* xp[NT];
-    bool tok_ok[NT];
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-        tok_ok[nt] = nt * 8 + g < M;
-        xp[nt] = X + (int64_t)(tok_ok[nt] ? nt * 8 + g : 0) * K + 8 * j;
-    }
+    for (int nt = 0; nt < NT; ++nt) xp[nt] = X + (int64_t)min(nt * 8 + g, M - 1) * K + 8 * j;
     float acc[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.f;
 
     const int steps = K / 32;
-    const uint4 zero = make_uint4(0, 0, 0, 0);
 #pragma unroll 4
     for (int s = warp; s < steps; s += kSkinnyWarps) {
-        const uint4 lo = row_ok0 ? ld_stream16(w0 + 32 * s) : zero;
-        const uint4 hi = row_ok1 ? ld_stream16(w1 + 32 * s) : zero;
+        const uint4 lo = ld_stream16(w0 + 32 * s);
+        const uint4 hi = ld_stream16(w1 + 32 * s);
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) {
-            const uint4 b = tok_ok[nt] ? __ldg(reinterpret_cast<const uint4*>(xp[nt] + 32 * s)) : zero;
+            const uint4 b = __ldg(reinterpret_cast<const uint4*>(xp[nt] + 32 * s));
             mma_16816_s(acc[nt], lo.x, hi.x, lo.y, hi.y, b.x, b.y);
             mma_16816_s(acc[nt], lo.z, hi.z, lo.w, hi.w, b.z, b.w);
         }
@@ -83,8 +77,9 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, void*
     __syncthreads();
     if (EPI == EPI_SILU) {
         // rows 0..7 are gate, rows 8..15 up, of features (n0 / 2) + 0..7
-        const int f = threadIdx.x & 7, tok = threadIdx.x >> 3;
-        if (tok < M && tok < MT) {
+        for (int o = threadIdx.x; o < 8 * MT; o += kSkinnyWarps * 32) {
+            const int f = o & 7, tok = o >> 3;
+            if (tok >= M) continue;
             float gate = 0.f, up = 0.f;
 #pragma unroll
             for (int w = 0; w < kSkinnyWarps; ++w) {
@@ -98,8 +93,9 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, void*
             }
         }
     } else {
-        const int row = threadIdx.x & 15, tok = threadIdx.x >> 4;
-        if (tok < M && tok < MT && n0 + row < N) {
+        for (int o = threadIdx.x; o < 16 * MT; o += kSkinnyWarps * 32) {
+            const int row = o & 15, tok = o >> 4;
+            if (tok >= M || n0 + row >= N) continue;
             float sum = 0.f;
 #pragma unroll
             for (int w = 0; w < kSkinnyWarps; ++w) sum += red[w][row][tok];
@@ -109,20 +105,25 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, void*
     }
 }
 
+template <int NT, int EPI>
+static int launch_skinny_epi(const void* W, const void* X, void* out, int M, int N, int K, float alpha,
+                             cudaStream_t stream) {
+    // Few row tiles (a narrow output): more warps per tile, so that enough loads are in flight.
+    const unsigned blocks = (unsigned)((N + 15) / 16);
+    if (blocks < 148 * 4)
+        skinny_gemm_kernel<NT, EPI, 16><<<blocks, 512, 0, stream>>>((const bf16*)W, (const bf16*)X, out, M, N, K, alpha);
+    else
+        skinny_gemm_kernel<NT, EPI, 8><<<blocks, 256, 0, stream>>>((const bf16*)W, (const bf16*)X, out, M, N, K, alpha);
+    return launch_status();
+}
+
 template <int NT>
 static int launch_skinny(const void* W, const void* X, void* out, int M, int N, int K, float alpha, int epilogue,
                          cudaStream_t stream) {
-    const unsigned blocks = (unsigned)((N + 15) / 16);
-    const int threads = kSkinnyWarps * 32;
-    if (epilogue == EPI_BF16)
-        skinny_gemm_kernel<NT, EPI_BF16><<<blocks, threads, 0, stream>>>((const bf16*)W, (const bf16*)X, out, M, N, K, alpha);
-    else if (epilogue == EPI_F32)
-        skinny_gemm_kernel<NT, EPI_F32><<<blocks, threads, 0, stream>>>((const bf16*)W, (const bf16*)X, out, M, N, K, alpha);
-    else if (epilogue == EPI_SILU)
-        skinny_gemm_kernel<NT, EPI_SILU><<<blocks, threads, 0, stream>>>((const bf16*)W, (const bf16*)X, out, M, N, K, alpha);
-    else
-        return CPM_BAD_ARGUMENT;
-    return launch_status();
+    if (epilogue == EPI_BF16) return launch_skinny_epi<NT, EPI_BF16>(W, X, out, M, N, K, alpha, stream);
+    if (epilogue == EPI_F32) return launch_skinny_epi<NT, EPI_F32>(W, X, out, M, N, K, alpha, stream);
+    if (epilogue == EPI_SILU) return launch_skinny_epi<NT, EPI_SILU>(W, X, out, M, N, K, alpha, stream);
+    return CPM_BAD_ARGUMENT;
 }
 
 // W [N,K] bf16, X [M,K] bf16 (both contiguous); out [M,N] bf16 or fp32, or [M,N/2] bf16 for the gated

@@ -23,7 +23,6 @@ from .library import check
 F32, BF16 = 0, 1
 PAGE_TOKENS = 64
 FAST_HEAD_DIMS = (32, 64, 96, 128)       # head sizes the tensor-core attention kernels are built for
-DECODE_TARGET_BLOCKS = 148 * 3           # blocks (of 4 warps) the split-key decode attention aims for
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -47,6 +46,7 @@ class Ops:
             raise library.KernelLibraryError("no CUDA device is available; there is no CPU path")
         self.lib = library.load()
         self.element_size = 4 if dtype == torch.float32 else 2
+        self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
 
     # ---- checks ----
     def _act(self, t: torch.Tensor, what: str) -> torch.Tensor:
@@ -266,12 +266,12 @@ class Ops:
                                           _ptr(live), ids.numel(), _stream()), "advance_decode")
 
     # ---- bf16 tensor-core attention ----
-    @staticmethod
-    def decode_splits(n_seqs: int, n_heads: int, n_kv: int) -> int:
-        """How many shares a sequence's pages are cut into: enough warps to fill the GPU."""
+    def decode_splits(self, n_seqs: int, n_heads: int, n_kv: int) -> int:
+        """How many shares a sequence's pages are cut into: the decode attention kernel holds one
+        block per SM (its page buffers fill the shared memory), so aim at one wave of blocks."""
         m_tiles = (n_heads // n_kv + 15) // 16
         units = max(1, n_seqs * n_kv * m_tiles)
-        return max(1, min(16, -(-DECODE_TARGET_BLOCKS // units)))
+        return max(1, min(16, self.sm_count // units))
 
     def decode_attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kv_len: torch.Tensor,
                          slots: torch.Tensor, page_table: torch.Tensor, n_kv: int, scale: float,
