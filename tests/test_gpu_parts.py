@@ -1,0 +1,326 @@
+"""The parts of a model alone, models put together from other parts than MiniCPM4's, and
+schedules that run a layer twice or share a layer's keys and values.  Everything here is
+built through the registries from a ModelSpec written in the test: no file of the
+package is changed to add a part."""
+import math
+
+import pytest
+import torch
+
+from tests import configs, helpers
+from tests.plain import minicpm4_plain as plain
+
+pytestmark = pytest.mark.gpu
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+TOL = {"float32": 2e-5, "bfloat16": 2e-2}
+
+
+def _ops(dtype):
+    from cpmcu_b200.ops.ops import Ops
+    return Ops(DT[dtype], "cuda:0")
+
+
+def _err(got, want):
+    got, want = got.float().cpu(), want.float().cpu()
+    return float((got - want).abs().max() / want.abs().max().clamp_min(1e-30))
+
+
+# ---------------------------------------------------------------------------
+# each part alone
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_norm_part(dtype):
+    from cpmcu_b200.parts import NORMS, PartSpec, build_part
+
+    ops = _ops(dtype)
+    norm = build_part(NORMS, PartSpec("rms_norm", {"hidden_size": 72, "eps": 3e-6}), ops)
+    assert norm.weight_specs()["weight"].shape == (72,) and norm.weight_specs()["weight"].role == "vector"
+    g = torch.Generator().manual_seed(0)
+    w = (1 + 0.1 * torch.randn(72, generator=g)).to(DT[dtype])
+    norm.load_weights({"weight": w.cuda()})
+    x = torch.randn(11, 72, generator=g)
+    assert _err(norm.forward(x.cuda()), plain.rms_norm(x, w.float(), 3e-6)) < TOL[dtype]
+    d = torch.randn(11, 72, generator=g).to(DT[dtype])
+    xs = x.clone().cuda()
+    y = norm.add_forward(xs, d.cuda(), 0.7)
+    assert _err(xs, x + 0.7 * d.float()) < 1e-6
+    assert _err(y, plain.rms_norm(x + 0.7 * d.float(), w.float(), 3e-6)) < TOL[dtype]
+
+
+def test_position_parts():
+    from cpmcu_b200.parts import POSITIONS, PartSpec, build_part
+
+    ops = _ops("float32")
+    cfg = configs.tiny_b()
+    rs = cfg["rope_scaling"]
+    long = build_part(POSITIONS, PartSpec("longrope", {
+        "head_dim": 32, "theta": cfg["rope_theta"], "long_factor": rs["long_factor"], "short_factor": rs["short_factor"],
+        "original_max_positions": 64, "max_positions": 256}), ops)
+    inv, mag, rot = long.rotary()
+    want_inv, want_mag = plain.rope_table(cfg)
+    assert rot == 32 and mag == pytest.approx(want_mag) and torch.equal(inv.cpu(), want_inv)
+    short = build_part(POSITIONS, PartSpec("longrope", {
+        "head_dim": 32, "theta": cfg["rope_theta"], "long_factor": rs["long_factor"], "short_factor": rs["short_factor"],
+        "original_max_positions": 64, "max_positions": 64}), ops)
+    inv_s, mag_s, _ = short.rotary()
+    assert mag_s == 1.0 and torch.equal(inv_s.cpu(), plain.rope_table(dict(cfg, max_position_embeddings=64))[0])
+    assert build_part(POSITIONS, PartSpec("none", {}), ops).rotary() == (None, 1.0, 0)
+    with pytest.raises(KeyError, match="known"):
+        build_part(POSITIONS, PartSpec("alibi", {}), ops)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("inter", [176, 100])          # a multiple of 8 (interleaved layout) and one that is not
+def test_feed_forward_part(dtype, inter):
+    from cpmcu_b200.parts import FEED_FORWARDS, PartSpec, build_part
+
+    ops = _ops(dtype)
+    ffn = build_part(FEED_FORWARDS, PartSpec("gated_ffn", {"hidden_size": 64, "intermediate_size": inter}), ops)
+    g = torch.Generator().manual_seed(1)
+    w = {n: (torch.randn(s.shape, generator=g) * 0.1).to(DT[dtype]) for n, s in ffn.weight_specs().items()}
+    ffn.load_weights({n: t.cuda() for n, t in w.items()})
+    for rows in (3, 40):                                # the decode product and the library product
+        y = torch.randn(rows, 64, generator=g).to(DT[dtype])
+        want = plain.gated_ffn(y.float(), {"p." + n: t.float() for n, t in w.items()}, "p.")
+        assert _err(ffn.forward(None, y.cuda()), want) < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embedding_and_head_parts(dtype):
+    from cpmcu_b200.parts import EMBEDDINGS, HEADS, PartSpec, build_part
+
+    ops = _ops(dtype)
+    emb = build_part(EMBEDDINGS, PartSpec("scaled_embedding", {"vocab_size": 777, "hidden_size": 72, "scale": 12.0}), ops)
+    head = build_part(HEADS, PartSpec("scaled_lm_head", {"vocab_size": 777, "hidden_size": 72, "scale": 0.25, "tied": True}), ops)
+    assert head.weight_specs() == {}
+    g = torch.Generator().manual_seed(2)
+    table = (torch.randn(777, 72, generator=g) * 0.02).to(DT[dtype])
+    emb.load_weights({"weight": table.cuda()})
+    head.tie(emb.weight)
+    ids = [5, 776, 0, 5]
+    assert _err(emb.forward(torch.tensor(ids, dtype=torch.int32).cuda()), plain.embed(ids, table.float(), 12.0)) < 1e-6
+    y = torch.randn(4, 72, generator=g).to(DT[dtype])
+    want = plain.lm_head(y.float(), {"model.embed_tokens.weight": table.float()}, {"tie_word_embeddings": True}, 0.25)
+    got = head.forward(y.cuda())
+    assert got.dtype == torch.float32 and _err(got, want) < TOL[dtype]
+
+
+# ---------------------------------------------------------------------------
+# a model from a hand-written specification, with a mixer the package does not know
+# ---------------------------------------------------------------------------
+
+def _register_toy_parts():
+    from cpmcu_b200.parts import MIXERS, CacheNeeds, Mixer, WeightSpec
+
+    if "toy_decay" in MIXERS:
+        return
+
+    @MIXERS.register("toy_decay")
+    class DecayMixer(Mixer):
+        """s_t = decay * s_{t-1} + W_in y_t;  out_t = W_out s_t.  The running sum s is state of the
+        mixer's own: one fp32 vector per sequence, kept by the cache beside the keys and values."""
+
+        def __init__(self, ops, hidden_size, state_size, decay):
+            super().__init__(ops)
+            self.h, self.n, self.decay = hidden_size, state_size, decay
+
+        def weight_specs(self):
+            return {"in.weight": WeightSpec((self.n, self.h)), "out.weight": WeightSpec((self.h, self.n))}
+
+        def load_weights(self, tensors):
+            self.w_in, self.w_out = tensors["in.weight"].float(), tensors["out.weight"].float()
+
+        def cache_needs(self):
+            return CacheNeeds(state={"s": ((self.n,), torch.float32)})
+
+        def forward(self, ctx, y, lane, writes_cache):
+            out = torch.empty_like(y)
+            state = lane.state["s"]
+            o = 0
+            for slot, n in zip(ctx.slots, ctx.q_lens):
+                s = state[slot].clone()
+                for t in range(n):
+                    s = self.decay * s + self.w_in @ y[o + t].float()
+                    out[o + t] = (self.w_out @ s).to(y.dtype)
+                state[slot] = s
+                o += n
+            return out
+
+
+TOY = dict(hidden=64, heads=4, kv=2, d=16, inter=96, vocab=300, eps=1e-5, state=24, decay=0.9, rs=0.8)
+
+
+def _toy_spec(schedule=None):
+    from cpmcu_b200.parts import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+
+    _register_toy_parts()
+    c = TOY
+    norm = PartSpec("rms_norm", {"hidden_size": c["hidden"], "eps": c["eps"]})
+    attn = PartSpec("gqa_attention", {"hidden_size": c["hidden"], "n_heads": c["heads"], "n_kv_heads": c["kv"],
+                                      "head_dim": c["d"], "position": PartSpec("rope", {"head_dim": c["d"], "theta": 10000.0})})
+    toy = PartSpec("toy_decay", {"hidden_size": c["hidden"], "state_size": c["state"], "decay": c["decay"]})
+    ffn = PartSpec("gated_ffn", {"hidden_size": c["hidden"], "intermediate_size": c["inter"]})
+    block = PartSpec("pre_norm_residual", {"residual_scale": c["rs"]})
+    names = {"mixer_norm": "n1.", "mixer": "mix.", "feed_forward_norm": "n2.", "feed_forward": "ff."}
+    layers = [LayerSpec(block, attn, ffn, norm, norm, "L0.", names), LayerSpec(block, toy, ffn, norm, norm, "L1.", names),
+              LayerSpec(block, attn, ffn, norm, norm, "L2.", names)]
+    if schedule is None:
+        schedule = [ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(2, 2)]
+    return ModelSpec("Toy", c["hidden"], c["vocab"], PartSpec("scaled_embedding", {"vocab_size": c["vocab"], "hidden_size": c["hidden"], "scale": 3.0}),
+                     layers, schedule, norm, PartSpec("scaled_lm_head", {"vocab_size": c["vocab"], "hidden_size": c["hidden"], "scale": 0.5}),
+                     embedding_name="emb.", final_norm_name="fn.", head_name="head.")
+
+
+def _toy_reference(w, ids, schedule):
+    """The toy model with the plain implementation's functions; runs are (layer, lane, writes)."""
+    c = TOY
+    cfg = {"num_attention_heads": c["heads"], "num_key_value_heads": c["kv"], "head_dim": c["d"], "hidden_size": c["hidden"],
+           "rope_theta": 10000.0, "max_position_embeddings": 4096}
+    w = {k: v.float().cpu() for k, v in w.items()}
+    S = len(ids)
+    x = plain.embed(ids, w["emb.weight"], 3.0)
+    lanes = {}
+    for layer, lane, writes in schedule:
+        p = f"L{layer}."
+        y = plain.rms_norm(x, w[p + "n1.weight"], c["eps"])
+        if layer == 1:
+            s = torch.zeros(c["state"])
+            a = torch.empty_like(y)
+            for t in range(S):
+                s = c["decay"] * s + w[p + "mix.in.weight"] @ y[t]
+                a[t] = w[p + "mix.out.weight"] @ s
+        else:
+            a, kv = plain.attention_layer(y, w, p + "mix.", cfg, torch.arange(S), None if writes else lanes[lane])
+            if writes:
+                lanes[lane] = kv
+        x = x + c["rs"] * a
+        y = plain.rms_norm(x, w[p + "n2.weight"], c["eps"])
+        ff = {"f.gate_proj.weight": w[p + "ff.gate_proj.weight"], "f.up_proj.weight": w[p + "ff.up_proj.weight"],
+              "f.down_proj.weight": w[p + "ff.down_proj.weight"]}
+        x = x + c["rs"] * plain.gated_ffn(y, ff, "f.")
+    return plain.lm_head(plain.rms_norm(x, w["fn.weight"], c["eps"]), {"lm_head.weight": w["head.weight"]}, {}, 0.5)
+
+
+def _toy_stepper(dtype, schedule=None):
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.engine import Stepper
+    from cpmcu_b200.models.model import Model
+    from cpmcu_b200.weights import random_tensors
+
+    spec = _toy_spec(schedule)
+    model = Model(spec, _ops(dtype))
+    w = random_tensors(model.weight_specs(), 7, DT[dtype], std=0.1)
+    model.load_weights({k: v.cuda() for k, v in w.items()})
+    cache = Cache(model.cache_needs(), max_tokens=64 * 8, dtype=DT[dtype], device="cuda:0")
+    return spec, w, Stepper(model, cache, chunk_tokens=16)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_mixer_with_state_of_its_own(dtype):
+    from cpmcu_b200.engine import SequenceStep
+
+    spec, w, st = _toy_stepper(dtype)
+    sched = [(e.layer, e.lane, e.writes_cache) for e in spec.schedule]
+    # the cache made a state tensor for the toy layer's lane, and no keys for it
+    assert st.cache.lane(1).k is None and st.cache.lane(1).state["s"].shape[1] == TOY["state"]
+    assert st.cache.lane(0).k is not None and st.cache.lane(0).state == {}
+    seqs = [helpers.random_ids(TOY["vocab"], n, n) for n in (37, 5, 20)]
+    wants = [_toy_reference(w, ids, sched) for ids in seqs]
+    for round_ in range(2):                                    # the second round reuses the slots: state must restart
+        slots = st.open(3)
+        cut = [20, 5, 1]
+        # prompts of unequal lengths in one step (chunked at 16 tokens), then token by token
+        out = st.step([SequenceStep(s, ids[:c], list(range(c))) for s, ids, c in zip(slots, seqs, cut)])
+        got = [[out[sum(cut[:i]):sum(cut[:i + 1])]] for i in range(3)]
+        t = 0
+        while any(c + t < len(ids) for ids, c in zip(seqs, cut)):
+            live = [i for i in range(3) if cut[i] + t < len(seqs[i])]
+            out = st.step([SequenceStep(slots[i], [seqs[i][cut[i] + t]], [0]) for i in live])
+            for r, i in enumerate(live):
+                got[i].append(out[r:r + 1])
+            t += 1
+        for i in range(3):
+            assert _err(torch.cat(got[i]), wants[i]) < TOL[dtype], (round_, i)
+            st.close(slots[i])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_schedule_runs_a_layer_twice_and_shares_a_cache_lane(dtype):
+    """Order of layers is data: layer 0 runs twice (each run with a lane of its own), and layer 2
+    reads the keys and values that the first run of layer 0 stored instead of making its own."""
+    from cpmcu_b200.engine import SequenceStep
+    from cpmcu_b200.parts import ScheduleEntry
+
+    schedule = [ScheduleEntry(0, 0), ScheduleEntry(1, 1), ScheduleEntry(0, 2), ScheduleEntry(2, 0, writes_cache=False)]
+    spec, w, st = _toy_stepper(dtype, schedule)
+    sched = [(e.layer, e.lane, e.writes_cache) for e in schedule]
+    ids = helpers.random_ids(TOY["vocab"], 50, 3)
+    want = _toy_reference(w, ids, sched)
+    slot = st.open(1)[0]
+    a = st.step([SequenceStep(slot, ids[:33], list(range(33)))])
+    b = torch.cat([st.step([SequenceStep(slot, ids[i:i + 1], [0])]) for i in range(33, 50)])
+    assert _err(torch.cat([a, b]), want) < TOL[dtype]
+    from cpmcu_b200.models.model import Model
+    with pytest.raises(ValueError, match="before any run has written"):
+        Model(_toy_spec([ScheduleEntry(0, 1, writes_cache=False), ScheduleEntry(1, 1)]), _ops(dtype))
+
+
+# ---------------------------------------------------------------------------
+# places where a fault would hide
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(model_folders, dtype):
+    """300 tokens decoded one by one from a one-token prompt: every page boundary is crossed by a
+    decode step, and the first tokens of the sequence are checked one by one."""
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.engine import SequenceStep, Stepper
+    from cpmcu_b200.loading import load_model
+
+    folder = model_folders("tiny_c", configs.tiny_c(), 5, dtype)
+    _, cfg, model = load_model(folder, dtype)
+    st = Stepper(model, Cache(model.cache_needs(), 64 * 6, DT[dtype], "cuda:0"))
+    ids = helpers.random_ids(cfg.vocab_size, 301, 9)
+    want = helpers.plain_logits(folder, ids)
+    slot = st.open(1)[0]
+    rows = [st.step([SequenceStep(slot, ids[i:i + 1], [0])]) for i in range(301)]
+    got = torch.cat(rows)
+    for i in (0, 1, 2, 3):
+        assert helpers.rel_err(got[i:i + 1], want[i:i + 1]) < helpers.TOL[dtype], i
+    for lo in range(0, 301, 64):
+        assert helpers.rel_err(got[lo:lo + 64], want[lo:lo + 64]) < helpers.TOL[dtype], lo
+
+
+def test_window_attention_is_a_parameter_of_the_mixer():
+    """A window of 24 keys on the attention part: its lanes form a cache group of their own."""
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.parts import MIXERS, PartSpec, StepContext, build_part
+
+    ops = _ops("float32")
+    spec = PartSpec("gqa_attention", {"hidden_size": 32, "n_heads": 2, "n_kv_heads": 1, "head_dim": 16, "window": 24,
+                                      "position": PartSpec("none", {})})
+    att = build_part(MIXERS, spec, ops)
+    full = build_part(MIXERS, PartSpec("gqa_attention", dict(spec.params, window=None)), ops)
+    g = torch.Generator().manual_seed(4)
+    w = {n: torch.randn(s.shape, generator=g) * 0.3 for n, s in att.weight_specs().items()}
+    att.load_weights({n: t.cuda() for n, t in w.items()})
+    full.load_weights({n: t.cuda() for n, t in w.items()})
+    cache = Cache([att.cache_needs(), full.cache_needs()], 256, torch.float32, "cuda:0")
+    assert len(cache.groups) == 2 and cache.groups[0].needs.window == 24 and cache.groups[1].needs.window is None
+    slot = cache.open_sequence()
+    n = 70
+    cache.reserve(slot, n)
+    cache.sync()
+    y = torch.randn(n, 32, generator=g)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32).cuda()
+    ctx = StepContext(n, 1, False, False, [n], [n], [slot], n, n, i32([0] * n), i32(list(range(n))), i32([0] * n),
+                      i32([0, n]), i32([n]), i32([slot]), cache)
+    got = att.forward(ctx, y.cuda(), cache.lane(0), True)
+    q = (y @ w["q_proj.weight"].T).view(n, 2, 16)
+    k = (y @ w["k_proj.weight"].T).view(n, 1, 16)
+    v = (y @ w["v_proj.weight"].T).view(n, 1, 16)
+    want = plain.dense_attention(q, k, v, 0.25, window=24).reshape(n, 32) @ w["o_proj.weight"].T
+    assert _err(got, want) < 2e-5
+    dense = full.forward(ctx, y.cuda(), cache.lane(1), True)
+    assert _err(dense[:24], want[:24]) < 2e-5 and _err(dense[30:], want[30:]) > 1e-3
