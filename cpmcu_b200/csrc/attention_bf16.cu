@@ -177,19 +177,19 @@ struct DecodeSmem {
 };
 
 // Copies one key page and one value page (both contiguous in global memory) into a stage.
-template <int D>
+template <int D, int kThreads = 32>
 __device__ __forceinline__ void copy_page_async(uint32_t stage, const bf16* __restrict__ kpage,
                                                 const bf16* __restrict__ vpage, int lane) {
     using S = DecodeSmem<D>;
     constexpr int kChunks = S::kKeyBytes / 16;
-#pragma unroll 8
-    for (int c = lane; c < kChunks; c += 32) {
+#pragma unroll 4
+    for (int c = lane; c < kChunks; c += kThreads) {
         const int row = c / S::kChunksPerKeyRow, col = c % S::kChunksPerKeyRow;
         const int pcol = S::kSwizzleKeys ? (col ^ ((row & 1) << 2)) : col;
         cp_async16(stage + (row * S::kChunksPerKeyRow + pcol) * 16, kpage + c * 8);
     }
-#pragma unroll 8
-    for (int c = lane; c < kChunks; c += 32) {
+#pragma unroll 4
+    for (int c = lane; c < kChunks; c += kThreads) {
         const int row = c >> 3, col = c & 7;                               // value rows hold 64 tokens = 8 chunks
         cp_async16(stage + S::kKeyBytes + (row * 8 + (col ^ ((row & 1) << 2))) * 16, vpage + c * 8);
     }
@@ -198,19 +198,23 @@ __device__ __forceinline__ void copy_page_async(uint32_t stage, const bf16* __re
 // attend_page with both pages in shared memory (same fragment assignment).
 template <int D>
 __device__ __forceinline__ void attend_page_smem(TileState<D>& st, const uint4 (&q)[2][D / 32], uint32_t stage, int key0,
-                                                 int limit, float scale_log2, int lane) {
+                                                 int limit0, int limit1, float scale_log2, int lane) {
     using S = DecodeSmem<D>;
     const int j = lane & 3, n = lane >> 2;
     float s[2][4][4];
 #pragma unroll
-    for (int u = 0; u < 2; ++u) {
+    for (int u = 0; u < 2; ++u)
 #pragma unroll
-        for (int t = 0; t < 4; ++t) {
-            s[u][t][0] = s[u][t][1] = s[u][t][2] = s[u][t][3] = 0.f;
-            const int krow = 32 * u + 8 * (n >> 1) + 2 * t + (n & 1);
-            const int swz = S::kSwizzleKeys ? ((krow & 1) << 2) : 0;
+        for (int t = 0; t < 4; ++t) s[u][t][0] = s[u][t][1] = s[u][t][2] = s[u][t][3] = 0.f;
+    // the eight score tiles are independent accumulator chains: walk head_dim in the outer loop
 #pragma unroll
-            for (int w = 0; w < D / 32; ++w) {
+    for (int w = 0; w < D / 32; ++w) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u) {
+#pragma unroll
+            for (int t = 0; t < 4; ++t) {
+                const int krow = 32 * u + 8 * (n >> 1) + 2 * t + (n & 1);
+                const int swz = S::kSwizzleKeys ? ((krow & 1) << 2) : 0;
                 const uint4 kv = lds16(stage + (krow * S::kChunksPerKeyRow + ((4 * w + j) ^ swz)) * 16);
                 mma_16816(s[u][t], q[0][w].x, q[1][w].x, q[0][w].y, q[1][w].y, kv.x, kv.y);
                 mma_16816(s[u][t], q[0][w].z, q[1][w].z, q[0][w].w, q[1][w].w, kv.z, kv.w);
@@ -225,8 +229,8 @@ __device__ __forceinline__ void attend_page_smem(TileState<D>& st, const uint4 (
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int key = key0 + 32 * u + 8 * j + 2 * t + e;
-                const float a = key <= limit ? s[u][t][e] * scale_log2 : -INFINITY;
-                const float b = key <= limit ? s[u][t][2 + e] * scale_log2 : -INFINITY;
+                const float a = key <= limit0 ? s[u][t][e] * scale_log2 : -INFINITY;
+                const float b = key <= limit1 ? s[u][t][2 + e] * scale_log2 : -INFINITY;
                 s[u][t][e] = a;
                 s[u][t][2 + e] = b;
                 mx0 = fmaxf(mx0, a);
@@ -330,7 +334,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
         cp_async_wait<kDecodeStages - 1>();
         __syncwarp();
         const int p = p0 + warp + k * kDecodeWarps;
-        attend_page_smem<D>(st, qf, my_stages + (k % kDecodeStages) * S::kStageBytes, p * kPageTokens, len - 1,
+        attend_page_smem<D>(st, qf, my_stages + (k % kDecodeStages) * S::kStageBytes, p * kPageTokens, len - 1, len - 1,
                             scale_log2, lane);
         __syncwarp();
         issue(k + kDecodeStages);
@@ -455,23 +459,47 @@ CPM_API int cpm_decode_attention_bf16(const void* q, const void* k_cache, const 
 // ---------------------------------------------------------------------------
 // prefill
 // ---------------------------------------------------------------------------
-// A block of 4 warps takes 64 consecutive query tokens of one sequence and one head;
-// tile_seq/tile_row name the sequence (index in the batch) and the first of the 64
-// tokens (offset inside this step's tokens of the sequence) of every block.
+// A block of 8 warps takes 128 consecutive query tokens of one sequence and one head, 16 per
+// warp; tile_seq/tile_row name the sequence (index in the batch) and the first of the 128
+// tokens (offset inside this step's tokens of the sequence) of every block.  The block walks
+// over the key pages up to its last token; a page is brought into shared memory once
+// (cp.async, two pages in flight) and read by all 8 warps.
+constexpr int kPrefillWarps = 8;
+constexpr int kPrefillRows = kPrefillWarps * 16;
+
 template <int D>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(kPrefillWarps * 32)
 prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                          bf16* __restrict__ out, const int* __restrict__ tile_seq, const int* __restrict__ tile_row,
                          const int* __restrict__ cu_q, const int* __restrict__ kv_len, const int* __restrict__ slots,
                          const int* __restrict__ page_table, int max_pages, int n_heads, int n_kv, float scale_log2) {
+    using S = DecodeSmem<D>;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    const uint32_t stages = (uint32_t)__cvta_generic_to_shared(smem_raw);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int j = lane & 3, g = lane >> 2;
-    const int seq = tile_seq[blockIdx.x], h = blockIdx.y;
+    const int tile = gridDim.y - 1 - blockIdx.y;                 // later tiles of a sequence are longer: they go first
+    const int seq = tile_seq[tile], h = blockIdx.x;
     const int kvh = h / (n_heads / n_kv);
     const int q_begin = cu_q[seq], q_len = cu_q[seq + 1] - q_begin;
-    const int row0 = tile_row[blockIdx.x] + 16 * warp;           // first of this warp's 16 tokens
-    if (row0 >= q_len) return;
+    const int tile_row0 = tile_row[tile];
+    const int row0 = tile_row0 + 16 * warp;                      // first of this warp's 16 tokens
     const int history = kv_len[seq] - q_len;                     // keys cached before this step's tokens
+    const int* pages = page_table + (int64_t)slots[seq] * max_pages;
+    const int64_t page_elems = (int64_t)n_kv * kPageTokens * D;
+    const int last_page = (history + min(tile_row0 + kPrefillRows, q_len) - 1) / kPageTokens;    // of the block
+    const int my_last_page = row0 < q_len ? (history + min(row0 + 16, q_len) - 1) / kPageTokens : -1;
+
+    auto issue = [&](int p) {
+        if (p <= last_page) {
+            const int64_t base = (int64_t)pages[p] * page_elems + (int64_t)kvh * kPageTokens * D;
+            copy_page_async<D, kPrefillWarps * 32>(stages + (p & 1) * S::kStageBytes, k_cache + base, v_cache + base,
+                                                   threadIdx.x);
+        }
+        cp_async_commit();
+    };
+    issue(0);
+    issue(1);
 
     uint4 qf[2][D / 32];
     int limit[2];
@@ -482,18 +510,19 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
         limit[r] = valid ? history + row : -1;
         const bf16* qrow = q + ((int64_t)(q_begin + (valid ? row : 0)) * n_heads + h) * D + 8 * j;
 #pragma unroll
-        for (int w = 0; w < D / 32; ++w) qf[r][w] = valid ? ldg16(qrow + 32 * w) : make_uint4(0, 0, 0, 0);
+        for (int w = 0; w < D / 32; ++w) qf[r][w] = __ldg(reinterpret_cast<const uint4*>(qrow + 32 * w));
     }
     TileState<D> st;
     st.init();
-    const int last_key = history + min(row0 + 15, q_len - 1);
-    const int* pages = page_table + (int64_t)slots[seq] * max_pages;
-    for (int p = 0; p <= last_key / kPageTokens; ++p) {
-        const int page = pages[p];
-        const bf16* kpage = k_cache + ((int64_t)page * n_kv + kvh) * kPageTokens * D;
-        const bf16* vpage = v_cache + ((int64_t)page * n_kv + kvh) * D * kPageTokens;
-        attend_page<D>(st, qf, kpage, vpage, p * kPageTokens, limit[0], limit[1], scale_log2, lane);
+    for (int p = 0; p <= last_page; ++p) {
+        cp_async_wait<1>();
+        __syncthreads();
+        if (p <= my_last_page)
+            attend_page_smem<D>(st, qf, stages + (p & 1) * S::kStageBytes, p * kPageTokens, limit[0], limit[1], scale_log2, lane);
+        __syncthreads();
+        issue(p + 2);
     }
+    cp_async_wait<0>();
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
@@ -508,12 +537,23 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
     }
 }
 
+// Query tokens per block of the prefill kernel (the tile lists are made for this size).
+CPM_API int cpm_prefill_attention_tile_rows() { return kPrefillRows; }
+
 template <int D>
 static int launch_prefill(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq,
                           const int* tile_row, int n_tiles, const int* cu_q, const int* kv_len, const int* slots,
                           const int* page_table, int max_pages, int n_heads, int n_kv, float scale,
                           cudaStream_t stream) {
-    prefill_attention_kernel<D><<<dim3(n_tiles, n_heads), 128, 0, stream>>>((const bf16*)q, (const bf16*)k_cache,
+    auto kern = prefill_attention_kernel<D>;
+    constexpr int smem = 2 * DecodeSmem<D>::kStageBytes;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    kern<<<dim3(n_heads, n_tiles), kPrefillWarps * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_cache,
         (const bf16*)v_cache, (bf16*)out, tile_seq, tile_row, cu_q, kv_len, slots, page_table, max_pages, n_heads, n_kv,
         scale * 1.4426950408889634f);
     return launch_status();
@@ -525,7 +565,7 @@ CPM_API int cpm_prefill_attention_bf16(const void* q, const void* k_cache, const
                                        const int* kv_len, const int* slots, const int* page_table, int max_pages,
                                        int n_heads, int n_kv, int d, float scale, cudaStream_t stream) {
     if (n_tiles <= 0) return CPM_OK;
-    if (n_kv <= 0 || n_heads % n_kv || n_heads > 65535) return CPM_BAD_ARGUMENT;
+    if (n_kv <= 0 || n_heads % n_kv || n_tiles > 65535) return CPM_BAD_ARGUMENT;
     switch (d) {
         case 32: return launch_prefill<32>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table, max_pages, n_heads, n_kv, scale, stream);
         case 64: return launch_prefill<64>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table, max_pages, n_heads, n_kv, scale, stream);

@@ -159,10 +159,35 @@ __global__ void silu_mul_kernel(const T* __restrict__ gu, T* __restrict__ h, int
     }
 }
 
+// bf16 rows in the interleaved layout: a thread takes one block of 8 features with three 16-byte accesses.
+__global__ void silu_mul_bf16_blocks_kernel(const bf16* __restrict__ gu, bf16* __restrict__ h, int inter) {
+    const int blk = blockIdx.y * blockDim.x + threadIdx.x;          // block of 8 features
+    if (blk * 8 >= inter) return;
+    const uint4* src = reinterpret_cast<const uint4*>(gu + (int64_t)blockIdx.x * 2 * inter + (int64_t)blk * 16);
+    const uint4 gv = src[0], uv = src[1];
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&gv);
+    const __nv_bfloat162* u2 = reinterpret_cast<const __nv_bfloat162*>(&uv);
+    uint4 ov;
+    __nv_bfloat162* o2 = reinterpret_cast<__nv_bfloat162*>(&ov);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 g = __bfloat1622float2(g2[i]), u = __bfloat1622float2(u2[i]);
+        const float a = g.x * (1.0f / (1.0f + expf(-g.x))) * u.x;
+        const float b = g.y * (1.0f / (1.0f + expf(-g.y))) * u.y;
+        o2[i] = __floats2bfloat162_rn(a, b);
+    }
+    *reinterpret_cast<uint4*>(h + (int64_t)blockIdx.x * inter + (int64_t)blk * 8) = ov;
+}
+
 CPM_API int cpm_silu_mul(const void* gu, void* h, int n_tokens, int inter, int interleave, int dtype,
                          cudaStream_t stream) {
     if (n_tokens <= 0) return CPM_OK;
     if (interleave != 0 && (interleave != 8 || inter % 8 != 0)) return CPM_BAD_ARGUMENT;
+    if (dtype == CPM_BF16 && interleave == 8) {
+        dim3 grid(n_tokens, (inter / 8 + 255) / 256);
+        silu_mul_bf16_blocks_kernel<<<grid, 256, 0, stream>>>((const bf16*)gu, (bf16*)h, inter);
+        return launch_status();
+    }
     dim3 grid(n_tokens, (inter + 511) / 512);
     if (grid.y > 65535) return CPM_BAD_ARGUMENT;
     if (dtype == CPM_BF16) silu_mul_kernel<bf16><<<grid, 256, 0, stream>>>((const bf16*)gu, (bf16*)h, inter, interleave);

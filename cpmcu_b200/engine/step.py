@@ -16,6 +16,7 @@ import torch
 
 from ..cache import Cache
 from ..models.model import Model
+from ..ops.ops import PREFILL_TILE_ROWS
 from ..parts.base import StepContext
 
 
@@ -148,9 +149,9 @@ class Stepper:
             q_lens.append(count)
             slots.append(s.slot)
         n_tok, n_seq = len(ids), len(slots)
-        # 64-token query tiles of the prefill attention kernel: (sequence, first token of the tile)
-        tile_seq = [j for j, n in enumerate(q_lens) for _ in range(0, n, 64)]
-        tile_row = [r for n in q_lens for r in range(0, n, 64)]
+        # query tiles of the prefill attention kernel: (sequence, first token of the tile)
+        tile_seq = [j for j, n in enumerate(q_lens) for _ in range(0, n, PREFILL_TILE_ROWS)]
+        tile_row = [r for n in q_lens for r in range(0, n, PREFILL_TILE_ROWS)]
         packed = torch.tensor(ids + positions + token_seq + cu_q + kv_lens + slots + want_rows + tile_seq + tile_row,
                               dtype=torch.int32)
         dev = packed.to(self.ops.device)

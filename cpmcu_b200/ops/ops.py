@@ -23,6 +23,7 @@ from .library import check
 F32, BF16 = 0, 1
 PAGE_TOKENS = 64
 FAST_HEAD_DIMS = (32, 64, 96, 128)       # head sizes the tensor-core attention kernels are built for
+PREFILL_TILE_ROWS = 128                  # query tokens per block of the prefill attention kernel
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -295,7 +296,7 @@ class Ops:
                           cu_q: torch.Tensor, kv_len: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
                           n_kv: int, scale: float) -> torch.Tensor:
         """q [tokens, heads, d] packed by sequence -> [tokens, heads*d]; tiles = (tile_seq, tile_row, count)
-        lists the 64-token query tiles."""
+        lists the query tiles of PREFILL_TILE_ROWS tokens."""
         self._act(q, "q")
         n, n_heads, d = q.shape
         tile_seq, tile_row, n_tiles = tiles

@@ -256,8 +256,9 @@ def test_tensor_core_attention_against_generic_and_plain(n_heads, n_kv, d):
                       for o, n in zip([0, 1, 65, 130, 260], lens)])
     cu = torch.tensor([0, 1, 65, 130, 260, 593], dtype=torch.int32).cuda()
     kv_len = torch.tensor(lens, dtype=torch.int32).cuda()
-    tile_seq = [j for j, n in enumerate(lens) for _ in range(0, n, 64)]
-    tile_row = [r for n in lens for r in range(0, n, 64)]
+    from cpmcu_b200.ops.ops import PREFILL_TILE_ROWS as TR
+    tile_seq = [j for j, n in enumerate(lens) for _ in range(0, n, TR)]
+    tile_row = [r for n in lens for r in range(0, n, TR)]
     tiles = (torch.tensor(tile_seq, dtype=torch.int32).cuda(), torch.tensor(tile_row, dtype=torch.int32).cuda(), len(tile_seq))
     got = ops.prefill_attention(q, lane.k, lane.v, tiles, cu, kv_len, sl, lane.page_table, n_kv, scale)
     assert _err(got, want) < KTOL["bfloat16"]
