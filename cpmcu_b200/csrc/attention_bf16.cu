@@ -301,6 +301,8 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
     const int kvh = blockIdx.y / m_tiles, mt = blockIdx.y % m_tiles, b = blockIdx.z;
     const int group = n_heads / n_kv;
     const int j = lane & 3, g = lane >> 2;
+    pdl_launch_dependents();
+    pdl_wait();
     const int len = kv_len[b];
     const int n_pages = (len + kPageTokens - 1) / kPageTokens;
     const int per = (n_pages + n_splits - 1) / n_splits;
@@ -387,6 +389,8 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
 __global__ void combine_splits_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                       bf16* __restrict__ out, int n_heads, int n_kv, int m_tiles, int n_splits,
                                       int D) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int h = blockIdx.x, b = blockIdx.y;
     const int group = n_heads / n_kv;
     const int kvh = h / group, local = h % group;
@@ -432,11 +436,11 @@ static int launch_decode(const void* q, const void* k_cache, const void* v_cache
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    kern<<<grid, kDecodeWarps * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
-        kv_len, slots, page_table, max_pages, part_o, part_ml, n_heads, n_kv, m_tiles, n_splits,
-        scale * 1.4426950408889634f);
-    combine_splits_kernel<<<dim3(n_heads, n_seqs), D >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, (bf16*)out, n_heads,
-                                                                               n_kv, m_tiles, n_splits, D);
+    cpm_launch(kern, grid, kDecodeWarps * 32, smem, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
+               kv_len, slots, page_table, max_pages, part_o, part_ml, n_heads, n_kv, m_tiles, n_splits,
+               scale * 1.4426950408889634f);
+    cpm_launch(combine_splits_kernel, dim3(n_heads, n_seqs), D >= 128 ? 128 : 64, 0, stream, (const float*)part_o,
+               (const float*)part_ml, (bf16*)out, n_heads, n_kv, m_tiles, n_splits, (int)D);
     return launch_status();
 }
 

@@ -110,6 +110,34 @@ __device__ __forceinline__ int64_t value_offset(int page, int kv_head, int dim, 
     return (((int64_t)page * n_kv + kv_head) * d + dim) * (int64_t)kPageTokens + in_page;
 }
 
+// Programmatic dependent launch.  A kernel launched with the attribute may start while the
+// kernel before it in the stream is still running; it must not touch anything that kernel
+// (or an earlier one) writes before pdl_wait() returns, which is when the preceding kernel
+// has completed and its writes are visible.  pdl_launch_dependents() lets the kernel after
+// this one begin its own launch.  Both are no-ops for a kernel launched the ordinary way.
+// What a kernel does before pdl_wait() here is only ever to prefetch weights, which no
+// kernel writes.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+extern int g_cpm_pdl;      // 1: kernels of the decode chain are launched with the attribute (default 0)
+
+template <typename... KArgs, typename... Args>
+static inline void cpm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                              Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = g_cpm_pdl ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 static inline int launch_status() {
     cudaError_t e = cudaPeekAtLastError();
     return e == cudaSuccess ? CPM_OK : (int)e;

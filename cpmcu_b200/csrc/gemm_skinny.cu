@@ -19,6 +19,10 @@
 
 enum : int { EPI_BF16 = 0, EPI_F32 = 1, EPI_SILU = 2 };
 
+// 128-byte lines of each weight row a block asks L2 for before it waits for the kernel ahead of it.
+static int g_skinny_prefetch_lines = 0;
+CPM_API void cpm_set_skinny_prefetch_lines(int n) { g_skinny_prefetch_lines = n < 0 ? 0 : n; }
+
 __device__ __forceinline__ void mma_16816_s(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                             uint32_t b0, uint32_t b1) {
     asm(
@@ -38,12 +42,25 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
 template <int NT, int EPI, int kSkinnyWarps>
 __global__ void __launch_bounds__(kSkinnyWarps * 32)
 skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, void* __restrict__ out, int M, int N, int K,
-                   float alpha) {
+                   float alpha, int prefetch_lines) {
     constexpr int MT = NT * 8;                          // token columns
     __shared__ float red[kSkinnyWarps][16][MT + 1];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = lane >> 2, j = lane & 3;
     const int n0 = blockIdx.x * 16;
+    // Before the kernel ahead of this one in the stream has finished, this block already asks for its
+    // 16 weight rows to be brought into L2: weights are never written, and the tail of one product then
+    // overlaps with the start of the next.
+    pdl_launch_dependents();
+    {
+        const int lines = min(prefetch_lines, (K * 2 + 127) / 128);      // 128-byte lines per row
+        for (int i = threadIdx.x; i < 16 * lines; i += kSkinnyWarps * 32) {
+            const int r = i / lines, l = i - r * lines;
+            const char* p = reinterpret_cast<const char*>(W + (int64_t)min(n0 + r, N - 1) * K) + l * 128;
+            asm volatile("prefetch.global.L2 [%0];" :: "l"(p));
+        }
+    }
+    pdl_wait();
     // Rows beyond N and token columns beyond M read a valid row instead and their results are never
     // stored: rows of the product are independent, so no load needs a predicate.
     const bf16* w0 = W + (int64_t)min(n0 + g, N - 1) * K + 8 * j;
@@ -111,9 +128,9 @@ static int launch_skinny_epi(const void* W, const void* X, void* out, int M, int
     // Few row tiles (a narrow output): more warps per tile, so that enough loads are in flight.
     const unsigned blocks = (unsigned)((N + 15) / 16);
     if (blocks < 148 * 4)
-        skinny_gemm_kernel<NT, EPI, 16><<<blocks, 512, 0, stream>>>((const bf16*)W, (const bf16*)X, out, M, N, K, alpha);
+        cpm_launch(skinny_gemm_kernel<NT, EPI, 16>, blocks, 512, 0, stream, (const bf16*)W, (const bf16*)X, out, M, N, K, alpha, g_skinny_prefetch_lines);
     else
-        skinny_gemm_kernel<NT, EPI, 8><<<blocks, 256, 0, stream>>>((const bf16*)W, (const bf16*)X, out, M, N, K, alpha);
+        cpm_launch(skinny_gemm_kernel<NT, EPI, 8>, blocks, 256, 0, stream, (const bf16*)W, (const bf16*)X, out, M, N, K, alpha, g_skinny_prefetch_lines);
     return launch_status();
 }
 

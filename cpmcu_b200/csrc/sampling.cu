@@ -39,6 +39,8 @@ sample_rows_kernel(const float* __restrict__ logits, int64_t ld, int vocab, int*
                    uint64_t seed, const int* __restrict__ seq_key, const int* __restrict__ step_key) {
     __shared__ ArgMax am_scratch[33];
     __shared__ float f_scratch[33];
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float thread_sums[kSampleThreads];
     __shared__ int chosen;
     const int row = blockIdx.x;
@@ -129,7 +131,7 @@ CPM_API int cpm_sample_rows(const float* logits, int64_t ld, int n_rows, int voc
     if (n_rows <= 0) return CPM_OK;
     if (vocab <= 0) return CPM_BAD_ARGUMENT;
     if (temperature && (!seq_key || !step_key)) return CPM_BAD_ARGUMENT;
-    sample_rows_kernel<<<n_rows, kSampleThreads, 0, stream>>>(logits, ld, vocab, out, temperature, top_p, seed,
-                                                             seq_key, step_key);
+    cpm_launch(sample_rows_kernel, n_rows, kSampleThreads, 0, stream, logits, ld, vocab, out, temperature, top_p, seed,
+               seq_key, step_key);
     return launch_status();
 }

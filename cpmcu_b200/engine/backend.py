@@ -53,6 +53,9 @@ class EngineBackend:
         if changed:
             self.runner.start([self.slots[p] for p in live], last_tokens, keys, steps_done, sampling)
             self.h2d_bytes += 4 * 7 * len(live)
+        else:
+            self.runner.feed(last_tokens)               # the step's inputs: host tokens, pinned, every step
+            self.h2d_bytes += 4 * len(live)
         self.runner.step()
         self.d2h_bytes += 4 * len(live)
         return self.runner.read_tokens()

@@ -68,6 +68,7 @@ class DecodeRunner:
         self.current: Optional[_Bucket] = None
         self.slots: List[int] = []
         self.pinned = None
+        self.pinned_in = None
 
     # ---- one step's work on the device ----
     def _body(self, b: _Bucket, captured: bool) -> None:
@@ -139,6 +140,15 @@ class DecodeRunner:
         b.temperature.copy_(fl[0]); b.top_p.copy_(fl[1])
         self.current = b
         self.slots = list(slots)
+
+    def feed(self, tokens: Sequence[int]) -> None:
+        """The next step's input tokens from the host (pinned memory, asynchronous copy).  Without
+        this call a step feeds on the tokens the last step sampled, which are already on the device."""
+        n = len(tokens)
+        if self.pinned_in is None or self.pinned_in.numel() < self.current.size:
+            self.pinned_in = torch.empty(max(64, self.current.size), dtype=torch.int32).pin_memory()
+        self.pinned_in[:n] = torch.tensor(list(tokens), dtype=torch.int32)
+        self.current.ids[:n].copy_(self.pinned_in[:n], non_blocking=True)
 
     def step(self) -> torch.Tensor:
         """Runs one decode step of the current batch; returns the sampled tokens (device,

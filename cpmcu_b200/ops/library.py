@@ -9,6 +9,7 @@ torch's headers.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from ctypes import c_float, c_int, c_int64, c_uint64, c_void_p
 from typing import Optional
@@ -67,6 +68,14 @@ def load() -> ctypes.CDLL:
             lib = ctypes.CDLL(path)
         except OSError as e:
             raise KernelLibraryError(f"the CUDA kernel library {path} could not be loaded: {e}") from None
+        lib.cpm_set_pdl.argtypes = [c_int]
+        lib.cpm_set_pdl.restype = None
+        if os.environ.get("CPMCU_PDL", "0") == "1":
+            lib.cpm_set_pdl(1)
+        lib.cpm_set_skinny_prefetch_lines.argtypes = [c_int]
+        lib.cpm_set_skinny_prefetch_lines.restype = None
+        if os.environ.get("CPMCU_SKINNY_PREFETCH"):
+            lib.cpm_set_skinny_prefetch_lines(int(os.environ["CPMCU_SKINNY_PREFETCH"]))
         lib.cpm_decode_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int, c_int]
         lib.cpm_decode_attention_scratch_floats.restype = c_int64
         for name, argtypes in _SIGNATURES.items():
