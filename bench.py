@@ -243,6 +243,80 @@ def time_e2e(cfg, model, steps: int, batch: int):
     }
 
 
+def kernel_bench(name: str, batch: int, ctx: int, rows: int, n: int, k: int, reps: int) -> int:
+    """One kernel alone at the benchmark's shapes, timed inside a CUDA graph with rotating
+    buffers larger than L2 (also the target of the ncu captures under profiles/)."""
+    import math
+    import torch
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.ops.ops import PREFILL_TILE_ROWS, Ops
+    from cpmcu_b200.parts.base import CacheNeeds
+
+    ops, dev = Ops(torch.bfloat16, "cuda:0"), "cuda:0"
+    heads, kv, d = MODEL["num_attention_heads"], MODEL["num_key_value_heads"], MODEL["head_dim"]
+
+    def timed(fn, n_inner):
+        fn(0)
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for i in range(n_inner):
+                fn(i)
+        g.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(reps):
+            g.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / (reps * n_inner)
+
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    out = {"kernel": name}
+    if name == "skinny_gemm":
+        copies = max(2, int(400e6 // (n * k * 2)) + 1)
+        ws = [torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+        x = torch.randn(rows, k, device=dev, dtype=torch.bfloat16)
+        us = timed(lambda i: ops.linear(x, ws[i % copies]), copies * 2)
+        out.update(rows=rows, n=n, k=k, us=us, gbs=n * k * 2 / 1e3 / us)
+    elif name == "decode_attention":
+        lanes = max(2, int(400e6 // (batch * ctx * kv * d * 4)) + 1)
+        cache = Cache([CacheNeeds(kv_heads=kv, head_dim=d)] * lanes, max_tokens=batch * (ctx + 64), dtype=torch.bfloat16,
+                      device=dev, n_slots=batch + 1, max_seq_tokens=ctx + 64)
+        slots = cache.open_sequences(batch)
+        for s_ in slots:
+            cache.reserve(s_, ctx)
+        cache.sync()
+        for lane in cache.lanes:
+            lane.k.normal_()
+            lane.v.normal_()
+        q = torch.randn(batch, heads, d, device=dev, dtype=torch.bfloat16)
+        kv_len, sl = i32([ctx] * batch), i32(slots)
+        us = timed(lambda i: ops.decode_attention(q, cache.lane(i % lanes).k, cache.lane(i % lanes).v, kv_len, sl,
+                                                  cache.lane(0).page_table, kv, 1 / math.sqrt(d)), lanes * 2)
+        out.update(batch=batch, ctx=ctx, us=us, gbs=batch * ctx * kv * d * 4 / 1e3 / us)
+    elif name == "prefill_attention":
+        cache = Cache([CacheNeeds(kv_heads=kv, head_dim=d)], max_tokens=ctx + 64, dtype=torch.bfloat16, device=dev, n_slots=2)
+        slot = cache.open_sequence()
+        cache.reserve(slot, ctx)
+        cache.sync()
+        cache.lane(0).k.normal_()
+        cache.lane(0).v.normal_()
+        q = torch.randn(ctx, heads, d, device=dev, dtype=torch.bfloat16)
+        n_tiles = (ctx + PREFILL_TILE_ROWS - 1) // PREFILL_TILE_ROWS
+        tiles = (i32([0] * n_tiles), i32(list(range(0, ctx, PREFILL_TILE_ROWS))), n_tiles)
+        cu, kv_len, sl = i32([0, ctx]), i32([ctx]), i32([slot])
+        us = timed(lambda i: ops.prefill_attention(q, cache.lane(0).k, cache.lane(0).v, tiles, cu, kv_len, sl,
+                                                   cache.lane(0).page_table, kv, 1 / math.sqrt(d)), 4)
+        out.update(tokens=ctx, us=us, tflops=4 * heads * d * ctx * ctx / 2 / us / 1e6)
+    else:
+        print(f"unknown kernel '{name}'; known: skinny_gemm, decode_attention, prefill_attention")
+        return 2
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -252,12 +326,20 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="layers built (the full model has 32)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the e2e run")
+    ap.add_argument("--kernel", default=None, help="time one kernel alone: skinny_gemm, decode_attention, prefill_attention")
+    ap.add_argument("--ctx", type=int, default=CONTEXT, help="--kernel: cached tokens per sequence (or prompt tokens)")
+    ap.add_argument("--rows", type=int, default=8, help="--kernel skinny_gemm: rows of the activation")
+    ap.add_argument("--n", type=int, default=4096, help="--kernel skinny_gemm: output features")
+    ap.add_argument("--k", type=int, default=4096, help="--kernel skinny_gemm: input features")
+    ap.add_argument("--reps", type=int, default=5, help="--kernel: graph replays that are timed")
     a = ap.parse_args()
     if a.impl == "reference":
         return reference_arm()
     if a.gpus != 1:
         print("bench.py: this library runs on one GPU; --gpus must be 1")
         return 2
+    if a.kernel:
+        return kernel_bench(a.kernel, a.batch, a.ctx, a.rows, a.n, a.k, a.reps)
     a.warmup = max(3, a.warmup)
     import torch
     from cpmcu_b200.ops import library
