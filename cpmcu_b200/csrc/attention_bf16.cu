@@ -461,6 +461,146 @@ CPM_API int cpm_decode_attention_bf16(const void* q, const void* k_cache, const 
 }
 
 // ---------------------------------------------------------------------------
+// attention over listed key blocks (block-sparse), one block of warps per (token, kv head)
+// ---------------------------------------------------------------------------
+// The 16 rows are the query heads of the token that share the kv head, as in decode; the key
+// pages are those the token's block list names (selected by cpm_select_blocks), or all pages up
+// to the token when the list says "dense" (first entry -2).  Serves block-sparse prefill and
+// decode when the sparse block is a page (64 tokens).  The reference's counterpart is its
+// block-mask flash kernel with 16-head tiles (src/flash_attn/src/flash_fwd_kernel.h:580-1170,
+// src/flash_attn/src/flash_blockmask.h:5-109).
+template <int D>
+__global__ void __launch_bounds__(kDecodeWarps * 32)
+listed_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                        bf16* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ token_seq,
+                        const int* __restrict__ slots, const int* __restrict__ page_table, int max_pages,
+                        const int* __restrict__ block_list, int list_cap, int n_heads, int n_kv, int m_tiles,
+                        float scale_log2) {
+    using S = DecodeSmem<D>;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ float sm_m[kDecodeWarps][16], sm_l[kDecodeWarps][16];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x;
+    const int kvh = blockIdx.y / m_tiles, mt = blockIdx.y % m_tiles;
+    const int group = n_heads / n_kv;
+    const int j = lane & 3, g = lane >> 2;
+    const int p = positions[t];
+    const int* pages = page_table + (int64_t)slots[token_seq[t]] * max_pages;
+    const int* list = block_list + ((int64_t)t * n_kv + kvh) * list_cap;
+    const bool dense = list[0] == -2;
+    int n_items = 0;
+    if (dense) n_items = p / kPageTokens + 1;
+    else while (n_items < list_cap && list[n_items] >= 0) ++n_items;
+    const uint32_t my_stages = (uint32_t)__cvta_generic_to_shared(smem_raw) + warp * kDecodeStages * S::kStageBytes;
+    const int64_t page_elems = (int64_t)n_kv * kPageTokens * D;
+
+    auto block_of = [&](int k) { const int i = warp + k * kDecodeWarps; return dense ? i : list[i]; };
+    auto issue = [&](int k) {
+        if (warp + k * kDecodeWarps < n_items) {
+            const int64_t base = (int64_t)pages[block_of(k)] * page_elems + (int64_t)kvh * kPageTokens * D;
+            copy_page_async<D>(my_stages + (k % kDecodeStages) * S::kStageBytes, k_cache + base, v_cache + base, lane);
+        }
+        cp_async_commit();
+    };
+    issue(0);
+    issue(1);
+
+    TileState<D> st;
+    st.init();
+    uint4 qf[2][D / 32];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int local = min(mt * 16 + g + 8 * r, group - 1);
+        const bf16* qrow = q + ((int64_t)t * n_heads + kvh * group + local) * D + 8 * j;
+#pragma unroll
+        for (int w = 0; w < D / 32; ++w) qf[r][w] = __ldg(reinterpret_cast<const uint4*>(qrow + 32 * w));
+    }
+    for (int k = 0; warp + k * kDecodeWarps < n_items; ++k) {
+        cp_async_wait<kDecodeStages - 1>();
+        __syncwarp();
+        attend_page_smem<D>(st, qf, my_stages + (k % kDecodeStages) * S::kStageBytes, block_of(k) * kPageTokens, p, p,
+                            scale_log2, lane);
+        __syncwarp();
+        issue(k + kDecodeStages);
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
+        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+    }
+    __syncthreads();
+    float* sm_o = reinterpret_cast<float*>(smem_raw);
+    constexpr int kLd = D + 4;
+#pragma unroll
+    for (int nt = 0; nt < D / 8; ++nt) {
+        *reinterpret_cast<float2*>(&sm_o[(warp * 16 + g) * kLd + 8 * nt + 2 * j]) = make_float2(st.o[nt][0], st.o[nt][1]);
+        *reinterpret_cast<float2*>(&sm_o[(warp * 16 + g + 8) * kLd + 8 * nt + 2 * j]) = make_float2(st.o[nt][2], st.o[nt][3]);
+    }
+    if (j == 0) {
+        sm_m[warp][g] = st.m[0];
+        sm_l[warp][g] = st.l[0];
+        sm_m[warp][g + 8] = st.m[1];
+        sm_l[warp][g + 8] = st.l[1];
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < 16 * D; i += kDecodeWarps * 32) {
+        const int row = i / D, c = i - row * D;
+        const int local = mt * 16 + row;
+        if (local >= group) continue;
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kDecodeWarps; ++w) mx = fmaxf(mx, sm_m[w][row]);
+        const float use = mx == -INFINITY ? 0.f : mx;
+        float o = 0.f, l = 0.f;
+#pragma unroll
+        for (int w = 0; w < kDecodeWarps; ++w) {
+            const float f = exp2f(sm_m[w][row] - use);
+            o += sm_o[(w * 16 + row) * kLd + c] * f;
+            l += sm_l[w][row] * f;
+        }
+        out[((int64_t)t * n_heads + kvh * group + local) * D + c] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+    }
+}
+
+template <int D>
+static int launch_listed(const void* q, const void* k_cache, const void* v_cache, void* out, const int* positions,
+                         const int* token_seq, const int* slots, const int* page_table, int max_pages,
+                         const int* block_list, int list_cap, int n_tokens, int n_heads, int n_kv, float scale,
+                         cudaStream_t stream) {
+    const int m_tiles = (n_heads / n_kv + 15) / 16;
+    auto kern = listed_attention_kernel<D>;
+    constexpr int smem = DecodeSmem<D>::kTotal;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    kern<<<dim3(n_tokens, n_kv * m_tiles), kDecodeWarps * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_cache,
+        (const bf16*)v_cache, (bf16*)out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_heads,
+        n_kv, m_tiles, scale * 1.4426950408889634f);
+    return launch_status();
+}
+
+// q, out [tokens, heads, d] bf16; block_list int32 [tokens, kv_heads, list_cap] of 64-token blocks.
+CPM_API int cpm_listed_attention_bf16(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                      const int* positions, const int* token_seq, const int* slots,
+                                      const int* page_table, int max_pages, const int* block_list, int list_cap,
+                                      int n_tokens, int n_heads, int n_kv, int d, float scale, cudaStream_t stream) {
+    if (n_tokens <= 0) return CPM_OK;
+    if (n_kv <= 0 || n_heads % n_kv || !block_list || list_cap < 1 || n_kv * ((n_heads / n_kv + 15) / 16) > 65535)
+        return CPM_BAD_ARGUMENT;
+    switch (d) {
+        case 32: return launch_listed<32>(q, k_cache, v_cache, out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_tokens, n_heads, n_kv, scale, stream);
+        case 64: return launch_listed<64>(q, k_cache, v_cache, out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_tokens, n_heads, n_kv, scale, stream);
+        case 96: return launch_listed<96>(q, k_cache, v_cache, out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_tokens, n_heads, n_kv, scale, stream);
+        case 128: return launch_listed<128>(q, k_cache, v_cache, out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_tokens, n_heads, n_kv, scale, stream);
+        default: return CPM_BAD_ARGUMENT;
+    }
+}
+
+// ---------------------------------------------------------------------------
 // prefill
 // ---------------------------------------------------------------------------
 // A block of 8 warps takes 128 consecutive query tokens of one sequence and one head, 16 per

@@ -235,6 +235,10 @@ class Ops:
             if tiles is not None:
                 return self.prefill_attention(q, lane.k, lane.v, tiles, ctx.cu_q, ctx.kv_len_dev, ctx.slot_dev,
                                               lane.page_table, n_kv, scale)
+        if (self.code == BF16 and block_list is not None and block_size == PAGE_TOKENS and not window
+                and d in FAST_HEAD_DIMS):
+            return self.listed_attention(q, lane.k, lane.v, ctx.positions, ctx.token_seq, ctx.slot_dev,
+                                         lane.page_table, block_list, n_kv, scale)
         return self.attention_generic(q, lane.k, lane.v, ctx.positions, ctx.token_seq, ctx.slot_dev,
                                       lane.page_table, n_kv, scale, window, block_list, block_size)
 
@@ -305,6 +309,21 @@ class Ops:
                                                   _ptr(tile_row), n_tiles, _ptr(cu_q), _ptr(kv_len), _ptr(slots),
                                                   _ptr(page_table), page_table.shape[1], n_heads, n_kv, d,
                                                   float(scale), _stream()), f"prefill attention (head_dim {d})")
+        return out
+
+
+    def listed_attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, positions: torch.Tensor,
+                         token_seq: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
+                         block_list: torch.Tensor, n_kv: int, scale: float) -> torch.Tensor:
+        """Attention of every token over the 64-token key blocks its list names (block-sparse)."""
+        self._act(q, "q")
+        self._i32(block_list, "block list")
+        n, n_heads, d = q.shape
+        out = self.empty(n, n_heads * d)
+        check(self.lib.cpm_listed_attention_bf16(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(positions),
+                                                 _ptr(token_seq), _ptr(slots), _ptr(page_table), page_table.shape[1],
+                                                 _ptr(block_list), block_list.shape[-1], n, n_heads, n_kv, d,
+                                                 float(scale), _stream()), f"block-list attention (head_dim {d})")
         return out
 
 

@@ -50,3 +50,17 @@ def tiny_c() -> dict:
         "head_dim": 48, "intermediate_size": 100, "vocab_size": 777,
         "max_position_embeddings": 512, "rms_norm_eps": 3e-6, "tie_word_embeddings": False,
     }
+
+
+def tiny_d() -> dict:
+    """Sparse attention with blocks of a whole cache page (64 tokens), as the 8B configuration has:
+    the block-list kernel of the bf16 path takes these."""
+    return {
+        "architectures": ["MiniCPMForCausalLM"], "model_type": "minicpm",
+        "num_hidden_layers": 2, "hidden_size": 96, "num_attention_heads": 6, "num_key_value_heads": 2,
+        "head_dim": 32, "intermediate_size": 160, "vocab_size": 640,
+        "rope_theta": 10000.0, "max_position_embeddings": 1024, "rms_norm_eps": 1e-6,
+        "scale_emb": 4, "dim_model_base": 48, "scale_depth": 1.2, "tie_word_embeddings": True,
+        "sparse_config": {"kernel_size": 32, "kernel_stride": 16, "block_size": 64, "init_blocks": 1, "topk": 3,
+                          "window_size": 64, "dense_len": 100},
+    }

@@ -128,7 +128,8 @@ def compress_keys(k: Tensor, kernel: int, stride: int) -> Tensor:
     return torch.stack([k[stride * i: stride * i + kernel].mean(dim=0) for i in range(n)])
 
 
-def select_blocks(q_p: Tensor, ck: Tensor, p: int, scale: float, sparse: dict) -> List[List[int]]:
+def select_blocks(q_p: Tensor, ck: Tensor, p: int, scale: float, sparse: dict,
+                  margins: Optional[List[float]] = None) -> List[List[int]]:
     """Key blocks a query at position p attends to, per kv head (InfLLM-v2).
 
     Reference pieces: stage-1 score = softmax of q against the compressed keys, summed
@@ -144,7 +145,10 @@ def select_blocks(q_p: Tensor, ck: Tensor, p: int, scale: float, sparse: dict) -
     always attended (the reference's local window is narrower in attention than in the
     selection, src/flash_attn/src/flash_blockmask.h:30, which leaves a gap no query sees);
     ``topk`` counts the forced leading blocks; the compress_lse normaliser is not built.
-    q_p: [heads, d]; ck: [n_compressed, kv, d] of the whole sequence.
+    q_p: [heads, d]; ck: [n_compressed, kv, d] of the whole sequence.  If ``margins`` is given, the
+    relative gap between the last block score that was chosen and the first that was not is appended
+    for every kv head (infinity when nothing was left out): a small gap means that rounding may
+    choose otherwise.
     """
     ks, st, bs = sparse["kernel_size"], sparse["kernel_stride"], sparse["block_size"]
     init_blocks, topk = sparse.get("init_blocks", 1), sparse["topk"]
@@ -172,12 +176,19 @@ def select_blocks(q_p: Tensor, ck: Tensor, p: int, scale: float, sparse: dict) -
         candidates.sort()
         room = max(0, topk - init_blocks)
         chosen.update(k for _, k in candidates[:room])
+        if margins is not None:
+            if 0 < room < len(candidates):
+                last_in, first_out = -candidates[room - 1][0], -candidates[room][0]
+                margins.append((last_in - first_out) / max(abs(last_in), 1e-30))
+            else:
+                margins.append(float("inf"))
         chosen.update(k for k in range(max(0, last_choice + 1), qb + 1))
         result.append(sorted(chosen))
     return result
 
 
-def sparse_attention(q: Tensor, k: Tensor, v: Tensor, scale: float, sparse: dict) -> Tensor:
+def sparse_attention(q: Tensor, k: Tensor, v: Tensor, scale: float, sparse: dict,
+                     margins: Optional[List[float]] = None) -> Tensor:
     """Per query: dense if it sees at most dense_len keys (the reference's sparse_switch,
     src/model/minicpm4/minicpm4_attn.cuh:116), else attention over the keys of its
     selected blocks that are at or before it (src/flash_attn/src/flash_blockmask.h:15-93)."""
@@ -191,7 +202,10 @@ def sparse_attention(q: Tensor, k: Tensor, v: Tensor, scale: float, sparse: dict
     for p in range(S):
         if p + 1 <= sparse.get("dense_len", 0):
             continue
-        blocks = select_blocks(q[p], ck, p, scale, sparse)
+        here: Optional[List[float]] = [] if margins is not None else None
+        blocks = select_blocks(q[p], ck, p, scale, sparse, here)
+        if margins is not None:
+            margins[p] = min(margins[p], min(here))
         for h in range(nh):
             keys = [j for b in blocks[h // group] for j in range(b * bs, min((b + 1) * bs, p + 1))]
             idx = torch.tensor(keys, dtype=torch.long)
@@ -201,7 +215,8 @@ def sparse_attention(q: Tensor, k: Tensor, v: Tensor, scale: float, sparse: dict
 
 
 def attention_layer(y: Tensor, w: Dict[str, Tensor], prefix: str, cfg: dict, positions: Tensor,
-                    shared_kv: Optional[Tuple[Tensor, Tensor]] = None) -> Tuple[Tensor, Tuple[Tensor, Tensor]]:
+                    shared_kv: Optional[Tuple[Tensor, Tensor]] = None,
+                    margins: Optional[List[float]] = None) -> Tuple[Tensor, Tuple[Tensor, Tensor]]:
     """src/model/attn.cuh:185-229: q, k, v projections without bias, rotary on q and k (keys
     are kept rotated), attention, output projection.  Returns (output, (k, v))."""
     nh, nkv, d = cfg["num_attention_heads"], cfg.get("num_key_value_heads") or cfg["num_attention_heads"], head_dim(cfg)
@@ -217,7 +232,7 @@ def attention_layer(y: Tensor, w: Dict[str, Tensor], prefix: str, cfg: dict, pos
         k, v = shared_kv
     scale = 1.0 / math.sqrt(d)
     sparse = cfg.get("sparse_config")
-    o = sparse_attention(q, k, v, scale, sparse) if sparse else dense_attention(q, k, v, scale)
+    o = sparse_attention(q, k, v, scale, sparse, margins) if sparse else dense_attention(q, k, v, scale)
     return o.reshape(S, nh * d) @ w[prefix + "o_proj.weight"].T, (k, v)
 
 
@@ -241,13 +256,16 @@ def lm_head(y: Tensor, w: Dict[str, Tensor], cfg: dict, scale: float) -> Tensor:
 # ---------------------------------------------------------------------------
 
 def forward(cfg: dict, weights: Dict[str, Tensor], ids: Sequence[int], dtype: torch.dtype = torch.float32,
-            schedule: Optional[Sequence[Tuple[int, int, bool]]] = None) -> Tensor:
+            schedule: Optional[Sequence[Tuple[int, int, bool]]] = None,
+            margins: Optional[List[float]] = None) -> Tensor:
     """Logits [S, vocab] at every position of one sequence.
 
     Order of operations as src/model/model.cuh:145-153 and src/model/layer.cuh:47-67:
     x = embed * scale_emb; per layer x += rs * attn(norm(x)); x += rs * ffn(norm(x));
     logits = head(norm(x)).  ``schedule`` lists runs (layer, cache lane, writes): a run
     that does not write uses the keys and values an earlier run stored in that lane.
+    ``margins``, if given, must be a list of len(ids) infinities; it receives, per position, the
+    smallest block-choice gap over all layers and kv heads (see select_blocks).
     """
     w = {k: v.to(dtype) for k, v in weights.items()}
     se, rs, sl = scales(cfg)
@@ -261,7 +279,7 @@ def forward(cfg: dict, weights: Dict[str, Tensor], ids: Sequence[int], dtype: to
     for layer, lane, writes in schedule:
         p = f"model.layers.{layer}."
         y = rms_norm(x, w[p + "input_layernorm.weight"], eps)
-        a, kv = attention_layer(y, w, p + "self_attn.", cfg, positions, None if writes else lanes[lane])
+        a, kv = attention_layer(y, w, p + "self_attn.", cfg, positions, None if writes else lanes[lane], margins)
         if writes:
             lanes[lane] = kv
         x = x + rs * a

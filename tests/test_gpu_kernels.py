@@ -314,3 +314,38 @@ def test_skinny_gemm(M, N, K):
     # a row's result does not depend on the other rows
     one = ops.linear(a[:1].contiguous().cuda(), w.cuda(), out_f32=True, alpha=0.125)
     assert torch.equal(one[0], got32[0])
+
+
+@pytest.mark.parametrize("n_heads,n_kv,d", [(4, 1, 32), (6, 2, 64), (32, 2, 128), (20, 1, 64)])
+def test_block_list_attention_against_generic(n_heads, n_kv, d):
+    """The bf16 block-list kernel against the generic kernel given the same lists: random subsets of
+    pages that always hold the token's own page, and tokens whose list says "dense"."""
+    ops = _ops("bfloat16")
+    lens = [300, 64, 700]
+    cache, slots = _paged_setup(ops, lens, n_kv, d, 0, "bfloat16")
+    lane = cache.lane(0)
+    g = torch.Generator().manual_seed(12)
+    T = sum(lens)
+    qkv = torch.randn(T, (n_heads + 2 * n_kv) * d, generator=g).bfloat16()
+    positions = torch.cat([torch.arange(n) for n in lens]).int()
+    token_seq = torch.cat([torch.full((n,), i) for i, n in enumerate(lens)]).int().cuda()
+    sl = torch.tensor(slots, dtype=torch.int32).cuda()
+    q = ops.rope_store(qkv.cuda(), n_heads, n_kv, d, positions.cuda(), token_seq, sl, lane.page_table, lane.k, lane.v,
+                       None, 1.0, 0)
+    cap = 7
+    lists = torch.full((T, n_kv, cap), -1, dtype=torch.int32)
+    for t in range(T):
+        own = int(positions[t]) // 64
+        for h in range(n_kv):
+            if t % 5 == 0:
+                lists[t, h, 0] = -2
+                continue
+            others = torch.randperm(own, generator=g)[:min(own, 4)].tolist() if own > 0 else []
+            blocks = sorted(set(others + [own]))
+            lists[t, h, :len(blocks)] = torch.tensor(blocks, dtype=torch.int32)
+    lists = lists.cuda()
+    scale = 1 / math.sqrt(d)
+    want = ops.attention_generic(q, lane.k, lane.v, positions.cuda(), token_seq, sl, lane.page_table, n_kv, scale,
+                                 block_list=lists, block_size=64)
+    got = ops.listed_attention(q, lane.k, lane.v, positions.cuda(), token_seq, sl, lane.page_table, lists, n_kv, scale)
+    assert _err(got, want) < KTOL["bfloat16"]

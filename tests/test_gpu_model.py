@@ -123,3 +123,38 @@ def test_unequal_batches_reuse_slots(model_folders, name, make, seed, dtype):
             assert err < helpers.TOL[dtype], (name, dtype, b, i, err)
         st.cache.check_consistent()
     assert st.cache.tokens_held() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_page_sized_sparse_blocks(model_folders, dtype):
+    """Tiny D: prompts far beyond dense_len, whole, then decoded, in a batch of unequal lengths.
+    The weights are drawn wider than usual (std 0.08) so that dropping the wrong block shows."""
+    from cpmcu_b200.engine import SequenceStep
+
+    folder = model_folders("tiny_d", configs.tiny_d(), 3, dtype, std=0.08)
+    cfg, st = _stepper(folder, dtype, max_tokens=64 * 24)
+    seqs = [helpers.random_ids(cfg.vocab_size, n, 50 + n) for n in (420, 130, 64)]
+    slots = st.open(3)
+    cut = [400, 101, 10]
+    out = st.step([SequenceStep(s, ids[:c], list(range(c))) for s, ids, c in zip(slots, seqs, cut)])
+    got = [[out[sum(cut[:i]):sum(cut[:i + 1])]] for i in range(3)]
+    t = 0
+    while any(c + t < len(ids) for ids, c in zip(seqs, cut)):
+        live = [i for i in range(3) if cut[i] + t < len(seqs[i])]
+        o = st.step([SequenceStep(slots[i], [seqs[i][cut[i] + t]], [0]) for i in live])
+        for r, i in enumerate(live):
+            got[i].append(o[r:r + 1])
+        t += 1
+    for i, ids in enumerate(seqs):
+        want = helpers.plain_logits(folder, ids)
+        g = torch.cat(got[i])
+        # float32 must agree everywhere; bfloat16 where the block choice is not a near tie
+        firm = torch.ones(len(ids), dtype=torch.bool) if dtype == "float32" else helpers.firm_positions(folder, ids)
+        assert int(firm.sum()) >= 0.75 * len(ids)
+        err = helpers.rel_err(g[firm], want[firm])
+        assert err < helpers.TOL[dtype], (dtype, i, err)
+    # the sparse rule matters for this model: dense attention gives other logits for the long sequence
+    cfgd, w = helpers.read_folder(folder)
+    from tests.plain import minicpm4_plain as plain
+    dense = plain.forward(dict(cfgd, sparse_config=None), w, seqs[0])
+    assert helpers.rel_err(dense[300:], helpers.plain_logits(folder, seqs[0])[300:]) > 5 * helpers.TOL[dtype]
