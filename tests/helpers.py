@@ -13,7 +13,7 @@ from tests.plain import minicpm4_plain as plain
 # Largest allowed |engine - plain| relative to the largest |plain logit| of the compared rows.
 # float32: both sides are fp32 with different summation orders.  bfloat16: weights are the
 # same bf16 values on both sides; activations and the cache are rounded to bf16 in the engine.
-TOL = {"float32": 2e-5, "bfloat16": 2.5e-2}
+TOL = {"float32": 5e-6, "bfloat16": 1.5e-2}
 
 
 def make_folder(cfgd: dict, out_dir: str, seed: int, dtype: str, std: float = 0.02, norm_mean: float = 1.0) -> str:
@@ -76,3 +76,26 @@ def firm_positions(folder: str, ids: Sequence[int], min_gap: float = 0.002) -> t
     margins = [float("inf")] * len(ids)
     plain.forward(cfg, w, list(ids), margins=margins)
     return torch.tensor([m >= min_gap for m in margins])
+
+
+_firm_cache: Dict[tuple, torch.Tensor] = {}
+
+
+def check_rows(got: torch.Tensor, folder: str, ids: Sequence[int], positions: Sequence[int], dtype: str, label=None) -> float:
+    """Asserts that ``got`` (one row of logits per entry of ``positions``) agrees with the plain
+    implementation's logits of the sequence ``ids`` at these positions.  In bfloat16, for a folder
+    with sparse attention, positions whose block choice is a near tie are left out (firm_positions)."""
+    want = plain_logits(folder, ids)
+    positions = list(positions)
+    keep = torch.ones(len(positions), dtype=torch.bool)
+    cfg, _ = read_folder(folder) if dtype == "bfloat16" else ({}, None)
+    if cfg.get("sparse_config"):
+        key = (folder, tuple(ids))
+        if key not in _firm_cache:
+            _firm_cache[key] = firm_positions(folder, ids)
+        keep = _firm_cache[key][torch.tensor(positions)]
+        if not bool(keep.any()):
+            return 0.0                                          # nothing but near ties among these rows
+    err = rel_err(got[keep], want[torch.tensor(positions)][keep])
+    assert err < TOL[dtype], (label, dtype, err)
+    return err
