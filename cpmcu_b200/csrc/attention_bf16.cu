@@ -475,7 +475,9 @@ listed_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
                         bf16* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ token_seq,
                         const int* __restrict__ slots, const int* __restrict__ page_table, int max_pages,
                         const int* __restrict__ block_list, int list_cap, int n_heads, int n_kv, int m_tiles,
-                        float scale_log2) {
+                        float scale_log2, float* __restrict__ part_o, float* __restrict__ part_ml, int n_splits) {
+    // With n_splits > 1 (few tokens: decode) the listed blocks of a token are shared out over
+    // gridDim.z blocks of threads, which write unnormalised partial results for combine_splits_kernel.
     using S = DecodeSmem<D>;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ float sm_m[kDecodeWarps][16], sm_l[kDecodeWarps][16];
@@ -491,12 +493,15 @@ listed_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
     int n_items = 0;
     if (dense) n_items = p / kPageTokens + 1;
     else while (n_items < list_cap && list[n_items] >= 0) ++n_items;
+    const int per_split = (n_items + n_splits - 1) / n_splits;
+    const int item0 = blockIdx.z * per_split;
+    n_items = min(n_items, item0 + per_split);
     const uint32_t my_stages = (uint32_t)__cvta_generic_to_shared(smem_raw) + warp * kDecodeStages * S::kStageBytes;
     const int64_t page_elems = (int64_t)n_kv * kPageTokens * D;
 
-    auto block_of = [&](int k) { const int i = warp + k * kDecodeWarps; return dense ? i : list[i]; };
+    auto block_of = [&](int k) { const int i = item0 + warp + k * kDecodeWarps; return dense ? i : list[i]; };
     auto issue = [&](int k) {
-        if (warp + k * kDecodeWarps < n_items) {
+        if (item0 + warp + k * kDecodeWarps < n_items) {
             const int64_t base = (int64_t)pages[block_of(k)] * page_elems + (int64_t)kvh * kPageTokens * D;
             copy_page_async<D>(my_stages + (k % kDecodeStages) * S::kStageBytes, k_cache + base, v_cache + base, lane);
         }
@@ -515,7 +520,7 @@ listed_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
 #pragma unroll
         for (int w = 0; w < D / 32; ++w) qf[r][w] = __ldg(reinterpret_cast<const uint4*>(qrow + 32 * w));
     }
-    for (int k = 0; warp + k * kDecodeWarps < n_items; ++k) {
+    for (int k = 0; item0 + warp + k * kDecodeWarps < n_items; ++k) {
         cp_async_wait<kDecodeStages - 1>();
         __syncwarp();
         attend_page_smem<D>(st, qf, my_stages + (k % kDecodeStages) * S::kStageBytes, block_of(k) * kPageTokens, p, p,
@@ -559,7 +564,16 @@ listed_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
             o += sm_o[(w * 16 + row) * kLd + c] * f;
             l += sm_l[w][row] * f;
         }
-        out[((int64_t)t * n_heads + kvh * group + local) * D + c] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+        if (n_splits == 1) {
+            out[((int64_t)t * n_heads + kvh * group + local) * D + c] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+        } else {
+            const int64_t unit = (((int64_t)t * n_kv + kvh) * m_tiles + mt) * n_splits + blockIdx.z;
+            part_o[(unit * 16 + row) * D + c] = o;
+            if (c == 0) {
+                part_ml[unit * 32 + 2 * row] = mx;
+                part_ml[unit * 32 + 2 * row + 1] = l;
+            }
+        }
     }
 }
 
@@ -567,8 +581,10 @@ template <int D>
 static int launch_listed(const void* q, const void* k_cache, const void* v_cache, void* out, const int* positions,
                          const int* token_seq, const int* slots, const int* page_table, int max_pages,
                          const int* block_list, int list_cap, int n_tokens, int n_heads, int n_kv, float scale,
-                         cudaStream_t stream) {
+                         float* scratch, int n_splits, cudaStream_t stream) {
     const int m_tiles = (n_heads / n_kv + 15) / 16;
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (int64_t)n_tokens * n_kv * m_tiles * n_splits * 16 * D : nullptr;
     auto kern = listed_attention_kernel<D>;
     constexpr int smem = DecodeSmem<D>::kTotal;
     static bool configured = false;
@@ -577,9 +593,12 @@ static int launch_listed(const void* q, const void* k_cache, const void* v_cache
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    kern<<<dim3(n_tokens, n_kv * m_tiles), kDecodeWarps * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_cache,
+    kern<<<dim3(n_tokens, n_kv * m_tiles, n_splits), kDecodeWarps * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_cache,
         (const bf16*)v_cache, (bf16*)out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_heads,
-        n_kv, m_tiles, scale * 1.4426950408889634f);
+        n_kv, m_tiles, scale * 1.4426950408889634f, part_o, part_ml, n_splits);
+    if (n_splits > 1)
+        combine_splits_kernel<<<dim3(n_heads, n_tokens), D >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, (bf16*)out, n_heads,
+                                                                                    n_kv, m_tiles, n_splits, D);
     return launch_status();
 }
 
@@ -587,15 +606,18 @@ static int launch_listed(const void* q, const void* k_cache, const void* v_cache
 CPM_API int cpm_listed_attention_bf16(const void* q, const void* k_cache, const void* v_cache, void* out,
                                       const int* positions, const int* token_seq, const int* slots,
                                       const int* page_table, int max_pages, const int* block_list, int list_cap,
-                                      int n_tokens, int n_heads, int n_kv, int d, float scale, cudaStream_t stream) {
+                                      int n_tokens, int n_heads, int n_kv, int d, float scale, float* scratch,
+                                      int n_splits, cudaStream_t stream) {
+    // scratch: cpm_decode_attention_scratch_floats(n_tokens, ...) floats when n_splits > 1, else unused
     if (n_tokens <= 0) return CPM_OK;
-    if (n_kv <= 0 || n_heads % n_kv || !block_list || list_cap < 1 || n_kv * ((n_heads / n_kv + 15) / 16) > 65535)
+    if (n_kv <= 0 || n_heads % n_kv || !block_list || list_cap < 1 || n_kv * ((n_heads / n_kv + 15) / 16) > 65535 ||
+        n_splits < 1 || n_splits > 65535 || (n_splits > 1 && (!scratch || n_tokens > 65535)))
         return CPM_BAD_ARGUMENT;
     switch (d) {
-        case 32: return launch_listed<32>(q, k_cache, v_cache, out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_tokens, n_heads, n_kv, scale, stream);
-        case 64: return launch_listed<64>(q, k_cache, v_cache, out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_tokens, n_heads, n_kv, scale, stream);
-        case 96: return launch_listed<96>(q, k_cache, v_cache, out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_tokens, n_heads, n_kv, scale, stream);
-        case 128: return launch_listed<128>(q, k_cache, v_cache, out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_tokens, n_heads, n_kv, scale, stream);
+        case 32: return launch_listed<32>(q, k_cache, v_cache, out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_tokens, n_heads, n_kv, scale, scratch, n_splits, stream);
+        case 64: return launch_listed<64>(q, k_cache, v_cache, out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_tokens, n_heads, n_kv, scale, scratch, n_splits, stream);
+        case 96: return launch_listed<96>(q, k_cache, v_cache, out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_tokens, n_heads, n_kv, scale, scratch, n_splits, stream);
+        case 128: return launch_listed<128>(q, k_cache, v_cache, out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_tokens, n_heads, n_kv, scale, scratch, n_splits, stream);
         default: return CPM_BAD_ARGUMENT;
     }
 }

@@ -59,23 +59,266 @@ CPM_API int cpm_pool_keys(const void* k_cache, float* pooled, const int* positio
     return launch_status();
 }
 
+// From the scores of the visible pooled keys to the list of blocks: block score = max over the
+// pooled keys that overlap the block; the leading blocks and the blocks of the local window are
+// always taken; of the others the topk - init_blocks best are chosen (ties to the lower index) by
+// sorting (score, index) keys in shared memory.  score: [n_vis]; flags: [>= candidates] scratch;
+// keys: [power of two >= candidates] scratch.  All threads of the block call this.
+__device__ void finish_selection(const float* __restrict__ score, float* __restrict__ flags,
+                                 unsigned long long* __restrict__ keys, int* __restrict__ list, int list_cap, int p,
+                                 int n_vis, int kernel, int stride, int block_size, int init_blocks, int topk,
+                                 int local_blocks) {
+    const int tid = threadIdx.x, n_threads = blockDim.x;
+    const int qb = p / block_size;
+    const int last_choice = qb - local_blocks;
+    const int per_block = block_size / stride;
+    const int reach_back = kernel / stride - 1;
+    const int n_cand = max(0, last_choice + 1 - init_blocks);
+    int n_sort = 1;
+    while (n_sort < n_cand) n_sort <<= 1;
+    // key: score bits made monotonic, then the inverted index, so that a descending sort puts the
+    // higher score first and among equal scores the lower index
+    for (int i = tid; i < n_sort; i += n_threads) {
+        unsigned long long key = 0ull;                       // below every real key
+        if (i < n_cand) {
+            const int k = init_blocks + i;
+            const int lo = max(0, k * per_block - reach_back), hi = min(n_vis, (k + 1) * per_block);
+            float b = -INFINITY;
+            for (int e = lo; e < hi; ++e) b = fmaxf(b, score[e]);
+            if (b > -INFINITY) {
+                const unsigned bits = __float_as_uint(b);
+                const unsigned mono = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
+                key = ((unsigned long long)mono << 32) | (unsigned)(0x7fffffff - i);
+            }
+            flags[i] = 0.f;
+        }
+        keys[i] = key;
+    }
+    __syncthreads();
+    for (int k = 2; k <= n_sort; k <<= 1) {
+        for (int j = k >> 1; j > 0; j >>= 1) {
+            for (int i = tid; i < n_sort; i += n_threads) {
+                const int partner = i ^ j;
+                if (partner > i) {
+                    const unsigned long long a = keys[i], b = keys[partner];
+                    const bool descending = (i & k) == 0;
+                    if (descending ? a < b : a > b) {
+                        keys[i] = b;
+                        keys[partner] = a;
+                    }
+                }
+            }
+            __syncthreads();
+        }
+    }
+    const int room = min(max(0, topk - init_blocks), n_cand);
+    for (int r = tid; r < room; r += n_threads) {
+        const unsigned long long key = keys[r];
+        if (key != 0ull) flags[0x7fffffff - (int)(unsigned)(key & 0xffffffffull)] = 1.f;
+    }
+    __syncthreads();
+    if (tid == 0) {
+        int n = 0;
+        const int n_init = min(init_blocks, qb + 1);
+        for (int k = 0; k < n_init && n < list_cap - 1; ++k) list[n++] = k;
+        for (int i = 0; i < n_cand && n < list_cap - 1; ++i)
+            if (flags[i] != 0.f) list[n++] = init_blocks + i;
+        for (int k = max(n_init, last_choice + 1); k <= qb && n < list_cap - 1; ++k) list[n++] = k;
+        list[n] = -1;
+    }
+}
+
 // One block per (token, kv head): writes the ascending list of key blocks the query
 // attends to, ended by -1; a first entry of -2 says "dense" (the query sees at most
 // dense_len keys).
+//
+// Scores: a warp takes one pooled key at a time, its lanes spread over head_dim (coalesced
+// 16-byte loads of the fp32 row), and forms the dot products with all query heads of the
+// group; the softmax over the visible pooled keys needs each head's maximum and sum first,
+// so the pooled keys are walked twice (statistics, then probabilities).
+constexpr int kSelectThreads = 256;
+constexpr int kSelectWarps = kSelectThreads / 32;
+constexpr int kMaxGroup = 32;              // query heads per kv head this kernel takes
+
+__device__ __forceinline__ const float* pooled_row(const float* __restrict__ pooled, const int* __restrict__ pages,
+                                                   int entry, int stride, int per_page, int n_kv, int kvh, int d) {
+    const int tok = entry * stride;
+    return pooled + (((int64_t)pages[tok / kPageTokens] * n_kv + kvh) * per_page + (tok % kPageTokens) / stride) * d;
+}
+
+// Dot products of one pooled key with every head of the group; every lane returns all of them
+// through ``dots`` (dots[h] valid for h < group).
+__device__ __forceinline__ void group_dots(const float* __restrict__ row, const float* __restrict__ qs, int group, int d,
+                                           int lane, float scale, float* dots /* [kMaxGroup] in registers */) {
+#pragma unroll
+    for (int h = 0; h < kMaxGroup; ++h) dots[h] = 0.f;
+    for (int c0 = 0; c0 < d; c0 += 128) {
+        const int c = c0 + 4 * lane;
+        if (c < d) {
+            const float4 kv = __ldg(reinterpret_cast<const float4*>(row + c));
+#pragma unroll
+            for (int h = 0; h < kMaxGroup; ++h) {
+                if (h < group) {
+                    const float4 qv = *reinterpret_cast<const float4*>(qs + h * d + c);
+                    dots[h] = fmaf(qv.x, kv.x, fmaf(qv.y, kv.y, fmaf(qv.z, kv.z, fmaf(qv.w, kv.w, dots[h]))));
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int h = 0; h < kMaxGroup; ++h)
+        if (h < group) dots[h] = warp_sum(dots[h]) * scale;
+}
+
 template <typename T>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(kSelectThreads)
 select_blocks_kernel(const T* __restrict__ q, const float* __restrict__ pooled, const int* __restrict__ positions,
                      const int* __restrict__ token_seq, const int* __restrict__ slots,
                      const int* __restrict__ page_table, int max_pages, int* __restrict__ lists, int list_cap,
                      int n_heads, int n_kv, int d, float scale, int kernel, int stride, int block_size,
                      int init_blocks, int topk, int local_blocks, int dense_len, int max_entries) {
-    extern __shared__ float sm[];
-    float* score = sm;                       // [max_entries]
-    float* tmp = sm + max_entries;           // [max_entries]: logits of one head, then block scores
-    float* qs = tmp + max_entries;           // [d]
-    float* red = qs + d;                     // [33]
-    ArgMax* am = (ArgMax*)(red + 34);        // [33]
+    extern __shared__ __align__(16) float sm[];
+    float* score = sm;                                   // [max_entries]
+    float* tmp = sm + max_entries;                       // [max_entries]: chosen flags of the blocks
+    float* qs = tmp + max_entries;                       // [group][d]
+    const int group = n_heads / n_kv;
+    float* stat_m = qs + group * d;                      // [warps][kMaxGroup]
+    float* stat_l = stat_m + kSelectWarps * kMaxGroup;   // [warps][kMaxGroup]
+    unsigned long long* keys = (unsigned long long*)(stat_l + kSelectWarps * kMaxGroup);   // [sort_size]
     const int t = blockIdx.x, kvh = blockIdx.y, tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31;
+    int* list = lists + ((int64_t)t * n_kv + kvh) * list_cap;
+    const int p = positions[t];
+    if (p + 1 <= dense_len) {
+        if (tid == 0) list[0] = -2;
+        return;
+    }
+    const int* pages = page_table + (int64_t)slots[token_seq[t]] * max_pages;
+    const int per_page = kPageTokens / stride;
+    int n_vis = p + 1 >= kernel ? (p + 1 - kernel) / stride + 1 : 0;
+    n_vis = min(n_vis, max_entries);
+
+    for (int i = tid; i < group * d; i += kSelectThreads)
+        qs[i] = to_f32(q[((int64_t)t * n_heads + kvh * group) * d + i]);
+    __syncthreads();
+
+    // first walk: maximum and sum of exponentials per head (lane h keeps head h's)
+    float dots[kMaxGroup];
+    float my_m = -INFINITY, my_l = 0.f;
+    for (int i = warp; i < n_vis; i += kSelectWarps) {
+        group_dots(pooled_row(pooled, pages, i, stride, per_page, n_kv, kvh, d), qs, group, d, lane, scale, dots);
+        float mine = -INFINITY;
+#pragma unroll
+        for (int h = 0; h < kMaxGroup; ++h)
+            if (h == lane) mine = dots[h];
+        if (lane < group) {
+            const float m_new = fmaxf(my_m, mine);
+            my_l = my_l * expf(my_m - m_new) + expf(mine - m_new);
+            my_m = m_new;
+        }
+    }
+    stat_m[warp * kMaxGroup + lane] = my_m;
+    stat_l[warp * kMaxGroup + lane] = my_l;
+    __syncthreads();
+    float head_m = -INFINITY, head_inv = 0.f;           // of head ``lane``
+    if (lane < group) {
+        for (int w = 0; w < kSelectWarps; ++w) head_m = fmaxf(head_m, stat_m[w * kMaxGroup + lane]);
+        float l = 0.f;
+        for (int w = 0; w < kSelectWarps; ++w) {
+            const float m = stat_m[w * kMaxGroup + lane];
+            if (m != -INFINITY) l += stat_l[w * kMaxGroup + lane] * expf(m - head_m);
+        }
+        head_inv = l > 0.f ? 1.f / l : 0.f;
+    }
+    // second walk: probabilities, summed over the heads of the group
+    for (int i = warp; i < n_vis; i += kSelectWarps) {
+        group_dots(pooled_row(pooled, pages, i, stride, per_page, n_kv, kvh, d), qs, group, d, lane, scale, dots);
+        float mine = 0.f;
+#pragma unroll
+        for (int h = 0; h < kMaxGroup; ++h)
+            if (h == lane) mine = dots[h];
+        const float prob = lane < group ? expf(mine - head_m) * head_inv : 0.f;
+        const float total = warp_sum(prob);
+        if (lane == 0) score[i] = total;
+    }
+    __syncthreads();
+
+    finish_selection(score, tmp, keys, list, list_cap, p, n_vis, kernel, stride, block_size, init_blocks, topk, local_blocks);
+}
+
+// ---------------------------------------------------------------------------
+// The same selection with the scores on the tensor cores (bf16 queries, groups of up to 16 heads).
+// The 16 rows of an mma tile are the query heads of the group, the 8 columns pooled keys.  A pooled
+// key is fp32; it enters as the sum of two bf16 numbers (its rounding and the rounding of the
+// remainder), so that the product with the bf16 query keeps about 16 bits beyond bf16.
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void mma_16816_sel(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                              uint32_t b0, uint32_t b1) {
+    asm("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+        : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+        : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+__device__ __forceinline__ void split_pair(float x, float y, uint32_t& hi, uint32_t& lo) {
+    const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
+    const float2 hf = __bfloat1622float2(h);
+    const __nv_bfloat162 l = __floats2bfloat162_rn(x - hf.x, y - hf.y);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+
+
+// This thread's part of a pooled key: 8 consecutive dims of every 32-dim window.
+template <int D>
+struct RawKey {
+    float4 v[D / 32][2];
+    __device__ __forceinline__ void load(const float* __restrict__ row, int j) {
+#pragma unroll
+        for (int w = 0; w < D / 32; ++w) {
+            v[w][0] = __ldg(reinterpret_cast<const float4*>(row + 32 * w + 8 * j));
+            v[w][1] = __ldg(reinterpret_cast<const float4*>(row + 32 * w + 8 * j + 4));
+        }
+    }
+};
+
+// scaled scores (log2 domain) of the warp's tile: rows g, g+8; columns = pooled keys tile*8 + 2j, 2j+1
+template <int D>
+__device__ __forceinline__ void score_tile(float (&sc)[4], const uint4 (&qf)[2][D / 32], const RawKey<D>& raw,
+                                           float scale_log2) {
+    sc[0] = sc[1] = sc[2] = sc[3] = 0.f;
+#pragma unroll
+    for (int w = 0; w < D / 32; ++w) {
+        const float4 lo4 = raw.v[w][0], hi4 = raw.v[w][1];
+        uint32_t h01, l01, h23, l23, h45, l45, h67, l67;
+        split_pair(lo4.x, lo4.y, h01, l01);
+        split_pair(lo4.z, lo4.w, h23, l23);
+        split_pair(hi4.x, hi4.y, h45, l45);
+        split_pair(hi4.z, hi4.w, h67, l67);
+        mma_16816_sel(sc, qf[0][w].x, qf[1][w].x, qf[0][w].y, qf[1][w].y, h01, h23);
+        mma_16816_sel(sc, qf[0][w].x, qf[1][w].x, qf[0][w].y, qf[1][w].y, l01, l23);
+        mma_16816_sel(sc, qf[0][w].z, qf[1][w].z, qf[0][w].w, qf[1][w].w, h45, h67);
+        mma_16816_sel(sc, qf[0][w].z, qf[1][w].z, qf[0][w].w, qf[1][w].w, l45, l67);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) sc[i] *= scale_log2;
+}
+
+// kSelMmaWarps: 4 when there are many (token, kv head) pairs (prefill), 16 when there are few (decode).
+template <int D, int kSelMmaWarps>
+__global__ void __launch_bounds__(kSelMmaWarps * 32)
+select_blocks_mma_kernel(const bf16* __restrict__ q, const float* __restrict__ pooled, const int* __restrict__ positions,
+                         const int* __restrict__ token_seq, const int* __restrict__ slots,
+                         const int* __restrict__ page_table, int max_pages, int* __restrict__ lists, int list_cap,
+                         int n_heads, int n_kv, float scale_log2, int kernel, int stride, int block_size,
+                         int init_blocks, int topk, int local_blocks, int dense_len, int max_entries) {
+    extern __shared__ __align__(16) float sm[];
+    float* score = sm;                                        // [max_entries]
+    float* flags = sm + max_entries;                          // [max_entries]
+    float* stat_m = flags + max_entries;                      // [warps][16]
+    float* stat_l = stat_m + kSelMmaWarps * 16;               // [warps][16]
+    unsigned long long* keys = (unsigned long long*)(stat_l + kSelMmaWarps * 16);
+    const int t = blockIdx.x, kvh = blockIdx.y, tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, j = lane & 3;
     int* list = lists + ((int64_t)t * n_kv + kvh) * list_cap;
     const int p = positions[t];
     if (p + 1 <= dense_len) {
@@ -87,71 +330,120 @@ select_blocks_kernel(const T* __restrict__ q, const float* __restrict__ pooled, 
     const int per_page = kPageTokens / stride;
     int n_vis = p + 1 >= kernel ? (p + 1 - kernel) / stride + 1 : 0;
     n_vis = min(n_vis, max_entries);
+    const int n_tiles = (n_vis + 7) / 8;
 
-    for (int i = tid; i < n_vis; i += blockDim.x) score[i] = 0.f;
-    for (int g = 0; g < group; ++g) {
-        const T* qrow = q + ((int64_t)t * n_heads + kvh * group + g) * d;
-        __syncthreads();
-        for (int c = tid; c < d; c += blockDim.x) qs[c] = to_f32(qrow[c]);
-        __syncthreads();
+    uint4 qf[2][D / 32];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const bool ok = g + 8 * r < group;
+        const bf16* qrow = q + ((int64_t)t * n_heads + kvh * group + (ok ? g + 8 * r : 0)) * D + 8 * j;
+#pragma unroll
+        for (int w = 0; w < D / 32; ++w) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(qrow + 32 * w));
+            qf[r][w] = ok ? v : make_uint4(0, 0, 0, 0);
+        }
+    }
+    // first walk: maximum and sum of exponentials of every head (rows g and g + 8 of this thread)
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    // As column g of a tile this thread loads pooled key tile*8 + g; the next tile's key is asked for
+    // before the current one is worked on.
+    auto row_of = [&](int tile) {
+        return pooled_row(pooled, pages, min(tile * 8 + g, n_vis - 1), stride, per_page, n_kv, kvh, D);
+    };
+    RawKey<D> cur, nxt;
+    if (warp < n_tiles) cur.load(row_of(warp), j);
+    for (int tile = warp; tile < n_tiles; tile += kSelMmaWarps) {
+        if (tile + kSelMmaWarps < n_tiles) nxt.load(row_of(tile + kSelMmaWarps), j);
+        float sc[4];
+        score_tile<D>(sc, qf, cur, scale_log2);
+        cur = nxt;
+        const int c0 = tile * 8 + 2 * j;
+        if (c0 >= n_vis) sc[0] = sc[2] = -INFINITY;
+        if (c0 + 1 >= n_vis) sc[1] = sc[3] = -INFINITY;
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            float mx = fmaxf(sc[2 * r], sc[2 * r + 1]);
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float mn = fmaxf(m[r], mx);                       // finite: column 0 of a tile is always visible
+            l[r] = l[r] * exp2f(m[r] - mn) + exp2f(sc[2 * r] - mn) + exp2f(sc[2 * r + 1] - mn);
+            m[r] = mn;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+        if (j == 0) {
+            stat_m[warp * 16 + g + 8 * r] = m[r];
+            stat_l[warp * 16 + g + 8 * r] = l[r];
+        }
+    }
+    __syncthreads();
+    float head_m[2], head_inv[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = g + 8 * r;
         float mx = -INFINITY;
-        for (int i = tid; i < n_vis; i += blockDim.x) {
-            const int tok = i * stride;
-            const float* row = pooled + (((int64_t)pages[tok / kPageTokens] * n_kv + kvh) * per_page
-                                         + (tok % kPageTokens) / stride) * d;
-            float dot = 0.f;
-            for (int c = 0; c < d; ++c) dot = fmaf(qs[c], row[c], dot);
-            dot *= scale;
-            tmp[i] = dot;
-            mx = fmaxf(mx, dot);
+#pragma unroll
+        for (int w = 0; w < kSelMmaWarps; ++w) mx = fmaxf(mx, stat_m[w * 16 + row]);
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kSelMmaWarps; ++w) {
+            const float mw = stat_m[w * 16 + row];
+            if (mw != -INFINITY) sum += stat_l[w * 16 + row] * exp2f(mw - mx);
         }
-        // block max through the argmax reduction (only the value is used)
-        mx = block_argmax(ArgMax{mx, 0}, am).v;
-        float part = 0.f;
-        for (int i = tid; i < n_vis; i += blockDim.x) part += expf(tmp[i] - mx);
-        const float total = block_sum(part, red);
-        const float inv = total > 0.f ? 1.f / total : 0.f;
-        for (int i = tid; i < n_vis; i += blockDim.x) score[i] += expf(tmp[i] - mx) * inv;
+        head_m[r] = mx;
+        head_inv[r] = (row < group && sum > 0.f) ? 1.f / sum : 0.f;     // rows beyond the group count for nothing
+    }
+    // second walk: probabilities summed over the heads
+    if (warp < n_tiles) cur.load(row_of(warp), j);
+    for (int tile = warp; tile < n_tiles; tile += kSelMmaWarps) {
+        if (tile + kSelMmaWarps < n_tiles) nxt.load(row_of(tile + kSelMmaWarps), j);
+        float sc[4];
+        score_tile<D>(sc, qf, cur, scale_log2);
+        cur = nxt;
+        float col0 = exp2f(sc[0] - head_m[0]) * head_inv[0] + exp2f(sc[2] - head_m[1]) * head_inv[1];
+        float col1 = exp2f(sc[1] - head_m[0]) * head_inv[0] + exp2f(sc[3] - head_m[1]) * head_inv[1];
+#pragma unroll
+        for (int o = 4; o < 32; o <<= 1) {
+            col0 += __shfl_xor_sync(0xffffffffu, col0, o);
+            col1 += __shfl_xor_sync(0xffffffffu, col1, o);
+        }
+        const int c0 = tile * 8 + 2 * j;
+        if (g == 0) {
+            if (c0 < n_vis) score[c0] = col0;
+            if (c0 + 1 < n_vis) score[c0 + 1] = col1;
+        }
     }
     __syncthreads();
+    finish_selection(score, flags, keys, list, list_cap, p, n_vis, kernel, stride, block_size, init_blocks, topk, local_blocks);
+}
 
-    // block scores of the blocks that can be chosen: init_blocks <= k <= last_choice
-    const int qb = p / block_size;
-    const int last_choice = qb - local_blocks;
-    const int per_block = block_size / stride;
-    const int reach_back = kernel / stride - 1;
-    const int n_cand = max(0, last_choice + 1 - init_blocks);
-    for (int i = tid; i < n_cand; i += blockDim.x) {
-        const int k = init_blocks + i;
-        const int lo = max(0, k * per_block - reach_back), hi = min(n_vis, (k + 1) * per_block);
-        float b = -INFINITY;
-        for (int e = lo; e < hi; ++e) b = fmaxf(b, score[e]);
-        tmp[i] = b;
+static int next_pow2(int n) {
+    int v = 1;
+    while (v < n) v <<= 1;
+    return v;
+}
+
+template <int D>
+static int launch_select_mma(const void* q, const float* pooled, const int* positions, const int* token_seq,
+                             const int* slots, const int* page_table, int max_pages, int* lists, int list_cap,
+                             int n_tokens, int n_heads, int n_kv, float scale, int kernel, int stride, int block_size,
+                             int init_blocks, int topk, int local_blocks, int dense_len, int max_entries, int sort_cap,
+                             cudaStream_t stream) {
+    const size_t smem = ((size_t)2 * max_entries + 2 * 16 * 16) * sizeof(float) + (size_t)sort_cap * 8;
+    if (smem > 227 * 1024) return CPM_BAD_ARGUMENT;
+    const bool few = n_tokens * n_kv < 148;
+    auto kern = few ? select_blocks_mma_kernel<D, 16> : select_blocks_mma_kernel<D, 4>;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
     }
-    __syncthreads();
-    // repeated arg-max: the chosen candidates are marked with NaN
-    const int room = min(max(0, topk - init_blocks), n_cand);
-    for (int r = 0; r < room; ++r) {
-        ArgMax best{-INFINITY, 0x7fffffff};
-        for (int i = tid; i < n_cand; i += blockDim.x) {
-            const float v = tmp[i];
-            if (v == v) best = better(best, ArgMax{v, i});
-        }
-        best = block_argmax(best, am);
-        if (best.i == 0x7fffffff || best.v == -INFINITY) break;     // nothing left with a visible pooled key
-        if (tid == 0) tmp[best.i] = __int_as_float(0x7fc00000);
-        __syncthreads();
-    }
-    __syncthreads();
-    if (tid == 0) {
-        int n = 0;
-        const int n_init = min(init_blocks, qb + 1);
-        for (int k = 0; k < n_init && n < list_cap - 1; ++k) list[n++] = k;
-        for (int i = 0; i < n_cand && n < list_cap - 1; ++i)
-            if (tmp[i] != tmp[i]) list[n++] = init_blocks + i;
-        for (int k = max(n_init, last_choice + 1); k <= qb && n < list_cap - 1; ++k) list[n++] = k;
-        list[n] = -1;
-    }
+    kern<<<dim3(n_tokens, n_kv), few ? 512 : 128, smem, stream>>>((const bf16*)q, pooled, positions, token_seq, slots,
+        page_table, max_pages, lists, list_cap, n_heads, n_kv, scale * 1.4426950408889634f, kernel, stride, block_size,
+        init_blocks, topk, local_blocks, dense_len, max_entries);
+    return launch_status();
 }
 
 CPM_API int cpm_select_blocks(const void* q, const float* pooled, const int* positions, const int* token_seq,
@@ -161,9 +453,23 @@ CPM_API int cpm_select_blocks(const void* q, const float* pooled, const int* pos
                               int max_entries, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return CPM_OK;
     if (stride <= 0 || kernel % stride || block_size % stride || kPageTokens % stride || n_kv > 65535 ||
-        n_heads % n_kv || list_cap < topk + local_blocks + 1 || max_entries < 1)
+        n_heads % n_kv || n_heads / n_kv > kMaxGroup || d % 4 || list_cap < topk + local_blocks + 1 || max_entries < 1)
         return CPM_BAD_ARGUMENT;
-    const size_t smem = ((size_t)2 * max_entries + d + 34) * sizeof(float) + 33 * sizeof(ArgMax);
+    max_entries = (max_entries + 3) & ~3;            // keeps the arrays behind it 16-byte aligned
+    const int sort_cap = next_pow2(max_entries / (block_size / stride) + 2);
+    const int group = n_heads / n_kv;
+    if (dtype == CPM_BF16 && group <= 16) {
+#define CPM_SELECT_MMA(DD) return launch_select_mma<DD>(q, pooled, positions, token_seq, slots, page_table, max_pages, lists, \
+        list_cap, n_tokens, n_heads, n_kv, scale, kernel, stride, block_size, init_blocks, topk, local_blocks, dense_len, \
+        max_entries, sort_cap, stream)
+        if (d == 32) CPM_SELECT_MMA(32);
+        if (d == 64) CPM_SELECT_MMA(64);
+        if (d == 96) CPM_SELECT_MMA(96);
+        if (d == 128) CPM_SELECT_MMA(128);
+#undef CPM_SELECT_MMA
+    }
+    const size_t smem = ((size_t)2 * max_entries + (size_t)group * d + 2 * kSelectWarps * kMaxGroup) * sizeof(float)
+                        + (size_t)sort_cap * 8;
     if (smem > 227 * 1024) return CPM_BAD_ARGUMENT;
     dim3 grid(n_tokens, n_kv);
     cudaError_t e = cudaSuccess;
@@ -171,14 +477,14 @@ CPM_API int cpm_select_blocks(const void* q, const float* pooled, const int* pos
         auto kern = select_blocks_kernel<bf16>;
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        kern<<<grid, 256, smem, stream>>>((const bf16*)q, pooled, positions, token_seq, slots, page_table, max_pages,
+        kern<<<grid, kSelectThreads, smem, stream>>>((const bf16*)q, pooled, positions, token_seq, slots, page_table, max_pages,
             lists, list_cap, n_heads, n_kv, d, scale, kernel, stride, block_size, init_blocks, topk, local_blocks,
             dense_len, max_entries);
     } else {
         auto kern = select_blocks_kernel<float>;
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
-        kern<<<grid, 256, smem, stream>>>((const float*)q, pooled, positions, token_seq, slots, page_table, max_pages,
+        kern<<<grid, kSelectThreads, smem, stream>>>((const float*)q, pooled, positions, token_seq, slots, page_table, max_pages,
             lists, list_cap, n_heads, n_kv, d, scale, kernel, stride, block_size, init_blocks, topk, local_blocks,
             dense_len, max_entries);
     }

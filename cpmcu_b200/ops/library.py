@@ -40,7 +40,8 @@ _SIGNATURES = {
     "cpm_decode_attention_bf16": [_P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, c_float, _P],
     "cpm_prefill_attention_bf16": [_P, _P, _P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float,
                                    _P],
-    "cpm_listed_attention_bf16": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, c_float, _P],
+    "cpm_listed_attention_bf16": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, c_float, _P,
+                                  c_int, _P],
     "cpm_sample_rows": [_P, c_int64, c_int, c_int, _P, _P, _P, c_uint64, _P, _P, _P],
 }
 

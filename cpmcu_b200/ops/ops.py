@@ -320,10 +320,16 @@ class Ops:
         self._i32(block_list, "block list")
         n, n_heads, d = q.shape
         out = self.empty(n, n_heads * d)
+        n_splits = self.decode_splits(n, n_heads, n_kv)          # few tokens (decode): share a token's blocks out
+        scratch = None
+        if n_splits > 1:
+            scratch = self.empty(self.lib.cpm_decode_attention_scratch_floats(n, n_heads, n_kv, d, n_splits),
+                                 dtype=torch.float32)
         check(self.lib.cpm_listed_attention_bf16(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(positions),
                                                  _ptr(token_seq), _ptr(slots), _ptr(page_table), page_table.shape[1],
                                                  _ptr(block_list), block_list.shape[-1], n, n_heads, n_kv, d,
-                                                 float(scale), _stream()), f"block-list attention (head_dim {d})")
+                                                 float(scale), _ptr(scratch), n_splits, _stream()),
+              f"block-list attention (head_dim {d})")
         return out
 
 
