@@ -13,6 +13,7 @@ kernel of this library takes the shape.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional, Tuple
 
 import torch
@@ -48,6 +49,7 @@ class Ops:
         self.lib = library.load()
         self.element_size = 4 if dtype == torch.float32 else 2
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
+        self.use_tcgen05 = os.environ.get("CPMCU_TCGEN05", "1") != "0"
 
     # ---- checks ----
     def _act(self, t: torch.Tensor, what: str) -> torch.Tensor:
@@ -153,6 +155,22 @@ class Ops:
             c.mul_(alpha)
         return c
 
+    def linear_tcgen05(self, a: torch.Tensor, w: torch.Tensor, gated: bool = False) -> torch.Tensor:
+        """a[M,K] @ w[N,K]^T on the tcgen05 tensor cores (TMA operands, TMEM accumulator); with ``gated`` the
+        weight is a gate_up matrix interleaved in blocks of 8 and the result is silu(gate) * up, [M, N/2]."""
+        self._act(a, "linear input")
+        self._act(w, "linear weight")
+        M, K = a.shape
+        N = w.shape[0]
+        out = self.empty(M, N // 2 if gated else N)
+        check(self.lib.cpm_gemm_bf16_tcgen05(_ptr(a), _ptr(w), _ptr(out), M, N, K, 2 if gated else 0, self.sm_count,
+                                             _stream()), f"tcgen05 matrix product [{M}x{K}] x [{N}x{K}]^T")
+        return out
+
+    def tcgen05_error(self) -> int:
+        """Error code the tcgen05 product kernel recorded since the last call (0 = none); synchronises."""
+        return int(self.lib.cpm_gemm_tcgen05_error())
+
     def gated_linear(self, a: torch.Tensor, w_gate_up: torch.Tensor, interleave: int) -> torch.Tensor:
         """silu(a @ gate^T) * (a @ up^T) for a gate_up matrix [2*inter, K] laid out as ``interleave`` says."""
         M, K = a.shape
@@ -163,6 +181,10 @@ class Ops:
             check(self.lib.cpm_gemm_skinny_bf16(_ptr(w_gate_up), _ptr(a), _ptr(h), M, w_gate_up.shape[0], K, 1.0, 2,
                                                 _stream()), "gated skinny matrix product")
             return h
+        if (self.code == BF16 and interleave == 8 and self.use_tcgen05 and K % 64 == 0 and w_gate_up.shape[0] % 32 == 0
+                and a.data_ptr() % 16 == 0):
+            # many rows (prefill): the tcgen05 product applies the activation in its epilogue
+            return self.linear_tcgen05(a, w_gate_up, gated=True)
         return self.silu_mul(self.linear(a, w_gate_up), interleave)
 
     # ---- attention ----

@@ -349,3 +349,25 @@ def test_block_list_attention_against_generic(n_heads, n_kv, d):
                                  block_list=lists, block_size=64)
     got = ops.listed_attention(q, lane.k, lane.v, positions.cuda(), token_seq, sl, lane.page_table, lists, n_kv, scale)
     assert _err(got, want) < KTOL["bfloat16"]
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 8, 64), (128, 256, 64), (300, 264, 192), (129, 4608, 128), (2048, 352, 64),
+                                   (777, 1024, 4096)])
+def test_tcgen05_gemm(M, N, K):
+    """The tcgen05 / TMA / TMEM product against fp32 torch: tiles that hang over the edge in M and in N,
+    one and many K blocks, more tiles than one wave of blocks, plain and gated epilogue."""
+    ops = _ops("bfloat16")
+    g = torch.Generator().manual_seed(13)
+    a = torch.randn(M, K, generator=g).bfloat16().cuda()
+    w = (torch.randn(N, K, generator=g) * 0.05).bfloat16().cuda()
+    want = a.float() @ w.float().T
+    got = ops.linear_tcgen05(a, w)
+    assert ops.tcgen05_error() == 0
+    assert _err(got, want) < KTOL["bfloat16"]
+    if N % 32 == 0:
+        inter = N // 2
+        wi = torch.stack([w[:inter].view(inter // 8, 8, K), w[inter:].view(inter // 8, 8, K)], dim=1).reshape(N, K).contiguous()
+        gate, up = a.float() @ w[:inter].float().T, a.float() @ w[inter:].float().T
+        h = ops.linear_tcgen05(a, wi, gated=True)
+        assert ops.tcgen05_error() == 0
+        assert _err(h, gate * torch.sigmoid(gate) * up) < KTOL["bfloat16"]
