@@ -124,6 +124,7 @@ class Ops:
 
     # ---- matrix products ----
     SKINNY_MAX_ROWS = 16
+    TCGEN05_MIN_ROWS = 256       # below this the 128-row tiles of the tcgen05 product are mostly empty
 
     def _skinny_ok(self, M: int, K: int) -> bool:
         return self.code == BF16 and M <= self.SKINNY_MAX_ROWS and K % 32 == 0
@@ -181,8 +182,8 @@ class Ops:
             check(self.lib.cpm_gemm_skinny_bf16(_ptr(w_gate_up), _ptr(a), _ptr(h), M, w_gate_up.shape[0], K, 1.0, 2,
                                                 _stream()), "gated skinny matrix product")
             return h
-        if (self.code == BF16 and interleave == 8 and self.use_tcgen05 and K % 64 == 0 and w_gate_up.shape[0] % 32 == 0
-                and a.data_ptr() % 16 == 0):
+        if (self.code == BF16 and interleave == 8 and self.use_tcgen05 and M >= self.TCGEN05_MIN_ROWS and K % 64 == 0
+                and w_gate_up.shape[0] % 32 == 0 and a.data_ptr() % 16 == 0):
             # many rows (prefill): the tcgen05 product applies the activation in its epilogue
             return self.linear_tcgen05(a, w_gate_up, gated=True)
         return self.silu_mul(self.linear(a, w_gate_up), interleave)
