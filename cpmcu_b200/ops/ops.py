@@ -123,7 +123,7 @@ class Ops:
         return h
 
     # ---- matrix products ----
-    SKINNY_MAX_ROWS = 16
+    SKINNY_MAX_ROWS = int(os.environ.get("CPMCU_SKINNY_MAX_ROWS", "8"))   # most rows the weight-streaming product takes
     TCGEN05_MIN_ROWS = 256       # below this the 128-row tiles of the tcgen05 product are mostly empty
 
     def _skinny_ok(self, M: int, K: int) -> bool:
