@@ -285,7 +285,7 @@ __device__ __forceinline__ void attend_page_smem(TileState<D>& st, const uint4 (
 }
 
 template <int D>
-__global__ void __launch_bounds__(kDecodeWarps * 32)
+__global__ void __launch_bounds__(kDecodeWarps * 32, 1)
 decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                         const int* __restrict__ kv_len, const int* __restrict__ slots,
                         const int* __restrict__ page_table, int max_pages, float* __restrict__ part_o,
@@ -470,7 +470,7 @@ CPM_API int cpm_decode_attention_bf16(const void* q, const void* k_cache, const 
 // block-mask flash kernel with 16-head tiles (src/flash_attn/src/flash_fwd_kernel.h:580-1170,
 // src/flash_attn/src/flash_blockmask.h:5-109).
 template <int D>
-__global__ void __launch_bounds__(kDecodeWarps * 32)
+__global__ void __launch_bounds__(kDecodeWarps * 32, 1)
 listed_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                         bf16* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ token_seq,
                         const int* __restrict__ slots, const int* __restrict__ page_table, int max_pages,
@@ -625,16 +625,17 @@ CPM_API int cpm_listed_attention_bf16(const void* q, const void* k_cache, const 
 // ---------------------------------------------------------------------------
 // prefill
 // ---------------------------------------------------------------------------
-// A block of 8 warps takes 128 consecutive query tokens of one sequence and one head, 16 per
-// warp; tile_seq/tile_row name the sequence (index in the batch) and the first of the 128
+// A block of 4 warps takes 64 consecutive query tokens of one sequence and one head, 16 per
+// warp; tile_seq/tile_row name the sequence (index in the batch) and the first of the 64
 // tokens (offset inside this step's tokens of the sequence) of every block.  The block walks
 // over the key pages up to its last token; a page is brought into shared memory once
-// (cp.async, two pages in flight) and read by all 8 warps.
-constexpr int kPrefillWarps = 8;
+// (cp.async, two pages in flight) and read by all 4 warps.  Two blocks share an SM (measured
+// faster than one block of 8 warps or three of 4).
+constexpr int kPrefillWarps = 4;
 constexpr int kPrefillRows = kPrefillWarps * 16;
 
 template <int D>
-__global__ void __launch_bounds__(kPrefillWarps * 32)
+__global__ void __launch_bounds__(kPrefillWarps * 32, 2)
 prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                          bf16* __restrict__ out, const int* __restrict__ tile_seq, const int* __restrict__ tile_row,
                          const int* __restrict__ cu_q, const int* __restrict__ kv_len, const int* __restrict__ slots,

@@ -24,7 +24,7 @@ from .library import check
 F32, BF16 = 0, 1
 PAGE_TOKENS = 64
 FAST_HEAD_DIMS = (32, 64, 96, 128)       # head sizes the tensor-core attention kernels are built for
-PREFILL_TILE_ROWS = 128                  # query tokens per block of the prefill attention kernel
+PREFILL_TILE_ROWS = 64                   # query tokens per block of the prefill attention kernel
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
