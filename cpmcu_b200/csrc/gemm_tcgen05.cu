@@ -29,9 +29,10 @@ constexpr int kStages = 4;
 constexpr int kABytes = kBlockM * kBlockK * 2;                  // 16 KiB
 constexpr int kBBytes = kBlockN * kBlockK * 2;                  // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
-constexpr int kSmemBytes = kStages * kStageBytes + 1024;        // + room to align the stages to 1 KiB
+constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 4 * 4096;   // + room to align the stages to 1 KiB, + the epilogue warps' staging
 constexpr int kThreads = 192;                                   // 6 warps
 constexpr int kTmemCols = 512;
+constexpr int kBandTiles = 16;                                  // 2048 rows of A are shared by the blocks that run together
 constexpr uint32_t kSpinLimit = 1u << 20;                       // tries of a bounded barrier wait (each try may block for a while)
 
 enum : int { EPI_BF16 = 0, EPI_SILU = 2 };
@@ -104,6 +105,83 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t addr) {
 constexpr uint32_t kInstrDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBlockN >> 3) << 17) |
                                 ((uint32_t)(kBlockM >> 4) << 24);
 
+// Order of the tiles: bands of ``band`` row tiles, inside a band the row tile runs fastest.  The blocks that
+// run at one time then share a few row tiles of A and a few of W, whatever the number of rows, and both
+// stay in L2 (with all rows in one band, 8192 rows took A out of L2 between its uses).
+struct TileCoord { int m, n; };
+__device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_m, int tiles_n, int band) {
+    const int per_band = band * tiles_n;
+    const int b = tile / per_band, in_band = tile - b * per_band;
+    const int first = b * band, height = min(band, tiles_m - first);
+    TileCoord c;
+    c.n = in_band / height;
+    c.m = first + (in_band - c.n * height);
+    return c;
+}
+
+// One epilogue warp's 32 rows of a tile: accumulator columns from TMEM, converted (or gated) to bf16, through a
+// 4 KiB staging area of the warp in shared memory, so that every store instruction writes whole 128-byte lines
+// of four output rows.  (Stores of 16 bytes to 32 different rows, straight from the registers, cost the
+// 128 x 256 kernel 12 % of its time.)  The staging rows are 128 bytes, their 16-byte chunks XOR-swizzled
+// by the row, which keeps both the writes (one row per lane) and the reads (eight lanes per row) free of
+// bank conflicts.  taddr: TMEM address of the warp's lanes and the tile's first column.
+template <int EPI>
+__device__ __forceinline__ void epilogue_tile(bf16* __restrict__ out, uint32_t taddr, unsigned char* staging, int row0, int n0,
+                                              int M, int N, int lane) {
+    constexpr int kLoadsPerPass = EPI == EPI_SILU ? 4 : 2;          // 32 accumulator columns each; a pass is 64 outputs
+    constexpr int kPasses = kBlockN / (32 * kLoadsPerPass);
+    const int ldo = EPI == EPI_SILU ? N >> 1 : N;
+    const int oc_tile = EPI == EPI_SILU ? n0 >> 1 : n0;
+    uint4* my_row = reinterpret_cast<uint4*>(staging + lane * 128);
+#pragma unroll 1
+    for (int p = 0; p < kPasses; ++p) {
+        if (oc_tile + p * 64 >= ldo) break;
+#pragma unroll
+        for (int h = 0; h < kLoadsPerPass; ++h) {
+            uint32_t v[32];
+            tmem_load_32cols(taddr + (p * kLoadsPerPass + h) * 32, v);
+            tmem_load_wait();
+            if (EPI == EPI_SILU) {
+                // columns: 8 gate, 8 up, 8 gate, 8 up of 16 consecutive features
+                uint32_t packed[8];
+#pragma unroll
+                for (int q = 0; q < 2; ++q)
+#pragma unroll
+                    for (int i = 0; i < 8; i += 2) {
+                        const float g0 = __uint_as_float(v[16 * q + i]), g1 = __uint_as_float(v[16 * q + i + 1]);
+                        const float u0 = __uint_as_float(v[16 * q + 8 + i]), u1 = __uint_as_float(v[16 * q + 9 + i]);
+                        const float a = __fdividef(g0, 1.0f + __expf(-g0)) * u0;      // the result is rounded to bf16
+                        const float b = __fdividef(g1, 1.0f + __expf(-g1)) * u1;
+                        const __nv_bfloat162 pk = __floats2bfloat162_rn(a, b);
+                        packed[4 * q + i / 2] = *reinterpret_cast<const uint32_t*>(&pk);
+                    }
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
+                    my_row[(2 * h + c) ^ (lane & 7)] = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+            } else {
+                uint32_t packed[16];
+#pragma unroll
+                for (int i = 0; i < 32; i += 2) {
+                    const __nv_bfloat162 pk = __floats2bfloat162_rn(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
+                    packed[i / 2] = *reinterpret_cast<const uint32_t*>(&pk);
+                }
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+                    my_row[(4 * h + c) ^ (lane & 7)] = make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+            }
+        }
+        __syncwarp();
+        const int j = lane & 7, col = oc_tile + p * 64 + j * 8;
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int r = 4 * i + (lane >> 3);
+            const uint4 val = *reinterpret_cast<const uint4*>(staging + r * 128 + ((j ^ (r & 7)) << 4));
+            if (row0 + r < M && col < ldo) *reinterpret_cast<uint4*>(out + (int64_t)(row0 + r) * ldo + col) = val;
+        }
+        __syncwarp();
+    }
+}
+
 template <int EPI>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
@@ -115,6 +193,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t stages = (smem_u32(smem_raw) + 1023u) & ~1023u;        // swizzled tiles want 1 KiB alignment
+    unsigned char* staging = smem_raw + (stages - smem_u32(smem_raw)) + kStages * kStageBytes;
     const int tiles_m = (M + kBlockM - 1) / kBlockM, tiles_n = (N + kBlockN - 1) / kBlockN;
     const int n_tiles = tiles_m * tiles_n, k_blocks = K / kBlockK;
 
@@ -150,7 +229,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         if (lane == 0) {
             uint32_t it = 0;
             for (int tile = blockIdx.x; tile < n_tiles && !*(volatile int*)&abort_flag; tile += gridDim.x) {
-                const int m0 = (tile % tiles_m) * kBlockM, n0 = (tile / tiles_m) * kBlockN;
+                const TileCoord tc = tile_coord(tile, tiles_m, tiles_n, kBandTiles);
+                const int m0 = tc.m * kBlockM, n0 = tc.n * kBlockN;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % kStages;
                     if (!mbar_wait_bounded(smem_u32(&empty_bar[s]), ((it / kStages) & 1) ^ 1)) { fail(ERR_EMPTY_WAIT); break; }
@@ -197,55 +277,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         const int quarter = warp & 3;
         uint32_t local_tile = 0;
         for (int tile = blockIdx.x; tile < n_tiles && !*(volatile int*)&abort_flag; tile += gridDim.x, ++local_tile) {
-            const int m0 = (tile % tiles_m) * kBlockM, n0 = (tile / tiles_m) * kBlockN;
+            const TileCoord tc = tile_coord(tile, tiles_m, tiles_n, kBandTiles);
+            const int m0 = tc.m * kBlockM, n0 = tc.n * kBlockN;
             const int acc = local_tile & 1;
             if (!mbar_wait_bounded(smem_u32(&acc_full_bar[acc]), (local_tile >> 1) & 1)) { fail(ERR_ACC_FULL_WAIT); break; }
             tcgen05_fence_after();
-            const int row = m0 + quarter * 32 + lane;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBlockN;
-#pragma unroll 1
-            for (int c = 0; c < kBlockN / 32; ++c) {
-                uint32_t v[32];
-                tmem_load_32cols(taddr + c * 32, v);
-                tmem_load_wait();
-                const int col = n0 + c * 32;
-                if (row < M && col < N) {
-                    if (EPI == EPI_SILU) {
-                        // columns: 8 gate, 8 up, 8 gate, 8 up of features (col / 2) .. + 15
-                        uint32_t packed[8];
-#pragma unroll
-                        for (int h = 0; h < 2; ++h)
-#pragma unroll
-                            for (int i = 0; i < 8; i += 2) {
-                                const float g0 = __uint_as_float(v[16 * h + i]), g1 = __uint_as_float(v[16 * h + i + 1]);
-                                const float u0 = __uint_as_float(v[16 * h + 8 + i]), u1 = __uint_as_float(v[16 * h + 9 + i]);
-                                const float a = g0 * (1.0f / (1.0f + __expf(-g0))) * u0;
-                                const float b = g1 * (1.0f / (1.0f + __expf(-g1))) * u1;
-                                const __nv_bfloat162 p = __floats2bfloat162_rn(a, b);
-                                packed[4 * h + i / 2] = *reinterpret_cast<const uint32_t*>(&p);
-                            }
-                        uint4* dst = reinterpret_cast<uint4*>(out + (int64_t)row * (N >> 1) + (col >> 1));
-                        dst[0] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-                        dst[1] = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-                    } else {
-                        uint32_t packed[16];
-#pragma unroll
-                        for (int i = 0; i < 32; i += 2) {
-                            const __nv_bfloat162 p = __floats2bfloat162_rn(__uint_as_float(v[i]), __uint_as_float(v[i + 1]));
-                            packed[i / 2] = *reinterpret_cast<const uint32_t*>(&p);
-                        }
-                        bf16* dst_row = out + (int64_t)row * N + col;
-                        if (col + 32 <= N) {
-                            uint4* dst = reinterpret_cast<uint4*>(dst_row);
-#pragma unroll
-                            for (int i = 0; i < 4; ++i) dst[i] = make_uint4(packed[4 * i], packed[4 * i + 1], packed[4 * i + 2], packed[4 * i + 3]);
-                        } else {
-                            for (int i = 0; i < 32 && col + i < N; ++i)
-                                dst_row[i] = __ushort_as_bfloat16((unsigned short)(packed[i / 2] >> (16 * (i & 1))));
-                        }
-                    }
-                }
-            }
+            epilogue_tile<EPI>(out, taddr, staging + quarter * 4096, m0 + quarter * 32, n0, M, N, lane);
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&acc_empty_bar[acc]));
@@ -257,6 +295,169 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 1) {
         tcgen05_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)kTmemCols) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Two blocks on one 256 x 256 tile (thread-block cluster of 2, tcgen05 cta_group::2).  Each block of
+// the pair loads its own 128 rows of A and its own 128 rows of W per 64-wide K block (32 KiB a stage,
+// so 6 stages fit where the single-block kernel has 4) and holds the accumulator of its own 128
+// output rows in its TMEM; the even block of the pair issues the MMAs for both.  Hand-overs: the
+// "full" barriers live in the even block and collect the bytes of both blocks' TMA loads (the odd
+// block reaches them through their cluster address); "empty" and "accumulator full" are
+// raised in both blocks at once by tcgen05.commit with a cluster multicast; the epilogue warps of
+// both blocks arrive on the even block's "accumulator empty".  The TMA loads carry no multicast.
+// ---------------------------------------------------------------------------
+constexpr int kStages2 = 6;
+constexpr int kHalfN = kBlockN / 2;                              // W rows a block of the pair loads
+constexpr int kABytes2 = kBlockM * kBlockK * 2;                  // 16 KiB
+constexpr int kBBytes2 = kHalfN * kBlockK * 2;                   // 16 KiB
+constexpr int kStageBytes2 = kABytes2 + kBBytes2;
+constexpr int kSmemBytes2 = kStages2 * kStageBytes2 + 1024 + 4 * 4096;   // + the epilogue warps' staging
+constexpr uint32_t kInstrDesc2 = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(kBlockN >> 3) << 17) |
+                                 ((uint32_t)((2 * kBlockM) >> 4) << 24);
+
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 :: "r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 :: "r"(bar), "h"((unsigned short)3) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_f16_pair(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc,
+                                                     uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %5, %5, %5, %5, %5, %5, %5}, p;\n\t}"
+                 :: "r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" :: "r"(bar) : "memory");
+}
+// The address, valid in the whole cluster, of this block's shared-memory location in the block of that rank.
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                         bf16* __restrict__ out, int M, int N, int K) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[kStages2], empty_bar[kStages2], acc_full_bar[2], acc_empty_bar[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_rank();                                  // 0: issues the MMAs of the pair
+    const uint32_t stages = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    unsigned char* staging = smem_raw + (stages - smem_u32(smem_raw)) + kStages2 * kStageBytes2;
+    const int tiles_m = (M + 2 * kBlockM - 1) / (2 * kBlockM), tiles_n = (N + kBlockN - 1) / kBlockN;
+    const int n_tiles = tiles_m * tiles_n, k_blocks = K / kBlockK;
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kStages2; ++s) {
+            mbar_init(smem_u32(&full_bar[s]), 1);
+            mbar_init(smem_u32(&empty_bar[s]), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(smem_u32(&acc_full_bar[b]), 1);
+            mbar_init(smem_u32(&acc_empty_bar[b]), 8);                     // 4 epilogue warps of each block
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"(smem_u32(&tmem_base_slot)), "r"((uint32_t)kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync();                                                        // the partner's barriers exist before anything is sent to them
+    tcgen05_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    auto fail = [&](int code) {
+        atomicCAS(&g_error, 0, code);
+        atomicExch(&abort_flag, 1);
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (int tile = pair; tile < n_tiles && !*(volatile int*)&abort_flag; tile += n_pairs) {
+                const TileCoord tc = tile_coord(tile, tiles_m, tiles_n, kBandTiles / 2);
+                const int m0 = tc.m * 2 * kBlockM + rank * kBlockM;
+                const int n0 = tc.n * kBlockN + rank * kHalfN;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % kStages2;
+                    if (!mbar_wait_bounded(smem_u32(&empty_bar[s]), ((it / kStages2) & 1) ^ 1)) { fail(ERR_EMPTY_WAIT); break; }
+                    const uint32_t bar = map_to_rank(smem_u32(&full_bar[s]), 0);   // the even block's barrier
+                    if (rank == 0) mbar_expect_tx(smem_u32(&full_bar[s]), 2 * kStageBytes2);
+                    tma_load_2d_pair(stages + s * kStageBytes2, &map_a, bar, kb * kBlockK, m0);
+                    tma_load_2d_pair(stages + s * kStageBytes2 + kABytes2, &map_w, bar, kb * kBlockK, n0);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            uint32_t it = 0, local_tile = 0;
+            for (int tile = pair; tile < n_tiles && !*(volatile int*)&abort_flag; tile += n_pairs, ++local_tile) {
+                const int acc = local_tile & 1;
+                if (!mbar_wait_bounded(smem_u32(&acc_empty_bar[acc]), ((local_tile >> 1) & 1) ^ 1)) { fail(ERR_ACC_EMPTY_WAIT); break; }
+                tcgen05_fence_after();
+                const uint32_t tmem_d = tmem_base + acc * kBlockN;
+                bool ok = true;
+                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                    const int s = it % kStages2;
+                    if (!mbar_wait_bounded(smem_u32(&full_bar[s]), (it / kStages2) & 1)) { fail(ERR_FULL_WAIT); ok = false; break; }
+                    tcgen05_fence_after();
+                    const uint64_t da = smem_desc_sw128(stages + s * kStageBytes2);
+                    const uint64_t db = smem_desc_sw128(stages + s * kStageBytes2 + kABytes2);
+#pragma unroll
+                    for (int k = 0; k < kBlockK / 16; ++k)
+                        tcgen05_mma_f16_pair(tmem_d, da + 2 * k, db + 2 * k, kInstrDesc2, (kb | k) != 0);
+                    tcgen05_commit_pair(smem_u32(&empty_bar[s]));          // frees the stage in both blocks
+                }
+                if (!ok) break;
+                tcgen05_commit_pair(smem_u32(&acc_full_bar[acc]));         // both blocks' epilogues may start
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        uint32_t local_tile = 0;
+        for (int tile = pair; tile < n_tiles && !*(volatile int*)&abort_flag; tile += n_pairs, ++local_tile) {
+            const TileCoord tc = tile_coord(tile, tiles_m, tiles_n, kBandTiles / 2);
+            const int m0 = tc.m * 2 * kBlockM + rank * kBlockM, n0 = tc.n * kBlockN;
+            const int acc = local_tile & 1;
+            if (!mbar_wait_bounded(smem_u32(&acc_full_bar[acc]), (local_tile >> 1) & 1)) { fail(ERR_ACC_FULL_WAIT); break; }
+            tcgen05_fence_after();
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBlockN;
+            epilogue_tile<EPI>(out, taddr, staging + quarter * 4096, m0 + quarter * 32, n0, M, N, lane);
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_rank(smem_u32(&acc_empty_bar[acc]), 0));
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    cluster_sync();                                                        // nothing of the pair is in flight towards this block any more
+    if (warp == 1) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)kTmemCols) : "memory");
     }
 }
 
@@ -306,7 +507,54 @@ static int launch(const void* A, const void* W, void* out, int M, int N, int K, 
     return launch_status();
 }
 
+// The pair kernel: clusters of two blocks, n_blocks rounded down to an even number.
+template <int EPI>
+static int launch_pair(const void* A, const void* W, void* out, int M, int N, int K, int n_blocks, cudaStream_t stream) {
+    CUtensorMap map_a, map_w;
+    if (!make_map(&map_a, A, M, K, kBlockM) || !make_map(&map_w, W, N, K, kHalfN)) return CPM_BAD_ARGUMENT;
+    auto kern = gemm_tcgen05_pair_kernel<EPI>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    const int tiles = ((M + 2 * kBlockM - 1) / (2 * kBlockM)) * ((N + kBlockN - 1) / kBlockN);
+    int pairs = n_blocks / 2;
+    if (pairs < 1) return CPM_BAD_ARGUMENT;
+    if (pairs > tiles) pairs = tiles;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = kSmemBytes2;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, kern, map_a, map_w, (bf16*)out, M, N, K);
+    if (e != cudaSuccess) return (int)e;
+    return launch_status();
+}
+
 }  // namespace tc5
+
+// The same product by pairs of blocks on 256 x 256 tiles (see the pair kernel); same arguments and limits.
+CPM_API int cpm_gemm_bf16_tcgen05_pair(const void* A, const void* W, void* out, int M, int N, int K, int epilogue,
+                                       int n_blocks, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return CPM_OK;
+    if (K <= 0 || K % tc5::kBlockK != 0 || n_blocks < 2 || ((uintptr_t)A & 15) || ((uintptr_t)W & 15) || ((uintptr_t)out & 15))
+        return CPM_BAD_ARGUMENT;
+    if (epilogue == tc5::EPI_SILU) {
+        if (N % 32 != 0) return CPM_BAD_ARGUMENT;
+        return tc5::launch_pair<tc5::EPI_SILU>(A, W, out, M, N, K, n_blocks, stream);
+    }
+    if (epilogue != tc5::EPI_BF16 || N % 8 != 0) return CPM_BAD_ARGUMENT;
+    return tc5::launch_pair<tc5::EPI_BF16>(A, W, out, M, N, K, n_blocks, stream);
+}
 
 // A [M,K], W [N,K] bf16 row-major (16-byte aligned, K a multiple of 64); out [M,N] bf16, or [M,N/2] for the
 // gated epilogue (N a multiple of 32, W rows interleaved in blocks of 8).  n_blocks: blocks to launch (one per SM).

@@ -43,6 +43,7 @@ _SIGNATURES = {
     "cpm_listed_attention_bf16": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, c_float, _P,
                                   c_int, _P],
     "cpm_gemm_bf16_tcgen05": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "cpm_gemm_bf16_tcgen05_pair": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
     "cpm_sample_rows": [_P, c_int64, c_int, c_int, _P, _P, _P, c_uint64, _P, _P, _P],
 }
 

@@ -50,6 +50,7 @@ class Ops:
         self.element_size = 4 if dtype == torch.float32 else 2
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.use_tcgen05 = os.environ.get("CPMCU_TCGEN05", "1") != "0"
+        self.tcgen05_pair = os.environ.get("CPMCU_TCGEN05_PAIR", "0") == "1"      # pairs of blocks on 256-row tiles
 
     # ---- checks ----
     def _act(self, t: torch.Tensor, what: str) -> torch.Tensor:
@@ -156,16 +157,18 @@ class Ops:
             c.mul_(alpha)
         return c
 
-    def linear_tcgen05(self, a: torch.Tensor, w: torch.Tensor, gated: bool = False) -> torch.Tensor:
+    def linear_tcgen05(self, a: torch.Tensor, w: torch.Tensor, gated: bool = False, pair: bool = False) -> torch.Tensor:
         """a[M,K] @ w[N,K]^T on the tcgen05 tensor cores (TMA operands, TMEM accumulator); with ``gated`` the
-        weight is a gate_up matrix interleaved in blocks of 8 and the result is silu(gate) * up, [M, N/2]."""
+        weight is a gate_up matrix interleaved in blocks of 8 and the result is silu(gate) * up, [M, N/2].
+        ``pair``: two blocks work on one 256 x 256 tile (cta_group::2)."""
         self._act(a, "linear input")
         self._act(w, "linear weight")
         M, K = a.shape
         N = w.shape[0]
         out = self.empty(M, N // 2 if gated else N)
-        check(self.lib.cpm_gemm_bf16_tcgen05(_ptr(a), _ptr(w), _ptr(out), M, N, K, 2 if gated else 0, self.sm_count,
-                                             _stream()), f"tcgen05 matrix product [{M}x{K}] x [{N}x{K}]^T")
+        entry = self.lib.cpm_gemm_bf16_tcgen05_pair if pair else self.lib.cpm_gemm_bf16_tcgen05
+        check(entry(_ptr(a), _ptr(w), _ptr(out), M, N, K, 2 if gated else 0, self.sm_count, _stream()),
+              f"tcgen05 matrix product [{M}x{K}] x [{N}x{K}]^T")
         return out
 
     def tcgen05_error(self) -> int:
@@ -185,7 +188,7 @@ class Ops:
         if (self.code == BF16 and interleave == 8 and self.use_tcgen05 and M >= self.TCGEN05_MIN_ROWS and K % 64 == 0
                 and w_gate_up.shape[0] % 32 == 0 and a.data_ptr() % 16 == 0):
             # many rows (prefill): the tcgen05 product applies the activation in its epilogue
-            return self.linear_tcgen05(a, w_gate_up, gated=True)
+            return self.linear_tcgen05(a, w_gate_up, gated=True, pair=self.tcgen05_pair)
         return self.silu_mul(self.linear(a, w_gate_up), interleave)
 
     # ---- attention ----

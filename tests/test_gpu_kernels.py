@@ -353,23 +353,25 @@ def test_block_list_attention_against_generic(n_heads, n_kv, d):
     assert _err(got, want) < KTOL["bfloat16"]
 
 
+@pytest.mark.parametrize("pair", [False, True])
 @pytest.mark.parametrize("M,N,K", [(1, 8, 64), (128, 256, 64), (300, 264, 192), (129, 4608, 128), (2048, 352, 64),
-                                   (777, 1024, 4096)])
-def test_tcgen05_gemm(M, N, K):
+                                   (777, 1024, 4096), (4500, 2560, 128)])
+def test_tcgen05_gemm(M, N, K, pair):
     """The tcgen05 / TMA / TMEM product against fp32 torch: tiles that hang over the edge in M and in N,
-    one and many K blocks, more tiles than one wave of blocks, plain and gated epilogue."""
+    one and many K blocks, more tiles than one wave of blocks, more rows than one band of tiles, plain and
+    gated epilogue; by single blocks and by pairs of blocks on one tile."""
     ops = _ops("bfloat16")
     g = torch.Generator().manual_seed(13)
     a = torch.randn(M, K, generator=g).bfloat16().cuda()
     w = (torch.randn(N, K, generator=g) * 0.05).bfloat16().cuda()
     want = a.float() @ w.float().T
-    got = ops.linear_tcgen05(a, w)
+    got = ops.linear_tcgen05(a, w, pair=pair)
     assert ops.tcgen05_error() == 0
     assert _err(got, want) < KTOL["bfloat16"]
     if N % 32 == 0:
         inter = N // 2
         wi = torch.stack([w[:inter].view(inter // 8, 8, K), w[inter:].view(inter // 8, 8, K)], dim=1).reshape(N, K).contiguous()
         gate, up = a.float() @ w[:inter].float().T, a.float() @ w[inter:].float().T
-        h = ops.linear_tcgen05(a, wi, gated=True)
+        h = ops.linear_tcgen05(a, wi, gated=True, pair=pair)
         assert ops.tcgen05_error() == 0
         assert _err(h, gate * torch.sigmoid(gate) * up) < KTOL["bfloat16"]
