@@ -1,0 +1,359 @@
+// Causal attention of prompt tokens over the paged cache for head size 128, on the fifth-generation
+// tensor cores: S = Q K^T and O += P V are tcgen05.mma with the accumulators in tensor memory (TMEM),
+// Q, K and V tiles come by TMA straight from the query matrix and from the cache pages, and the softmax
+// works on the rows of S that it reads from TMEM, one thread per row.
+//
+// A block takes 128 query tokens of two heads that share a key/value head, so that the tensor cores work
+// on one head's products while the other head's rows are in the softmax ("ping-pong"), and both heads use
+// the same K and V tiles in shared memory.  Keys come 128 at a time (two cache pages).  A key page
+// [64 keys][128] is, as it lies in the cache, the K-major B operand of Q K^T; a value page is stored
+// transposed, [128][64 keys], which is the K-major B operand of P V.  P never goes through shared
+// memory: the softmax threads write it as bf16 over the first 64 columns of the S they have just read,
+// and the second product takes its A operand from TMEM.
+//
+// Warps 0-3 and 4-7 are the softmax of head 0 and head 1 (a warp reads TMEM lanes 32 * (warp % 4) ...),
+// warp 8 allocates TMEM and issues every MMA from one thread, warp 9 is the TMA producer.  TMEM columns:
+// S0 0-127, S1 128-255, O0 256-383, O1 384-511.  The running maximum of a row is only raised when the new
+// maximum exceeds it by more than 8 (in log2 units), in which case the thread rescales its row of O in
+// TMEM; between the products of one head nothing else touches that head's O, because the barrier that
+// announces S(j) is raised by a tcgen05.commit that also covers the earlier P V product.
+//
+// The reference uses its vendored flash-attention kernels (mma.sync) for this step
+// (src/flash_attn/flash_api.hpp, src/model/attn.cuh:137-170).
+//
+// Every barrier wait is bounded; a block that runs out of patience records an error code, stops,
+// waits (bounded) for its copies in flight, frees its TMEM and returns.
+#include "tcgen05.cuh"
+
+namespace fa5 {
+using namespace tc5;
+
+constexpr int kD = 128;
+constexpr int kTileRows = 128;                   // query tokens of a block
+constexpr int kBlockKeys = 128;                  // keys per step: two cache pages
+constexpr int kTileBytes = 128 * 128 * 2;        // a Q, K or V tile: 32 KiB
+constexpr int kHalfBytes = kTileBytes / 2;       // 128 rows x 128 bytes, one swizzle atom wide
+constexpr int kKvStages = 2;
+constexpr int kSmemBytes = 2 * kTileBytes + 2 * kKvStages * kTileBytes + 1024;
+constexpr int kThreads = 320;
+constexpr int kTmemCols = 512;
+constexpr uint32_t kIdesc = instr_desc_bf16(128, 128);
+constexpr float kRescaleThreshold = 8.0f;
+
+enum : int { ERR_NONE = 0, ERR_Q = 1, ERR_K_FULL = 2, ERR_V_FULL = 3, ERR_K_EMPTY = 4, ERR_V_EMPTY = 5, ERR_S_FULL = 6,
+             ERR_P_FULL = 7, ERR_O_FULL = 8 };
+
+__device__ int g_error = 0;
+
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                                 const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
+                                 const int* __restrict__ tile_seq, const int* __restrict__ tile_row,
+                                 const int* __restrict__ cu_q, const int* __restrict__ kv_len,
+                                 const int* __restrict__ slots, const int* __restrict__ page_table, int max_pages,
+                                 int n_pages, int n_heads, int n_kv, float scale_log2) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t q_full, k_full[kKvStages], v_full[kKvStages], k_empty[kKvStages], v_empty[kKvStages],
+        s_full[2], p_full[2], o_full[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    // The tile lists are made of 64-token tiles; this kernel takes them in pairs.
+    const int tile = gridDim.y - 1 - blockIdx.y;                 // later tiles of a sequence have more keys: they go first
+    const int tile_row0 = tile_row[tile];
+    if (tile_row0 % kTileRows != 0) return;
+    const int seq = tile_seq[tile];
+    const int h0 = 2 * blockIdx.x;                               // heads h0, h0 + 1
+    const int kvh = h0 / (n_heads / n_kv);
+    const int q_begin = cu_q[seq], q_len = cu_q[seq + 1] - q_begin;
+    const int history = kv_len[seq] - q_len;                     // keys cached before this step's tokens
+    const int n_keys = history + min(tile_row0 + kTileRows, q_len);
+    const int n_blocks = (n_keys + kBlockKeys - 1) / kBlockKeys;
+    const int last_page = (n_keys - 1) / kPageTokens;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;          // swizzled tiles want 1 KiB alignment
+    const uint32_t q_smem = base, k_smem = base + 2 * kTileBytes, v_smem = k_smem + kKvStages * kTileBytes;
+
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&q_full), 1);
+        for (int s = 0; s < kKvStages; ++s) {
+            mbar_init(smem_u32(&k_full[s]), 1);
+            mbar_init(smem_u32(&v_full[s]), 1);
+            mbar_init(smem_u32(&k_empty[s]), 1);
+            mbar_init(smem_u32(&v_empty[s]), 1);
+        }
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(smem_u32(&s_full[i]), 1);
+            mbar_init(smem_u32(&p_full[i]), 4);                  // the four softmax warps of a head
+            mbar_init(smem_u32(&o_full[i]), 1);
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 8) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"(smem_u32(&tmem_base_slot)), "r"((uint32_t)kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    auto fail = [&](int code) {
+        atomicCAS(&g_error, 0, code);
+        atomicExch(&abort_flag, 1);
+    };
+    auto aborted = [&]() { return *(volatile int*)&abort_flag != 0; };
+
+    if (warp == 9) {
+        // ---- TMA producer ----
+        if (lane == 0) {
+            const int* pages = page_table + (int64_t)slots[seq] * max_pages;
+            mbar_expect_tx(smem_u32(&q_full), 2 * kTileBytes);
+            for (int i = 0; i < 2; ++i)
+                for (int half = 0; half < 2; ++half)
+                    tma_load_2d(q_smem + i * kTileBytes + half * kHalfBytes, &map_q, smem_u32(&q_full),
+                                (h0 + i) * kD + half * 64, q_begin + tile_row0);
+            int issued = 0;
+            for (int j = 0; j < n_blocks && !aborted(); ++j, ++issued) {
+                const int s = j & 1, ph = (j >> 1) & 1;
+                // the second page of the last step may lie beyond the keys: its scores are masked, any page will do
+                const int pa = min(max(pages[2 * j], 0), n_pages - 1);
+                const int pb = min(max(pages[min(2 * j + 1, last_page)], 0), n_pages - 1);
+                if (!mbar_wait_bounded(smem_u32(&k_empty[s]), ph ^ 1)) { fail(ERR_K_EMPTY); break; }
+                mbar_expect_tx(smem_u32(&k_full[s]), kTileBytes);
+                for (int half = 0; half < 2; ++half) {
+                    const uint32_t dst = k_smem + s * kTileBytes + half * kHalfBytes;
+                    tma_load_2d(dst, &map_k, smem_u32(&k_full[s]), half * 64, (pa * n_kv + kvh) * kPageTokens);
+                    tma_load_2d(dst + kHalfBytes / 2, &map_k, smem_u32(&k_full[s]), half * 64, (pb * n_kv + kvh) * kPageTokens);
+                }
+                if (!mbar_wait_bounded(smem_u32(&v_empty[s]), ph ^ 1)) { fail(ERR_V_EMPTY); break; }
+                mbar_expect_tx(smem_u32(&v_full[s]), kTileBytes);
+                tma_load_2d(v_smem + s * kTileBytes, &map_v, smem_u32(&v_full[s]), 0, (pa * n_kv + kvh) * kD);
+                tma_load_2d(v_smem + s * kTileBytes + kHalfBytes, &map_v, smem_u32(&v_full[s]), 0, (pb * n_kv + kvh) * kD);
+            }
+            if (aborted()) {
+                // copies that nobody consumed: wait for them (bounded), so that none is in flight at the exit
+                mbar_wait_bounded(smem_u32(&q_full), 0);
+                for (int j = max(0, issued - kKvStages); j < issued; ++j) {
+                    mbar_wait_bounded(smem_u32(&k_full[j & 1]), (j >> 1) & 1);
+                    mbar_wait_bounded(smem_u32(&v_full[j & 1]), (j >> 1) & 1);
+                }
+            }
+        }
+    } else if (warp == 8) {
+        // ---- MMA issue ----
+        if (lane == 0) {
+            auto issue_qk = [&](int i, int s) {
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {
+                    const uint64_t da = smem_desc_sw128(q_smem + i * kTileBytes + half * kHalfBytes);
+                    const uint64_t db = smem_desc_sw128(k_smem + s * kTileBytes + half * kHalfBytes);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        tcgen05_mma_f16(tmem_base + i * 128, da + 2 * k, db + 2 * k, kIdesc, (half | k) != 0);
+                }
+            };
+            auto issue_pv = [&](int i, int s, bool accumulate) {
+#pragma unroll
+                for (int page = 0; page < 2; ++page) {
+                    const uint64_t db = smem_desc_sw128(v_smem + s * kTileBytes + page * kHalfBytes);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        tcgen05_mma_f16_ts(tmem_base + 256 + i * 128, tmem_base + i * 128 + page * 32 + k * 8, db + 2 * k, kIdesc,
+                                           accumulate || (page | k) != 0);
+                }
+            };
+            bool ok = mbar_wait_bounded(smem_u32(&q_full), 0);
+            if (!ok) fail(ERR_Q);
+            if (ok && !mbar_wait_bounded(smem_u32(&k_full[0]), 0)) { fail(ERR_K_FULL); ok = false; }
+            if (ok) {
+                tcgen05_fence_after();
+                issue_qk(0, 0);
+                tcgen05_commit(smem_u32(&s_full[0]));
+                issue_qk(1, 0);
+                tcgen05_commit(smem_u32(&s_full[1]));
+                tcgen05_commit(smem_u32(&k_empty[0]));
+            }
+            for (int j = 0; ok && j < n_blocks && !aborted(); ++j) {
+                const int s = j & 1, ph = (j >> 1) & 1;
+                const int s1 = (j + 1) & 1, ph1 = ((j + 1) >> 1) & 1;
+                if (!mbar_wait_bounded(smem_u32(&v_full[s]), ph)) { fail(ERR_V_FULL); break; }
+                for (int i = 0; i < 2; ++i) {
+                    if (!mbar_wait_bounded(smem_u32(&p_full[i]), j & 1)) { fail(ERR_P_FULL); ok = false; break; }
+                    tcgen05_fence_after();
+                    issue_pv(i, s, j > 0);
+                    if (i == 1) tcgen05_commit(smem_u32(&v_empty[s]));
+                    if (j + 1 < n_blocks) {
+                        if (i == 0 && !mbar_wait_bounded(smem_u32(&k_full[s1]), ph1)) { fail(ERR_K_FULL); ok = false; break; }
+                        tcgen05_fence_after();
+                        issue_qk(i, s1);
+                        tcgen05_commit(smem_u32(&s_full[i]));
+                        if (i == 1) tcgen05_commit(smem_u32(&k_empty[s1]));
+                    } else {
+                        tcgen05_commit(smem_u32(&o_full[i]));
+                    }
+                }
+            }
+        }
+    } else {
+        // ---- softmax and epilogue: head i, row of this thread ----
+        const int i = warp >> 2, quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const int row = tile_row0 + r;
+        const int limit = row < q_len ? history + row : -1;      // last key this row may see
+        const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+        const uint32_t s_addr = lane_base + i * 128, o_addr = lane_base + 256 + i * 128;
+        float m_ref = -INFINITY, l = 0.f;
+        bool ok = true;
+        for (int j = 0; j < n_blocks; ++j) {
+            if (__any_sync(0xffffffffu, aborted())) { ok = false; break; }
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&s_full[i]), j & 1))) {
+                if (lane == 0) fail(ERR_S_FULL);
+                ok = false;
+                break;
+            }
+            tcgen05_fence_after();
+            uint32_t v[4][32];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) tmem_load_32cols(s_addr + c * 32, v[c]);
+            tmem_load_wait();
+            const int key0 = j * kBlockKeys;
+            if (key0 + kBlockKeys - 1 > history + tile_row0) {   // the diagonal, or the end of the keys
+#pragma unroll
+                for (int c = 0; c < 4; ++c)
+#pragma unroll
+                    for (int e = 0; e < 32; ++e)
+                        if (key0 + c * 32 + e > limit) v[c][e] = 0xff800000u;      // -inf
+            }
+            float mx = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < 4; ++c)
+#pragma unroll
+                for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[c][e]));
+            const float m_new = mx * scale_log2;
+            const bool grow = m_new > m_ref + kRescaleThreshold || (m_ref == -INFINITY && m_new > -INFINITY);
+            if (__any_sync(0xffffffffu, grow)) {
+                const float alpha = grow ? ex2(m_ref - m_new) : 1.f;     // 0 the first time
+                l *= alpha;
+                if (j > 0) {
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {
+                        uint32_t o[32];
+                        tmem_load_32cols(o_addr + c * 32, o);
+                        tmem_load_wait();
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+                        tmem_store_32cols(o_addr + c * 32, o);
+                    }
+                }
+                if (grow) m_ref = m_new;
+            }
+            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+            float sum = 0.f;
+#pragma unroll
+            for (int c = 0; c < 2; ++c) {
+                uint32_t packed[32];
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const float p0 = ex2(fmaf(__uint_as_float(v[2 * c + (e >> 4)][(2 * e) & 31]), scale_log2, -m_use));
+                    const float p1 = ex2(fmaf(__uint_as_float(v[2 * c + (e >> 4)][(2 * e + 1) & 31]), scale_log2, -m_use));
+                    sum += p0 + p1;
+                    packed[e] = pack_bf16(p0, p1);
+                }
+                tmem_store_32cols(s_addr + c * 32, packed);
+            }
+            l += sum;
+            tmem_store_wait();
+            tcgen05_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&p_full[i]));
+        }
+        if (ok && n_blocks > 0) {
+            if (!__all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&o_full[i]), 0))) {
+                if (lane == 0) fail(ERR_O_FULL);
+                ok = false;
+            }
+        }
+        if (ok && n_blocks > 0) {
+            tcgen05_fence_after();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            bf16* orow = out + ((int64_t)(q_begin + min(row, q_len - 1)) * n_heads + h0 + i) * kD;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t o[32];
+                tmem_load_32cols(o_addr + c * 32, o);
+                tmem_load_wait();
+                if (row < q_len) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 8) {
+                        uint4 w;
+                        w.x = pack_bf16(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv);
+                        w.y = pack_bf16(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv);
+                        w.z = pack_bf16(__uint_as_float(o[e + 4]) * inv, __uint_as_float(o[e + 5]) * inv);
+                        w.w = pack_bf16(__uint_as_float(o[e + 6]) * inv, __uint_as_float(o[e + 7]) * inv);
+                        *reinterpret_cast<uint4*>(orow + c * 32 + e) = w;
+                    }
+                }
+            }
+        }
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 8) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)kTmemCols) : "memory");
+    }
+}
+
+}  // namespace fa5
+
+// q, out [tokens, heads, 128] bf16, tokens packed by sequence (cu_q); the cache (n_pages pages of 64 tokens, K pages
+// [n_kv][64][128], V pages [n_kv][128][64]) already holds this step's keys.  The tile lists are those of the 64-token
+// prefill tiles.  Needs an even number of query heads per key/value head.
+CPM_API int cpm_prefill_attention_tcgen05(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                          const int* tile_seq, const int* tile_row, int n_tiles, const int* cu_q,
+                                          const int* kv_len, const int* slots, const int* page_table, int max_pages,
+                                          int n_tokens, int n_pages, int n_heads, int n_kv, int d, float scale,
+                                          cudaStream_t stream) {
+    using namespace fa5;
+    if (n_tiles <= 0 || n_tokens <= 0) return CPM_OK;
+    if (d != kD || n_kv <= 0 || n_heads % n_kv || (n_heads / n_kv) % 2 || n_tiles > 65535 || n_pages <= 0 ||
+        ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 15))
+        return CPM_BAD_ARGUMENT;
+    CUtensorMap map_q, map_k, map_v;
+    if (!tc5::make_map_2d_bf16(&map_q, q, (uint64_t)n_tokens, (uint64_t)n_heads * kD, (uint64_t)n_heads * kD * 2, 64, kTileRows) ||
+        !tc5::make_map_2d_bf16(&map_k, k_cache, (uint64_t)n_pages * n_kv * kPageTokens, kD, kD * 2, 64, kPageTokens) ||
+        !tc5::make_map_2d_bf16(&map_v, v_cache, (uint64_t)n_pages * n_kv * kD, kPageTokens, kPageTokens * 2, 64, kD))
+        return CPM_BAD_ARGUMENT;
+    auto kern = prefill_attention_tcgen05_kernel;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    kern<<<dim3(n_heads / 2, n_tiles), kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, (bf16*)out, tile_seq, tile_row,
+        cu_q, kv_len, slots, page_table, max_pages, n_pages, n_heads, n_kv, scale * 1.4426950408889634f);
+    return launch_status();
+}
+
+// Error code recorded by the kernel since the last call (0 = none), and reset.  Synchronises the device.
+CPM_API int cpm_attention_tcgen05_error() {
+    int code = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&code, fa5::g_error, sizeof(int)) != cudaSuccess) return -1;
+    cudaMemcpyToSymbol(fa5::g_error, &zero, sizeof(int));
+    return code;
+}

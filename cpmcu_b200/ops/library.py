@@ -43,6 +43,8 @@ _SIGNATURES = {
     "cpm_listed_attention_bf16": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, c_float, _P,
                                   c_int, _P],
     "cpm_gemm_bf16_tcgen05": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "cpm_prefill_attention_tcgen05": [_P, _P, _P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
+                                      c_float, _P],
     "cpm_gemm_bf16_tcgen05_pair": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
     "cpm_sample_rows": [_P, c_int64, c_int, c_int, _P, _P, _P, c_uint64, _P, _P, _P],
 }
@@ -82,6 +84,8 @@ def load() -> ctypes.CDLL:
             lib.cpm_set_skinny_prefetch_lines(int(os.environ["CPMCU_SKINNY_PREFETCH"]))
         lib.cpm_gemm_tcgen05_error.argtypes = []
         lib.cpm_gemm_tcgen05_error.restype = c_int
+        lib.cpm_attention_tcgen05_error.argtypes = []
+        lib.cpm_attention_tcgen05_error.restype = c_int
         lib.cpm_decode_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int, c_int]
         lib.cpm_decode_attention_scratch_floats.restype = c_int64
         for name, argtypes in _SIGNATURES.items():

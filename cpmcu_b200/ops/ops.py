@@ -338,6 +338,26 @@ class Ops:
         return out
 
 
+    def prefill_attention_tcgen05(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tiles,
+                                  cu_q: torch.Tensor, kv_len: torch.Tensor, slots: torch.Tensor,
+                                  page_table: torch.Tensor, n_kv: int, scale: float) -> torch.Tensor:
+        """The same as ``prefill_attention`` on the tcgen05 tensor cores: head size 128 and an even number of
+        query heads per key/value head."""
+        self._act(q, "q")
+        n, n_heads, d = q.shape
+        tile_seq, tile_row, n_tiles = tiles
+        out = self.empty(n, n_heads * d)
+        check(self.lib.cpm_prefill_attention_tcgen05(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(tile_seq),
+                                                     _ptr(tile_row), n_tiles, _ptr(cu_q), _ptr(kv_len), _ptr(slots),
+                                                     _ptr(page_table), page_table.shape[1], n, k_cache.shape[0],
+                                                     n_heads, n_kv, d, float(scale), _stream()),
+              f"tcgen05 prefill attention (head_dim {d})")
+        return out
+
+    def attention_tcgen05_error(self) -> int:
+        """Error code the tcgen05 attention kernel recorded since the last call (0 = none); synchronises."""
+        return int(self.lib.cpm_attention_tcgen05_error())
+
     def listed_attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, positions: torch.Tensor,
                          token_seq: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
                          block_list: torch.Tensor, n_kv: int, scale: float) -> torch.Tensor:
