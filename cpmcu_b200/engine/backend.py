@@ -47,7 +47,9 @@ class EngineBackend:
         batch = [SequenceStep(s, list(p), [len(p) - 1]) for s, p in zip(self.slots, prompts)]
         self.h2d_bytes += 4 * sum(len(p) for p in prompts)
         logits = self.stepper.step(batch)
-        return self._sample(logits, keys, [0] * len(prompts), sampling)
+        tokens = self._sample(logits, keys, [0] * len(prompts), sampling)
+        self.ops.raise_on_kernel_error()                # the host has just waited for the tokens anyway
+        return tokens
 
     def decode(self, live, last_tokens, keys, steps_done, sampling, changed) -> List[int]:
         if changed:

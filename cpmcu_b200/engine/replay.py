@@ -52,6 +52,7 @@ def run(model_dir: str, dtype: str, out_dir: str, max_tokens: int, stdin: IO[str
             os.replace(tmp, os.path.join(out_dir, f"{step_no}.f32"))
         else:
             torch.cuda.synchronize()
+        stepper.ops.raise_on_kernel_error()
         for rid in msg.get("end", []):
             rid = str(rid)
             if rid in slots:

@@ -50,6 +50,7 @@ class Ops:
         self.element_size = 4 if dtype == torch.float32 else 2
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.use_tcgen05 = os.environ.get("CPMCU_TCGEN05", "1") != "0"
+        self.use_tcgen05_attention = os.environ.get("CPMCU_TCGEN05_ATTENTION", "1") != "0"
         self.tcgen05_pair = os.environ.get("CPMCU_TCGEN05_PAIR", "0") == "1"      # pairs of blocks on 256-row tiles
 
     # ---- checks ----
@@ -258,6 +259,9 @@ class Ops:
                 return self.decode_attention(q, lane.k, lane.v, ctx.kv_len_dev, ctx.slot_dev, lane.page_table,
                                              n_kv, scale)
             tiles = ctx.extras.get("q_tiles")
+            if tiles is not None and self.use_tcgen05_attention and d == 128 and (n_heads // n_kv) % 2 == 0:
+                return self.prefill_attention_tcgen05(q, lane.k, lane.v, tiles, ctx.cu_q, ctx.kv_len_dev, ctx.slot_dev,
+                                                      lane.page_table, n_kv, scale)
             if tiles is not None:
                 return self.prefill_attention(q, lane.k, lane.v, tiles, ctx.cu_q, ctx.kv_len_dev, ctx.slot_dev,
                                               lane.page_table, n_kv, scale)
@@ -357,6 +361,14 @@ class Ops:
     def attention_tcgen05_error(self) -> int:
         """Error code the tcgen05 attention kernel recorded since the last call (0 = none); synchronises."""
         return int(self.lib.cpm_attention_tcgen05_error())
+
+    def raise_on_kernel_error(self) -> None:
+        """The tcgen05 kernels bound every wait and record a code instead of hanging; this turns a recorded
+        code into an exception.  It synchronises the device: call it where the host waits anyway."""
+        gemm, attn = self.tcgen05_error(), self.attention_tcgen05_error()
+        if gemm or attn:
+            raise RuntimeError(f"a tcgen05 kernel gave up waiting on a barrier (product: code {gemm}, attention: code "
+                               f"{attn}); the results of this step are not valid")
 
     def listed_attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, positions: torch.Tensor,
                          token_seq: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,

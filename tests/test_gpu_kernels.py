@@ -353,6 +353,68 @@ def test_block_list_attention_against_generic(n_heads, n_kv, d):
     assert _err(got, want) < KTOL["bfloat16"]
 
 
+@pytest.mark.parametrize("n_heads,n_kv", [(4, 2), (2, 1), (32, 2)])
+def test_tcgen05_prefill_attention(n_heads, n_kv):
+    """The tcgen05 prefill attention (head size 128, heads in pairs) against the plain implementation:
+    sequences that end inside a page, at a page or tile boundary and just after it, pages in scrambled
+    order, a chunk after a history; and one far key made to dominate a late query."""
+    d = 128
+    ops = _ops("bfloat16")
+    lens = [1, 64, 128, 129, 300, 577]
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.parts.base import CacheNeeds
+    cache = Cache([CacheNeeds(kv_heads=n_kv, head_dim=d)], max_tokens=64 * 40, dtype=torch.bfloat16, device="cuda:0")
+    junk = cache.open_sequences(3)
+    for j, s_ in enumerate(junk):
+        cache.reserve(s_, 64 * (j + 1))
+    slots = cache.open_sequences(len(lens))
+    cache.close_sequence(junk[1])
+    for s_, n in zip(slots, lens):
+        cache.reserve(s_, n)
+        cache.set_length(s_, n)
+    cache.sync()
+    lane = cache.lane(0)
+    g = torch.Generator().manual_seed(11)
+    T = sum(lens)
+    starts = [sum(lens[:i]) for i in range(len(lens))]
+    qkv = (torch.randn(T, (n_heads + 2 * n_kv) * d, generator=g) * 0.5)
+    rows = qkv.view(T, n_heads + 2 * n_kv, d)
+    far_key, late = starts[5] + 70, starts[5] + 560                  # in the longest sequence
+    rows[far_key, n_heads:n_heads + n_kv] = 2.0
+    rows[late, :n_heads] = 2.0
+    qkv = qkv.bfloat16()
+    rows = qkv.float().view(T, n_heads + 2 * n_kv, d)
+    positions = torch.cat([torch.arange(n) for n in lens]).int().cuda()
+    token_seq = torch.cat([torch.full((n,), i) for i, n in enumerate(lens)]).int().cuda()
+    sl = torch.tensor(slots, dtype=torch.int32).cuda()
+    q = ops.rope_store(qkv.cuda(), n_heads, n_kv, d, positions, token_seq, sl, lane.page_table, lane.k, lane.v,
+                       None, 1.0, 0)
+    scale = 1 / math.sqrt(d)
+    want = torch.cat([plain.dense_attention(rows[o:o + n, :n_heads], rows[o:o + n, n_heads:n_heads + n_kv],
+                                            rows[o:o + n, n_heads + n_kv:], scale).reshape(n, -1)
+                      for o, n in zip(starts, lens)])
+    cu = torch.tensor(starts + [T], dtype=torch.int32).cuda()
+    kv_len = torch.tensor(lens, dtype=torch.int32).cuda()
+    from cpmcu_b200.ops.ops import PREFILL_TILE_ROWS as TR
+    tile_seq = [j for j, n in enumerate(lens) for _ in range(0, n, TR)]
+    tile_row = [r for n in lens for r in range(0, n, TR)]
+    tiles = (torch.tensor(tile_seq, dtype=torch.int32).cuda(), torch.tensor(tile_row, dtype=torch.int32).cuda(), len(tile_seq))
+    got = ops.prefill_attention_tcgen05(q, lane.k, lane.v, tiles, cu, kv_len, sl, lane.page_table, n_kv, scale)
+    assert ops.attention_tcgen05_error() == 0
+    assert _err(got, want) < KTOL["bfloat16"]
+    # the far key's value comes through at the late query
+    v_far = rows[far_key, n_heads + n_kv]
+    assert _err(got[late].view(n_heads, d)[0], v_far) < 2e-2
+    # the last 150 tokens of the longest sequence as a step of their own: the earlier ones are history
+    o, n = starts[5], lens[5]
+    cu2 = torch.tensor([0, 150], dtype=torch.int32).cuda()
+    tiles2 = (torch.zeros(3, dtype=torch.int32).cuda(), torch.tensor([0, 64, 128], dtype=torch.int32).cuda(), 3)
+    got2 = ops.prefill_attention_tcgen05(q[o + n - 150:o + n].contiguous(), lane.k, lane.v, tiles2, cu2,
+                                         kv_len[5:6].contiguous(), sl[5:6].contiguous(), lane.page_table, n_kv, scale)
+    assert ops.attention_tcgen05_error() == 0
+    assert _err(got2, want[o + n - 150:o + n]) < KTOL["bfloat16"]
+
+
 @pytest.mark.parametrize("pair", [False, True])
 @pytest.mark.parametrize("M,N,K", [(1, 8, 64), (128, 256, 64), (300, 264, 192), (129, 4608, 128), (2048, 352, 64),
                                    (777, 1024, 4096), (4500, 2560, 128)])
