@@ -278,6 +278,91 @@ __global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
     }
 }
 
+// The same for bf16 with all of a head rotated (rot_dim == d, a multiple of 16): a thread takes eight pairs,
+// two 16-byte loads and two 16-byte stores; value heads are copied 16 elements per thread (their store is
+// transposed, one element per 128 bytes).  heads_per_block: all heads of a token for prompts, a few for
+// decode steps, where the tokens alone would not fill the GPU.
+__global__ void rope_store_vec_kernel(const bf16* __restrict__ qkv, bf16* __restrict__ q_out,
+                                      bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
+                                      const int* __restrict__ positions, const int* __restrict__ token_seq,
+                                      const int* __restrict__ slots, const int* __restrict__ page_table,
+                                      int max_pages, const float* __restrict__ inv_freq, float magnitude,
+                                      int n_heads, int n_kv, int d, int heads_per_block) {
+    extern __shared__ float cs_table[];       // cos[half], sin[half] of this token
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int half = d >> 1;
+    const int64_t row_stride = (int64_t)(n_heads + 2 * n_kv) * d;
+    const bf16* row = qkv + t * row_stride;
+    const int n_all = n_heads + (k_cache ? 2 * n_kv : 0);
+    const int h_begin = blockIdx.y * heads_per_block;
+    const int h_end = min(n_all, h_begin + heads_per_block);
+    if (h_begin >= h_end) return;
+
+    for (int c = threadIdx.x; c < half; c += blockDim.x) {
+        float cs = 1.f, sn = 0.f;
+        if (inv_freq) {
+            const float angle = (float)pos * inv_freq[c];
+            sincosf(angle, &sn, &cs);
+            cs *= magnitude;
+            sn *= magnitude;
+        }
+        cs_table[c] = cs;
+        cs_table[half + c] = sn;
+    }
+    __syncthreads();
+
+    int64_t k_base = 0, v_base = 0;
+    if (k_cache) {
+        const int slot = slots[token_seq[t]];
+        const int page = page_table[(int64_t)slot * max_pages + pos / kPageTokens];
+        k_base = page_row_offset(page, 0, pos % kPageTokens, n_kv, d);
+        v_base = value_offset(page, 0, 0, pos % kPageTokens, n_kv, d);
+    }
+    const int per_head = d >> 4;                                 // items of 16 elements in a head
+    const int items = (h_end - h_begin) * per_head;
+    for (int item = threadIdx.x; item < items; item += blockDim.x) {
+        const int h = h_begin + item / per_head, part = item % per_head;
+        const bf16* src = row + (int64_t)h * d;
+        if (h >= n_heads + n_kv) {                               // a value head: transposed store
+            const int kvh = h - n_heads - n_kv;
+            const uint4 a = *reinterpret_cast<const uint4*>(src + 16 * part);
+            const uint4 b = *reinterpret_cast<const uint4*>(src + 16 * part + 8);
+            const bf16* ea = reinterpret_cast<const bf16*>(&a);
+            const bf16* eb = reinterpret_cast<const bf16*>(&b);
+            bf16* dst = v_cache + v_base + ((int64_t)kvh * d + 16 * part) * kPageTokens;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                dst[(int64_t)e * kPageTokens] = ea[e];
+                dst[(int64_t)(e + 8) * kPageTokens] = eb[e];
+            }
+            continue;
+        }
+        bf16* dst = h < n_heads ? q_out + ((int64_t)t * n_heads + h) * d
+                                : k_cache + k_base + (int64_t)(h - n_heads) * kPageTokens * d;
+        const int c = 8 * part;                                  // pairs (c + e, c + e + half)
+        const uint4 lo = *reinterpret_cast<const uint4*>(src + c);
+        const uint4 hi = *reinterpret_cast<const uint4*>(src + c + half);
+        const __nv_bfloat162* lo2 = reinterpret_cast<const __nv_bfloat162*>(&lo);
+        const __nv_bfloat162* hi2 = reinterpret_cast<const __nv_bfloat162*>(&hi);
+        uint4 out_lo, out_hi;
+        __nv_bfloat162* ol = reinterpret_cast<__nv_bfloat162*>(&out_lo);
+        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&out_hi);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 a = __bfloat1622float2(lo2[e]), b = __bfloat1622float2(hi2[e]);
+            const float c0 = cs_table[c + 2 * e], s0 = cs_table[half + c + 2 * e];
+            const float c1 = cs_table[c + 2 * e + 1], s1 = cs_table[half + c + 2 * e + 1];
+            ol[e] = __floats2bfloat162_rn(a.x * c0 - b.x * s0, a.y * c1 - b.y * s1);
+            oh[e] = __floats2bfloat162_rn(a.x * s0 + b.x * c0, a.y * s1 + b.y * c1);
+        }
+        *reinterpret_cast<uint4*>(dst + c) = out_lo;
+        *reinterpret_cast<uint4*>(dst + c + half) = out_hi;
+    }
+}
+
 CPM_API int cpm_rope_store(const void* qkv, void* q_out, void* k_cache, void* v_cache, const int* positions,
                            const int* token_seq, const int* slots, const int* page_table, int max_pages,
                            const float* inv_freq, float magnitude, int n_tokens, int n_heads, int n_kv, int d,
@@ -286,6 +371,18 @@ CPM_API int cpm_rope_store(const void* qkv, void* q_out, void* k_cache, void* v_
     if (rot_dim < 0 || rot_dim > d || (rot_dim & 1)) return CPM_BAD_ARGUMENT;
     if ((k_cache == nullptr) != (v_cache == nullptr)) return CPM_BAD_ARGUMENT;
     const int n_all = n_heads + (k_cache ? 2 * n_kv : 0);
+    if (dtype == CPM_BF16 && rot_dim == d && d % 16 == 0 && d >= 16 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)q_out & 15) == 0 &&
+        ((uintptr_t)k_cache & 15) == 0) {
+        const int heads_per_block = n_tokens >= 64 ? n_all : kRopeHeadsPerBlock;
+        const int items = heads_per_block * (d / 16);
+        const int threads = items >= 256 ? 256 : ((items + 31) / 32) * 32;
+        dim3 vgrid(n_tokens, (n_all + heads_per_block - 1) / heads_per_block);
+        if (vgrid.y > 65535) return CPM_BAD_ARGUMENT;
+        cpm_launch(rope_store_vec_kernel, vgrid, threads, (size_t)d * sizeof(float), stream, (const bf16*)qkv, (bf16*)q_out,
+                   (bf16*)k_cache, (bf16*)v_cache, positions, token_seq, slots, page_table, max_pages, inv_freq, magnitude,
+                   n_heads, n_kv, d, heads_per_block);
+        return launch_status();
+    }
     dim3 grid(n_tokens, (n_all + kRopeHeadsPerBlock - 1) / kRopeHeadsPerBlock);
     if (grid.y > 65535) return CPM_BAD_ARGUMENT;
     const int threads = d >= 128 ? 64 : 32;
