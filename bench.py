@@ -296,7 +296,7 @@ def kernel_bench(name: str, batch: int, ctx: int, rows: int, n: int, k: int, rep
         us = timed(lambda i: ops.decode_attention(q, cache.lane(i % lanes).k, cache.lane(i % lanes).v, kv_len, sl,
                                                   cache.lane(0).page_table, kv, 1 / math.sqrt(d)), lanes * 2)
         out.update(batch=batch, ctx=ctx, us=us, gbs=batch * ctx * kv * d * 4 / 1e3 / us)
-    elif name == "prefill_attention":
+    elif name in ("prefill_attention", "prefill_attention_mma"):
         cache = Cache([CacheNeeds(kv_heads=kv, head_dim=d)], max_tokens=ctx + 64, dtype=torch.bfloat16, device=dev, n_slots=2)
         slot = cache.open_sequence()
         cache.reserve(slot, ctx)
@@ -307,11 +307,20 @@ def kernel_bench(name: str, batch: int, ctx: int, rows: int, n: int, k: int, rep
         n_tiles = (ctx + PREFILL_TILE_ROWS - 1) // PREFILL_TILE_ROWS
         tiles = (i32([0] * n_tiles), i32(list(range(0, ctx, PREFILL_TILE_ROWS))), n_tiles)
         cu, kv_len, sl = i32([0, ctx]), i32([ctx]), i32([slot])
-        us = timed(lambda i: ops.prefill_attention(q, cache.lane(0).k, cache.lane(0).v, tiles, cu, kv_len, sl,
-                                                   cache.lane(0).page_table, kv, 1 / math.sqrt(d)), 4)
-        out.update(tokens=ctx, us=us, tflops=4 * heads * d * ctx * ctx / 2 / us / 1e6)
+        fn = ops.prefill_attention if name == "prefill_attention_mma" else ops.prefill_attention_tcgen05
+        us = timed(lambda i: fn(q, cache.lane(0).k, cache.lane(0).v, tiles, cu, kv_len, sl,
+                                cache.lane(0).page_table, kv, 1 / math.sqrt(d)), 4)
+        out.update(tokens=ctx, us=us, tflops=4 * heads * d * ctx * ctx / 2 / us / 1e6,
+                   error_code=ops.attention_tcgen05_error())
+    elif name == "gemm_tcgen05":
+        # the gated gate_up product of a prompt chunk: rows x k times (n x k)^T, silu(gate) * up in the epilogue
+        copies = max(2, int(400e6 // (n * k * 2)) + 1)
+        ws = [torch.randn(n, k, device=dev, dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+        x = torch.randn(rows, k, device=dev, dtype=torch.bfloat16)
+        us = timed(lambda i: ops.linear_tcgen05(x, ws[i % copies], gated=True), copies * 2)
+        out.update(rows=rows, n=n, k=k, us=us, tflops=2.0 * rows * n * k / us / 1e6, error_code=ops.tcgen05_error())
     else:
-        print(f"unknown kernel '{name}'; known: skinny_gemm, decode_attention, prefill_attention")
+        print(f"unknown kernel '{name}'; known: skinny_gemm, decode_attention, prefill_attention, prefill_attention_mma, gemm_tcgen05")
         return 2
     print(json.dumps(out))
     return 0
@@ -326,9 +335,9 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="layers built (the full model has 32)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the e2e run")
-    ap.add_argument("--kernel", default=None, help="time one kernel alone: skinny_gemm, decode_attention, prefill_attention")
+    ap.add_argument("--kernel", default=None, help="time one kernel alone: skinny_gemm, decode_attention, prefill_attention (tcgen05), prefill_attention_mma, gemm_tcgen05")
     ap.add_argument("--ctx", type=int, default=CONTEXT, help="--kernel: cached tokens per sequence (or prompt tokens)")
-    ap.add_argument("--rows", type=int, default=8, help="--kernel skinny_gemm: rows of the activation")
+    ap.add_argument("--rows", type=int, default=8, help="--kernel skinny_gemm / gemm_tcgen05: rows of the activation")
     ap.add_argument("--n", type=int, default=4096, help="--kernel skinny_gemm: output features")
     ap.add_argument("--k", type=int, default=4096, help="--kernel skinny_gemm: input features")
     ap.add_argument("--reps", type=int, default=5, help="--kernel: graph replays that are timed")
