@@ -8,7 +8,9 @@ instead of all keys, pooled keys) form a group of their own.  A sequence's token
 live in pages of 64 tokens; a key page is [kv_head][token_in_page][head_dim], a value
 page is its transpose [kv_head][head_dim][token_in_page].  Pages and slots go back to the free lists when
 a sequence ends and are used again as they are: only a slot's state is cleared, its
-pages never are.
+pages never are.  A group whose lanes look at a window of keys gives a sequence's pages
+back as soon as every key in them has fallen out of the window of all later queries,
+so what such a group holds per sequence is bounded by the window and the step size.
 
 The reference keeps one sequence in one contiguous buffer per layer
 (src/model/kvcache.cuh:7-26) and its per-sequence counters in host-side fields of each
@@ -25,6 +27,7 @@ from ..parts.base import CacheNeeds
 from .allocator import CacheFull, FreeList, HandleError
 
 PAGE_TOKENS = 64
+RELEASED = -1          # entry of a sequence's page list whose page went back to the pool
 
 
 def pages_for(tokens: int) -> int:
@@ -41,7 +44,8 @@ class CacheGroup:
         self.n_pages = n_pages
         self.max_pages_per_seq = max_pages_per_seq
         self.pages = FreeList(n_pages, "page")
-        self.pages_of_slot: Dict[int, List[int]] = {}
+        self.pages_of_slot: Dict[int, List[int]] = {}     # by logical page; RELEASED where the window has moved on
+        self.first_live: Dict[int, int] = {}              # slot -> first logical page still held
         self.page_table = torch.zeros(n_slots, max_pages_per_seq, dtype=torch.int32, device=device)
         self._dirty: Dict[int, int] = {}      # slot -> first table column not yet on the device
         n = len(lanes)
@@ -79,14 +83,41 @@ class CacheGroup:
             self._dirty[slot] = min(self._dirty.get(slot, first_new), first_new)
 
     def release(self, slot: int) -> None:
-        self.pages.give_back(self.pages_of_slot.pop(slot, []))
+        self.pages.give_back([p for p in self.pages_of_slot.pop(slot, []) if p != RELEASED])
+        self.first_live.pop(slot, None)
         self._dirty.pop(slot, None)
+
+    def pages_held(self, slot: int) -> int:
+        return sum(1 for p in self.pages_of_slot.get(slot, []) if p != RELEASED)
+
+    def trim(self, slot: int, length: int) -> int:
+        """After a step that left the sequence ``length`` tokens long: gives back the pages all of whose keys
+        lie before the window of every later query (a query at position p >= length sees the keys
+        j > p - window).  The page table keeps the stale entries; no kernel follows them.  Returns the count."""
+        window = self.needs.window
+        if not window:
+            return 0
+        pages = self.pages_of_slot.get(slot)
+        if not pages:
+            return 0
+        dead = min(max(0, length - window + 1) // PAGE_TOKENS, len(pages))
+        first = self.first_live.get(slot, 0)
+        if dead <= first:
+            return 0
+        self.pages.give_back(pages[first:dead])
+        for i in range(first, dead):
+            pages[i] = RELEASED
+        self.first_live[slot] = dead
+        return dead - first
 
     def sync(self) -> None:
         """Brings the device's page table up to date (pageable staging: no later host
         write can reach a copy that is still queued)."""
         for slot, first in self._dirty.items():
             pages = self.pages_of_slot[slot]
+            first = max(first, self.first_live.get(slot, 0))
+            if first >= len(pages):
+                continue
             row = torch.tensor(pages[first:], dtype=torch.int32)
             self.page_table[slot, first:len(pages)].copy_(row)
         self._dirty.clear()
@@ -120,11 +151,13 @@ class Lane:
 
 class Cache:
     def __init__(self, needs_per_lane: Sequence[CacheNeeds], max_tokens: int, dtype: torch.dtype,
-                 device: "torch.device | str", n_slots: Optional[int] = None, max_seq_tokens: Optional[int] = None):
+                 device: "torch.device | str", n_slots: Optional[int] = None, max_seq_tokens: Optional[int] = None,
+                 max_step_tokens: Optional[int] = None):
         """max_tokens: the most tokens live sequences hold together, each sequence's count
         rounded up to a whole page.  max_seq_tokens: the longest single sequence (default:
         all of max_tokens).  n_slots: the most live sequences (default: one per page, at
-        most 1024)."""
+        most 1024).  max_step_tokens: the most tokens one step adds to a sequence; when given,
+        a group with a window is sized for window + step tokens per slot instead of max_tokens."""
         self.device = torch.device(device)
         self.dtype = dtype
         n_pages = max(1, pages_for(max_tokens))
@@ -143,7 +176,12 @@ class Cache:
         self.lanes: List[Optional[Lane]] = [None] * len(needs_per_lane)
         for key, lane_ids in by_key.items():
             needs = needs_per_lane[lane_ids[0]]
-            group = CacheGroup(needs, lane_ids, n_pages, self.n_slots, self.max_pages_per_seq, dtype, self.device)
+            group_pages = n_pages
+            if needs.window and max_step_tokens:
+                # a sequence holds at most the pages its window and one step's tokens touch
+                per_slot = pages_for(needs.window + int(max_step_tokens)) + 1
+                group_pages = min(n_pages, self.n_slots * per_slot)
+            group = CacheGroup(needs, lane_ids, group_pages, self.n_slots, self.max_pages_per_seq, dtype, self.device)
             self.groups.append(group)
             for j, lane_id in enumerate(lane_ids):
                 state = {
@@ -174,12 +212,35 @@ class Cache:
             extra = pages_for(new_length) - len(g.pages_of_slot.get(slot, []))
             if extra > g.pages.n_free:
                 raise CacheFull(f"growing a sequence to {new_length} tokens needs {extra} more pages, "
-                                f"{g.pages.n_free} of {g.n_pages} are free (cache holds {self.max_tokens} tokens)")
+                                f"{g.pages.n_free} of {g.n_pages} are free (this group of layers holds "
+                                f"{g.n_pages * PAGE_TOKENS} tokens)")
         for g in self.groups:
             g.reserve(slot, new_length)
 
+    def check_room(self, growth: Sequence[tuple], step_tokens: int) -> None:
+        """Raises CacheFull unless the sequences can all grow to their new lengths, (slot, new_length) each,
+        when they do so in steps of at most ``step_tokens`` tokens with ``set_length`` after every step
+        (which lets windowed groups give pages back on the way).  Takes nothing."""
+        for g in self.groups:
+            need = 0
+            for slot, new_length in growth:
+                if not self.slots.is_held(slot):
+                    raise HandleError(f"slot {slot} is not open")
+                extra = pages_for(new_length) - len(g.pages_of_slot.get(slot, []))
+                if g.needs.window:
+                    peak = pages_for(g.needs.window + int(step_tokens)) + 1      # most pages a sequence holds at once
+                    extra = min(extra, peak - g.pages_held(slot))
+                need += max(0, extra)
+            if need > g.pages.n_free:
+                raise CacheFull(f"the step needs {need} more pages, {g.pages.n_free} of {g.n_pages} are free "
+                                f"(this group of layers holds {g.n_pages * PAGE_TOKENS} tokens)")
+
     def set_length(self, slot: int, length: int) -> None:
+        """Called when a step is over and the sequence holds ``length`` tokens: windowed groups let go of the
+        pages that no later query can see."""
         self.lengths[slot] = length
+        for g in self.groups:
+            g.trim(slot, length)
 
     def length(self, slot: int) -> int:
         return self.lengths[slot]
@@ -214,6 +275,8 @@ class Cache:
                 if not self.slots.is_held(slot):
                     raise HandleError(f"pages held by closed slot {slot}")
                 for p in pages:
+                    if p == RELEASED:
+                        continue
                     if p in seen:
                         raise HandleError(f"page {p} is held twice")
                     seen.add(p)

@@ -29,7 +29,8 @@ def run(model_dir: str, dtype: str, out_dir: str, max_tokens: int, stdin: IO[str
         device: str = "cuda:0", chunk_tokens: int = 2048) -> int:
     os.makedirs(out_dir, exist_ok=True)
     _, config, model = load_model(model_dir, parse_dtype(dtype), device)
-    cache = Cache(model.cache_needs(), max_tokens=max_tokens, dtype=model.ops.dtype, device=device)
+    cache = Cache(model.cache_needs(), max_tokens=max_tokens, dtype=model.ops.dtype, device=device,
+                  max_step_tokens=chunk_tokens)
     stepper = Stepper(model, cache, chunk_tokens=chunk_tokens)
     slots: Dict[str, int] = {}
     for line in stdin:

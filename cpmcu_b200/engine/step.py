@@ -103,9 +103,15 @@ class Stepper:
                     raise ValueError(f"wanted place {w} is outside the {len(s.tokens)} tokens of slot {s.slot}")
         lengths = [len(s.tokens) for s in batch]
         history = [self.cache.length(s.slot) for s in batch]
-        for s, h, n in zip(batch, history, lengths):
-            self.cache.reserve(s.slot, h + n)
-        self.cache.sync()
+        chunks = plan_chunks(lengths, self.chunk_tokens)
+        # One chunk: room for the whole step is taken before anything runs.  Several chunks: the room is checked
+        # before anything runs and taken chunk by chunk, so that layers with a window can give pages back on the way.
+        if len(chunks) == 1:
+            for s, h, n in zip(batch, history, lengths):
+                self.cache.reserve(s.slot, h + n)
+            self.cache.sync()
+        else:
+            self.cache.check_room([(s.slot, h + n) for s, h, n in zip(batch, history, lengths)], self.chunk_tokens)
 
         # wanted rows in packed coordinates, in request order
         offsets = [0]
@@ -116,10 +122,16 @@ class Stepper:
         if wanted:
             logits = torch.empty(len(wanted), self.vocab_size, dtype=torch.float32, device=self.ops.device)
 
-        chunks = plan_chunks(lengths, self.chunk_tokens)
         for chunk in chunks:
             rows_here = [(k, p - chunk.begin) for k, p in enumerate(wanted) if chunk.begin <= p < chunk.end]
+            if len(chunks) > 1:
+                for i, first, count in chunk.pieces:
+                    self.cache.reserve(batch[i].slot, history[i] + first + count)
+                self.cache.sync()
             out = self._run_chunk(batch, history, chunk, [r for _, r in rows_here])
+            if len(chunks) > 1:
+                for i, first, count in chunk.pieces:
+                    self.cache.set_length(batch[i].slot, history[i] + first + count)
             if rows_here:
                 if len(chunks) == 1 and len(rows_here) == len(wanted):
                     logits = out

@@ -70,7 +70,12 @@ def test_random_open_grow_close_never_loses_a_page():
                 c.close_sequence(s)                          # closed twice
         c.check_consistent()
         for g in c.groups:
-            assert g.pages.n_held == sum(pages_for(n) for n in live.values())
+            if g.needs.window:
+                # pages whose keys are all before the window of any later query have gone back
+                want = sum(pages_for(n) - max(0, n - g.needs.window + 1) // 64 for n in live.values())
+            else:
+                want = sum(pages_for(n) for n in live.values())
+            assert g.pages.n_held == want
     for s in list(live):
         c.close_sequence(s)
     assert c.tokens_held() == 0 and c.slots.n_free == 6
@@ -169,3 +174,26 @@ def test_sampling_params():
         SamplingParams(temperature=-1)
     with pytest.raises(ValueError):
         SamplingParams(top_p=0)
+
+
+def test_window_group_gives_pages_back_as_the_window_moves():
+    needs = [CacheNeeds(kv_heads=1, head_dim=16), CacheNeeds(kv_heads=1, head_dim=16, window=100)]
+    c = Cache(needs, max_tokens=64 * 64, dtype=torch.float32, device="cpu", n_slots=3, max_step_tokens=130)
+    full, win = c.lane(0).group, c.lane(1).group
+    assert win.n_pages == 3 * (pages_for(100 + 130) + 1) and full.n_pages == 64      # sized by window + step
+    s = c.open_sequence()
+    length = 0
+    for step in [130, 130, 1, 1, 64, 1] + [1] * 200 + [130] * 5:
+        c.reserve(s, length + step)
+        length += step
+        c.set_length(s, length)
+        c.check_consistent()
+        assert full.pages_held(s) == pages_for(length)
+        first_needed = max(0, length - 100 + 1) // 64
+        assert win.pages_held(s) == pages_for(length) - first_needed
+        assert win.pages_held(s) <= pages_for(100) + 1
+        # the pages of the keys that later queries see are all there
+        assert all(p >= 0 for p in win.pages_of_slot[s][first_needed:])
+    c.close_sequence(s)
+    assert win.pages.n_held == 0 and full.pages.n_held == 0
+    c.check_consistent()

@@ -324,3 +324,63 @@ def test_window_attention_is_a_parameter_of_the_mixer():
     assert _err(got, want) < 2e-5
     dense = full.forward(ctx, y.cuda(), cache.lane(1), True)
     assert _err(dense[:24], want[:24]) < 2e-5 and _err(dense[30:], want[30:]) > 1e-3
+
+
+def test_window_group_lets_pages_go_while_decoding():
+    """The window part fed in steps (a chunk, then token by token, then chunks again): the pages of keys that
+    have left the window go back to the pool on the way (the group holds a bounded number per sequence), a
+    second sequence takes them over, and every output still equals the windowed plain attention."""
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.parts import MIXERS, PartSpec, StepContext, build_part
+
+    ops = _ops("float32")
+    window = 40
+    spec = PartSpec("gqa_attention", {"hidden_size": 32, "n_heads": 2, "n_kv_heads": 1, "head_dim": 16, "window": window,
+                                      "position": PartSpec("none", {})})
+    att = build_part(MIXERS, spec, ops)
+    g = torch.Generator().manual_seed(5)
+    w = {n: torch.randn(s.shape, generator=g) * 0.3 for n, s in att.weight_specs().items()}
+    att.load_weights({n: t.cuda() for n, t in w.items()})
+    step_tokens = 70
+    cache = Cache([att.cache_needs()], 64 * 64, torch.float32, "cuda:0", n_slots=2, max_step_tokens=step_tokens)
+    group = cache.groups[0]
+    per_slot = (window + step_tokens + 63) // 64 + 1
+    assert group.n_pages == 2 * per_slot                     # far fewer than the 64 pages of a group without window
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32).cuda()
+
+    def run(slot, y_all, cuts):
+        outs, length = [], 0
+        for n in cuts:
+            cache.reserve(slot, length + n)
+            cache.sync()
+            ctx = StepContext(n, 1, n == 1, False, [n], [length + n], [slot], n, length + n, i32([0] * n),
+                              i32(list(range(length, length + n))), i32([0] * n), i32([0, n]), i32([length + n]),
+                              i32([slot]), cache)
+            outs.append(att.forward(ctx, y_all[length:length + n].cuda(), cache.lane(0), True))
+            length += n
+            cache.set_length(slot, length)
+            cache.check_consistent()
+            assert group.pages_held(slot) <= per_slot
+        return torch.cat(outs)
+
+    def want_of(y):
+        n = y.shape[0]
+        q = (y @ w["q_proj.weight"].T).view(n, 2, 16)
+        k = (y @ w["k_proj.weight"].T).view(n, 1, 16)
+        v = (y @ w["v_proj.weight"].T).view(n, 1, 16)
+        return plain.dense_attention(q, k, v, 0.25, window=window).reshape(n, 32) @ w["o_proj.weight"].T
+
+    cuts = [70, 1, 1, 63] + [1] * 300 + [70, 5, 70]
+    total = sum(cuts)
+    y1, y2 = torch.randn(total, 32, generator=g), torch.randn(total, 32, generator=g)
+    s1 = cache.open_sequence()
+    got1 = run(s1, y1, cuts)
+    assert _err(got1, want_of(y1)) < 2e-5
+    assert total // 64 > group.n_pages                       # the sequence is longer than the whole group
+    # a second sequence beside the first one: it gets pages that the first one has let go
+    s2 = cache.open_sequence()
+    got2 = run(s2, y2, cuts[::-1])
+    assert _err(got2, want_of(y2)) < 2e-5
+    cache.close_sequence(s1)
+    cache.close_sequence(s2)
+    assert group.pages.n_held == 0
