@@ -51,6 +51,8 @@ def peaks() -> dict:
             data = json.load(f)
         if "hbm_gbs" in data and "bf16_tflops" in data:
             out = {"hbm_gbs": float(data["hbm_gbs"]), "bf16_tflops": float(data["bf16_tflops"]), "source": "measured"}
+            if "bf16_tflops_sustained" in data:
+                out["bf16_tflops_sustained"] = float(data["bf16_tflops_sustained"])
     except (OSError, ValueError):
         pass
     return out
@@ -68,7 +70,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
-                                          "--format=csv,noheader,nounits", "-lms", "200"],
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except OSError:
             return
@@ -366,6 +368,8 @@ def main() -> int:
     flops = prefill_flops(cfg, a.layers, PREFILL_TOKENS)
     prefill = {"value": PREFILL_TOKENS / (pre_ms * 1e-3), "tokens": PREFILL_TOKENS, "ms": pre_ms,
                "frac": flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)}
+    if "bf16_tflops_sustained" in pk:       # the step is 32 layers long: the peak under the power cap, beside the burst peak
+        prefill["frac_sustained"] = flops / (pre_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12)
 
     points, e2e = {}, None
     if not a.no_points:
