@@ -289,10 +289,11 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, 1)
 decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                         const int* __restrict__ kv_len, const int* __restrict__ slots,
                         const int* __restrict__ page_table, int max_pages, float* __restrict__ part_o,
-                        float* __restrict__ part_ml, int n_heads, int n_kv, int m_tiles, int n_splits,
-                        float scale_log2) {
+                        float* __restrict__ part_ml, bf16* __restrict__ out, int n_heads, int n_kv, int m_tiles,
+                        int n_splits, float scale_log2) {
     // A block takes one share of a sequence's pages; its warps take every third page of the
-    // share and merge their results in shared memory before anything is written.
+    // share and merge their results in shared memory before anything is written.  With one share
+    // per sequence the block writes the final result to ``out`` itself and no combine kernel follows.
     using S = DecodeSmem<D>;
     extern __shared__ __align__(128) unsigned char smem_raw[];
     __shared__ float sm_m[kDecodeWarps][16], sm_l[kDecodeWarps][16];
@@ -377,6 +378,12 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
             o += sm_o[(w * 16 + row) * kLd + c] * f;
             l += sm_l[w][row] * f;
         }
+        if (n_splits == 1) {
+            const int local = mt * 16 + row;
+            if (local < group)
+                out[((int64_t)b * n_heads + kvh * group + local) * D + c] = __float2bfloat16_rn(l > 0.f ? o / l : 0.f);
+            continue;
+        }
         po[i] = o;
         if (c == 0) {
             part_ml[unit * 32 + 2 * row] = mx;
@@ -437,10 +444,11 @@ static int launch_decode(const void* q, const void* k_cache, const void* v_cache
         configured = true;
     }
     cpm_launch(kern, grid, kDecodeWarps * 32, smem, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
-               kv_len, slots, page_table, max_pages, part_o, part_ml, n_heads, n_kv, m_tiles, n_splits,
+               kv_len, slots, page_table, max_pages, part_o, part_ml, (bf16*)out, n_heads, n_kv, m_tiles, n_splits,
                scale * 1.4426950408889634f);
-    cpm_launch(combine_splits_kernel, dim3(n_heads, n_seqs), D >= 128 ? 128 : 64, 0, stream, (const float*)part_o,
-               (const float*)part_ml, (bf16*)out, n_heads, n_kv, m_tiles, n_splits, (int)D);
+    if (n_splits > 1)
+        cpm_launch(combine_splits_kernel, dim3(n_heads, n_seqs), D >= 128 ? 128 : 64, 0, stream, (const float*)part_o,
+                   (const float*)part_ml, (bf16*)out, n_heads, n_kv, m_tiles, n_splits, (int)D);
     return launch_status();
 }
 

@@ -330,7 +330,8 @@ class Ops:
                                                  _ptr(slots), _ptr(page_table), page_table.shape[1], _ptr(scratch),
                                                  n, n_heads, n_kv, d, n_splits, float(scale), _stream()),
               f"decode attention (head_dim {d})")
-        LAUNCHES_EXTRA[0] += 1           # the launcher starts two kernels
+        if n_splits > 1:
+            LAUNCHES_EXTRA[0] += 1       # the launcher starts two kernels: the shares, then their combination
         return out
 
     def prefill_attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tiles,
