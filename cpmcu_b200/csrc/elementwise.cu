@@ -46,6 +46,23 @@ CPM_API int cpm_embed_rows(const int* ids, const void* table, float* out, int n_
 // rows != nullptr: only the listed rows are normed, y is compact [n_rows, hidden]
 // and x is left as it is.
 // ---------------------------------------------------------------------------
+// Four consecutive elements (16-byte or 8-byte aligned) as floats, and back.
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const uint32_t*>(&lo);
+    raw.y = *reinterpret_cast<const uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
 template <typename T, typename W>
 __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ delta, float alpha,
                                    const W* __restrict__ w, T* __restrict__ y,
@@ -59,14 +76,15 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
     const T* dr = delta ? delta + src_row * hidden : nullptr;
     float ss = 0.f;
     if ((hidden & 3) == 0) {
-        // four elements per thread and step: 16-byte loads of the fp32 stream
+        // four elements per thread and step: 16-byte loads of the fp32 stream, one load of the addend's four
         for (int c = 4 * threadIdx.x; c < hidden; c += 4 * blockDim.x) {
             float4 v = *reinterpret_cast<const float4*>(xr + c);
             if (dr) {
-                v.x = fmaf(alpha, to_f32(dr[c]), v.x);
-                v.y = fmaf(alpha, to_f32(dr[c + 1]), v.y);
-                v.z = fmaf(alpha, to_f32(dr[c + 2]), v.z);
-                v.w = fmaf(alpha, to_f32(dr[c + 3]), v.w);
+                const float4 d4 = load4(dr + c);
+                v.x = fmaf(alpha, d4.x, v.x);
+                v.y = fmaf(alpha, d4.y, v.y);
+                v.z = fmaf(alpha, d4.z, v.z);
+                v.w = fmaf(alpha, d4.w, v.w);
                 if (write_back) *reinterpret_cast<float4*>(xr + c) = v;
             }
             *reinterpret_cast<float4*>(row_cache + c) = v;
@@ -89,10 +107,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const T* __restrict__ 
     if ((hidden & 3) == 0) {
         for (int c = 4 * threadIdx.x; c < hidden; c += 4 * blockDim.x) {
             const float4 v = *reinterpret_cast<const float4*>(row_cache + c);
-            yr[c] = from_f32<T>(v.x * r * to_f32(w[c]));
-            yr[c + 1] = from_f32<T>(v.y * r * to_f32(w[c + 1]));
-            yr[c + 2] = from_f32<T>(v.z * r * to_f32(w[c + 2]));
-            yr[c + 3] = from_f32<T>(v.w * r * to_f32(w[c + 3]));
+            const float4 w4 = load4(w + c);
+            store4(yr + c, make_float4(v.x * r * w4.x, v.y * r * w4.y, v.z * r * w4.z, v.w * r * w4.w));
         }
     } else {
         for (int c = threadIdx.x; c < hidden; c += blockDim.x)
