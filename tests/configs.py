@@ -64,3 +64,15 @@ def tiny_d() -> dict:
         "sparse_config": {"kernel_size": 32, "kernel_stride": 16, "block_size": 64, "init_blocks": 1, "topk": 3,
                           "window_size": 64, "dense_len": 100},
     }
+
+
+def tiny_e() -> dict:
+    """Head size 128 with two query heads per key-value head and sizes in multiples of 64: the shapes that
+    the tcgen05 attention and the tcgen05 gated product of the bf16 path take (from 256 prompt tokens on)."""
+    return {
+        "architectures": ["MiniCPMForCausalLM"], "model_type": "minicpm",
+        "num_hidden_layers": 2, "hidden_size": 192, "num_attention_heads": 4, "num_key_value_heads": 2,
+        "head_dim": 128, "intermediate_size": 160, "vocab_size": 900,
+        "rope_theta": 50000.0, "max_position_embeddings": 2048, "rms_norm_eps": 2e-6,
+        "scale_emb": 6, "dim_model_base": 96, "scale_depth": 1.1, "tie_word_embeddings": False,
+    }

@@ -13,6 +13,7 @@ CASES = [
     ("tiny_b_dense", lambda: configs.tiny_b(sparse=False), 1),
     ("tiny_b", configs.tiny_b, 1),
     ("tiny_c", configs.tiny_c, 5),
+    ("tiny_e", configs.tiny_e, 6),
 ]
 DTYPES = ["float32", "bfloat16"]
 
@@ -150,3 +151,32 @@ def test_page_sized_sparse_blocks(model_folders, dtype):
     from tests.plain import minicpm4_plain as plain
     dense = plain.forward(dict(cfgd, sparse_config=None), w, seqs[0])
     assert helpers.rel_err(dense[300:], helpers.plain_logits(folder, seqs[0])[300:]) > 5 * helpers.TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_long_prompts_through_the_tcgen05_kernels(model_folders, dtype):
+    """Head size 128 and prompts of 300 and more tokens: in bf16 the prompt goes through the tcgen05 attention
+    and the tcgen05 gated product (both from their own size limits on), whole, in chunks of 128 with the
+    history growing, two unequal prompts in one step, and then token by token through the decode kernels."""
+    from cpmcu_b200.engine import SequenceStep
+
+    folder = model_folders("tiny_e", configs.tiny_e(), 6, dtype)
+    cfg, st = _stepper(folder, dtype, max_tokens=4096)
+    a = helpers.random_ids(cfg.vocab_size, 420, 61)
+    b = helpers.random_ids(cfg.vocab_size, 300, 62)
+    want_rows = [0, 1, 127, 128, 255, 256, 299]
+    s1, s2 = st.open(2)
+    got = st.step([SequenceStep(s1, a[:400], want_rows + [399]), SequenceStep(s2, b, want_rows)])
+    helpers.check_rows(got[:8], folder, a, want_rows + [399], dtype, "a whole")
+    helpers.check_rows(got[8:], folder, b, want_rows, dtype, "b whole")
+    tail = torch.cat([st.step([SequenceStep(s1, a[i:i + 1], [0])]) for i in range(400, 420)])
+    helpers.check_rows(tail, folder, a, range(400, 420), dtype, "a decoded")
+    st.close(s1)
+    st.close(s2)
+    _, st2 = _stepper(folder, dtype, max_tokens=4096, chunk_tokens=128)
+    s3 = st2.open(1)[0]
+    got = st2.step([SequenceStep(s3, a[:400], want_rows + [399])])
+    helpers.check_rows(got, folder, a, want_rows + [399], dtype, "a in chunks")
+    st2.close(s3)
+    st.ops.raise_on_kernel_error()
+    st.cache.check_consistent()
