@@ -1,4 +1,4 @@
-// Causal attention of prompt tokens over the paged cache for head size 128, on the fifth-generation
+// Causal attention of prompt tokens over the paged cache for head sizes 128 and 64, on the fifth-generation
 // tensor cores: S = Q K^T and O += P V are tcgen05.mma with the accumulators in tensor memory (TMEM),
 // Q, K and V tiles come by TMA straight from the query matrix and from the cache pages, and the softmax
 // works on the rows of S that it reads from TMEM, one thread per row.
@@ -7,13 +7,13 @@
 // on one head's products while the other head's rows are in the softmax ("ping-pong"), and both heads use
 // the same K and V tiles in shared memory.  Keys come 128 at a time (two cache pages).  A key page
 // [64 keys][128] is, as it lies in the cache, the K-major B operand of Q K^T; a value page is stored
-// transposed, [128][64 keys], which is the K-major B operand of P V.  P never goes through shared
+// transposed, [head size][64 keys], which is the K-major B operand of P V.  P never goes through shared
 // memory: the softmax threads write it as bf16 over the first 64 columns of the S they have just read,
 // and the second product takes its A operand from TMEM.
 //
 // Warps 0-3 and 4-7 are the softmax of head 0 and head 1 (a warp reads TMEM lanes 32 * (warp % 4) ...),
-// warp 8 allocates TMEM and issues every MMA from one thread, warp 9 is the TMA producer.  TMEM columns:
-// S0 0-127, S1 128-255, O0 256-383, O1 384-511.  The running maximum of a row is only raised when the new
+// warp 8 allocates TMEM and issues every MMA from one thread, warp 9 is the TMA producer.  TMEM columns
+// (head size 128): S0 0-127, S1 128-255, O0 256-383, O1 384-511.  The running maximum of a row is only raised when the new
 // maximum exceeds it by more than 8 (in log2 units), in which case the thread rescales its row of O in
 // TMEM; between the products of one head nothing else touches that head's O, because the barrier that
 // announces S(j) is raised by a tcgen05.commit that also covers the earlier P V product.
@@ -28,17 +28,26 @@
 namespace fa5 {
 using namespace tc5;
 
-constexpr int kD = 128;
 constexpr int kTileRows = 128;                   // query tokens of a block
 constexpr int kBlockKeys = 128;                  // keys per step: two cache pages
-constexpr int kTileBytes = 128 * 128 * 2;        // a Q, K or V tile: 32 KiB
-constexpr int kHalfBytes = kTileBytes / 2;       // 128 rows x 128 bytes, one swizzle atom wide
+constexpr int kHalfBytes = 128 * 64 * 2;         // 128 rows x 128 bytes, one swizzle atom wide: 16 KiB
 constexpr int kKvStages = 2;
-constexpr int kSmemBytes = 2 * kTileBytes + 2 * kKvStages * kTileBytes + 1024;
 constexpr int kThreads = 320;
 constexpr int kTmemCols = 512;
-constexpr uint32_t kIdesc = instr_desc_bf16(128, 128);
 constexpr float kRescaleThreshold = 8.0f;
+
+// Sizes that depend on the head size D (64 or 128).  A Q tile and a K tile of 128 keys are D / 64 halves of
+// [128 rows][64 elements]; a V tile of 128 keys is two pages of [D rows][64 keys].
+template <int D>
+struct Sizes {
+    static constexpr int kHalves = D / 64;
+    static constexpr int kTileBytes = kTileRows * D * 2;                  // Q, or 128 keys of K, or 128 keys of V
+    static constexpr int kVPageBytes = D * 64 * 2;
+    static constexpr int kSmemBytes = 2 * kTileBytes + 2 * kKvStages * kTileBytes + 1024;
+    static constexpr uint32_t kIdescQK = instr_desc_bf16(128, 128);       // S = Q K^T: N = 128 keys
+    static constexpr uint32_t kIdescPV = instr_desc_bf16(128, D);         // O += P V: N = D
+    static constexpr int kOCol0 = 256;                                    // O of head i at column 256 + i * D
+};
 
 enum : int { ERR_NONE = 0, ERR_Q = 1, ERR_K_FULL = 2, ERR_V_FULL = 3, ERR_K_EMPTY = 4, ERR_V_EMPTY = 5, ERR_S_FULL = 6,
              ERR_P_FULL = 7, ERR_O_FULL = 8 };
@@ -55,6 +64,7 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
+template <int kD>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                                  const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
@@ -62,6 +72,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                  const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                                  const int* __restrict__ slots, const int* __restrict__ page_table, int max_pages,
                                  int n_pages, int n_heads, int n_kv, float scale_log2) {
+    using Z = Sizes<kD>;
+    constexpr int kTileBytes = Z::kTileBytes;
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t q_full, k_full[kKvStages], v_full[kKvStages], k_empty[kKvStages], v_empty[kKvStages],
         s_full[2], p_full[2], o_full[2];
@@ -123,7 +135,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             const int* pages = page_table + (int64_t)slots[seq] * max_pages;
             mbar_expect_tx(smem_u32(&q_full), 2 * kTileBytes);
             for (int i = 0; i < 2; ++i)
-                for (int half = 0; half < 2; ++half)
+                for (int half = 0; half < Z::kHalves; ++half)
                     tma_load_2d(q_smem + i * kTileBytes + half * kHalfBytes, &map_q, smem_u32(&q_full),
                                 (h0 + i) * kD + half * 64, q_begin + tile_row0);
             int issued = 0;
@@ -134,7 +146,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 const int pb = min(max(pages[min(2 * j + 1, last_page)], 0), n_pages - 1);
                 if (!mbar_wait_bounded(smem_u32(&k_empty[s]), ph ^ 1)) { fail(ERR_K_EMPTY); break; }
                 mbar_expect_tx(smem_u32(&k_full[s]), kTileBytes);
-                for (int half = 0; half < 2; ++half) {
+                for (int half = 0; half < Z::kHalves; ++half) {
                     const uint32_t dst = k_smem + s * kTileBytes + half * kHalfBytes;
                     tma_load_2d(dst, &map_k, smem_u32(&k_full[s]), half * 64, (pa * n_kv + kvh) * kPageTokens);
                     tma_load_2d(dst + kHalfBytes / 2, &map_k, smem_u32(&k_full[s]), half * 64, (pb * n_kv + kvh) * kPageTokens);
@@ -142,7 +154,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 if (!mbar_wait_bounded(smem_u32(&v_empty[s]), ph ^ 1)) { fail(ERR_V_EMPTY); break; }
                 mbar_expect_tx(smem_u32(&v_full[s]), kTileBytes);
                 tma_load_2d(v_smem + s * kTileBytes, &map_v, smem_u32(&v_full[s]), 0, (pa * n_kv + kvh) * kD);
-                tma_load_2d(v_smem + s * kTileBytes + kHalfBytes, &map_v, smem_u32(&v_full[s]), 0, (pb * n_kv + kvh) * kD);
+                tma_load_2d(v_smem + s * kTileBytes + Z::kVPageBytes, &map_v, smem_u32(&v_full[s]), 0, (pb * n_kv + kvh) * kD);
             }
             if (aborted()) {
                 // copies that nobody consumed: wait for them (bounded), so that none is in flight at the exit
@@ -158,22 +170,22 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         if (lane == 0) {
             auto issue_qk = [&](int i, int s) {
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {
+                for (int half = 0; half < Z::kHalves; ++half) {
                     const uint64_t da = smem_desc_sw128(q_smem + i * kTileBytes + half * kHalfBytes);
                     const uint64_t db = smem_desc_sw128(k_smem + s * kTileBytes + half * kHalfBytes);
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        tcgen05_mma_f16(tmem_base + i * 128, da + 2 * k, db + 2 * k, kIdesc, (half | k) != 0);
+                        tcgen05_mma_f16(tmem_base + i * 128, da + 2 * k, db + 2 * k, Z::kIdescQK, (half | k) != 0);
                 }
             };
             auto issue_pv = [&](int i, int s, bool accumulate) {
 #pragma unroll
                 for (int page = 0; page < 2; ++page) {
-                    const uint64_t db = smem_desc_sw128(v_smem + s * kTileBytes + page * kHalfBytes);
+                    const uint64_t db = smem_desc_sw128(v_smem + s * kTileBytes + page * Z::kVPageBytes);
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        tcgen05_mma_f16_ts(tmem_base + 256 + i * 128, tmem_base + i * 128 + page * 32 + k * 8, db + 2 * k, kIdesc,
-                                           accumulate || (page | k) != 0);
+                        tcgen05_mma_f16_ts(tmem_base + Z::kOCol0 + i * kD, tmem_base + i * 128 + page * 32 + k * 8, db + 2 * k,
+                                           Z::kIdescPV, accumulate || (page | k) != 0);
                 }
             };
             bool ok = mbar_wait_bounded(smem_u32(&q_full), 0);
@@ -215,7 +227,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         const int row = tile_row0 + r;
         const int limit = row < q_len ? history + row : -1;      // last key this row may see
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        const uint32_t s_addr = lane_base + i * 128, o_addr = lane_base + 256 + i * 128;
+        const uint32_t s_addr = lane_base + i * 128, o_addr = lane_base + Z::kOCol0 + i * kD;
         float m_ref = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_blocks; ++j) {
@@ -250,7 +262,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 l *= alpha;
                 if (j > 0) {
 #pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
+                    for (int c = 0; c < kD / 32; ++c) {
                         uint32_t o[32];
                         tmem_load_32cols(o_addr + c * 32, o);
                         tmem_load_wait();
@@ -292,7 +304,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             const float inv = l > 0.f ? 1.f / l : 0.f;
             bf16* orow = out + ((int64_t)(q_begin + min(row, q_len - 1)) * n_heads + h0 + i) * kD;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < kD / 32; ++c) {
                 uint32_t o[32];
                 tmem_load_32cols(o_addr + c * 32, o);
                 tmem_load_wait();
@@ -320,34 +332,46 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 
 }  // namespace fa5
 
-// q, out [tokens, heads, 128] bf16, tokens packed by sequence (cu_q); the cache (n_pages pages of 64 tokens, K pages
-// [n_kv][64][128], V pages [n_kv][128][64]) already holds this step's keys.  The tile lists are those of the 64-token
-// prefill tiles.  Needs an even number of query heads per key/value head.
+namespace fa5 {
+template <int D>
+static int launch(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq, const int* tile_row,
+                  int n_tiles, const int* cu_q, const int* kv_len, const int* slots, const int* page_table, int max_pages,
+                  int n_tokens, int n_pages, int n_heads, int n_kv, float scale, cudaStream_t stream) {
+    CUtensorMap map_q, map_k, map_v;
+    if (!tc5::make_map_2d_bf16(&map_q, q, (uint64_t)n_tokens, (uint64_t)n_heads * D, (uint64_t)n_heads * D * 2, 64, kTileRows) ||
+        !tc5::make_map_2d_bf16(&map_k, k_cache, (uint64_t)n_pages * n_kv * kPageTokens, D, D * 2, 64, kPageTokens) ||
+        !tc5::make_map_2d_bf16(&map_v, v_cache, (uint64_t)n_pages * n_kv * D, kPageTokens, kPageTokens * 2, 64, D))
+        return CPM_BAD_ARGUMENT;
+    auto kern = prefill_attention_tcgen05_kernel<D>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Sizes<D>::kSmemBytes);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    kern<<<dim3(n_heads / 2, n_tiles), kThreads, Sizes<D>::kSmemBytes, stream>>>(map_q, map_k, map_v, (bf16*)out, tile_seq,
+        tile_row, cu_q, kv_len, slots, page_table, max_pages, n_pages, n_heads, n_kv, scale * 1.4426950408889634f);
+    return launch_status();
+}
+}  // namespace fa5
+
+// q, out [tokens, heads, d] bf16 with d = 128 or 64, tokens packed by sequence (cu_q); the cache (n_pages pages of 64
+// tokens, K pages [n_kv][64][d], V pages [n_kv][d][64]) already holds this step's keys.  The tile lists are those of the
+// 64-token prefill tiles.  Needs an even number of query heads per key/value head.
 CPM_API int cpm_prefill_attention_tcgen05(const void* q, const void* k_cache, const void* v_cache, void* out,
                                           const int* tile_seq, const int* tile_row, int n_tiles, const int* cu_q,
                                           const int* kv_len, const int* slots, const int* page_table, int max_pages,
                                           int n_tokens, int n_pages, int n_heads, int n_kv, int d, float scale,
                                           cudaStream_t stream) {
-    using namespace fa5;
     if (n_tiles <= 0 || n_tokens <= 0) return CPM_OK;
-    if (d != kD || n_kv <= 0 || n_heads % n_kv || (n_heads / n_kv) % 2 || n_tiles > 65535 || n_pages <= 0 ||
+    if ((d != 128 && d != 64) || n_kv <= 0 || n_heads % n_kv || (n_heads / n_kv) % 2 || n_tiles > 65535 || n_pages <= 0 ||
         ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 15))
         return CPM_BAD_ARGUMENT;
-    CUtensorMap map_q, map_k, map_v;
-    if (!tc5::make_map_2d_bf16(&map_q, q, (uint64_t)n_tokens, (uint64_t)n_heads * kD, (uint64_t)n_heads * kD * 2, 64, kTileRows) ||
-        !tc5::make_map_2d_bf16(&map_k, k_cache, (uint64_t)n_pages * n_kv * kPageTokens, kD, kD * 2, 64, kPageTokens) ||
-        !tc5::make_map_2d_bf16(&map_v, v_cache, (uint64_t)n_pages * n_kv * kD, kPageTokens, kPageTokens * 2, 64, kD))
-        return CPM_BAD_ARGUMENT;
-    auto kern = prefill_attention_tcgen05_kernel;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
-    kern<<<dim3(n_heads / 2, n_tiles), kThreads, kSmemBytes, stream>>>(map_q, map_k, map_v, (bf16*)out, tile_seq, tile_row,
-        cu_q, kv_len, slots, page_table, max_pages, n_pages, n_heads, n_kv, scale * 1.4426950408889634f);
-    return launch_status();
+    if (d == 128)
+        return fa5::launch<128>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table, max_pages,
+                                n_tokens, n_pages, n_heads, n_kv, scale, stream);
+    return fa5::launch<64>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table, max_pages,
+                           n_tokens, n_pages, n_heads, n_kv, scale, stream);
 }
 
 // Error code recorded by the kernel since the last call (0 = none), and reset.  Synchronises the device.

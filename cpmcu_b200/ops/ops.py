@@ -266,7 +266,8 @@ class Ops:
                 return self.decode_attention(q, lane.k, lane.v, ctx.kv_len_dev, ctx.slot_dev, lane.page_table,
                                              n_kv, scale)
             tiles = ctx.extras.get("q_tiles")
-            if tiles is not None and self.use_tcgen05_attention and d == 128 and (n_heads // n_kv) % 2 == 0:
+            if (tiles is not None and self.use_tcgen05_attention and (n_heads // n_kv) % 2 == 0
+                    and (d == 128 or (d == 64 and ctx.max_kv_len >= 1024))):      # short prompts of head size 64: the smaller tiles win
                 return self.prefill_attention_tcgen05(q, lane.k, lane.v, tiles, ctx.cu_q, ctx.kv_len_dev, ctx.slot_dev,
                                                       lane.page_table, n_kv, scale)
             if tiles is not None:
@@ -353,8 +354,8 @@ class Ops:
     def prefill_attention_tcgen05(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tiles,
                                   cu_q: torch.Tensor, kv_len: torch.Tensor, slots: torch.Tensor,
                                   page_table: torch.Tensor, n_kv: int, scale: float) -> torch.Tensor:
-        """The same as ``prefill_attention`` on the tcgen05 tensor cores: head size 128 and an even number of
-        query heads per key/value head."""
+        """The same as ``prefill_attention`` on the tcgen05 tensor cores: head size 128 or 64 and an even number
+        of query heads per key/value head."""
         self._act(q, "q")
         n, n_heads, d = q.shape
         tile_seq, tile_row, n_tiles = tiles

@@ -353,12 +353,11 @@ def test_block_list_attention_against_generic(n_heads, n_kv, d):
     assert _err(got, want) < KTOL["bfloat16"]
 
 
-@pytest.mark.parametrize("n_heads,n_kv", [(4, 2), (2, 1), (32, 2)])
-def test_tcgen05_prefill_attention(n_heads, n_kv):
-    """The tcgen05 prefill attention (head size 128, heads in pairs) against the plain implementation:
+@pytest.mark.parametrize("n_heads,n_kv,d", [(4, 2, 128), (2, 1, 128), (32, 2, 128), (16, 2, 64), (4, 2, 64)])
+def test_tcgen05_prefill_attention(n_heads, n_kv, d):
+    """The tcgen05 prefill attention (head sizes 128 and 64, heads in pairs) against the plain implementation:
     sequences that end inside a page, at a page or tile boundary and just after it, pages in scrambled
     order, a chunk after a history; and one far key made to dominate a late query."""
-    d = 128
     ops = _ops("bfloat16")
     lens = [1, 64, 128, 129, 300, 577]
     from cpmcu_b200.cache import Cache
