@@ -436,3 +436,57 @@ def test_tcgen05_gemm(M, N, K, pair):
         h = ops.linear_tcgen05(a, wi, gated=True, pair=pair)
         assert ops.tcgen05_error() == 0
         assert _err(h, gate * torch.sigmoid(gate) * up) < KTOL["bfloat16"]
+
+
+@pytest.mark.parametrize("d", [128, 64])
+def test_tcgen05_prefill_attention_rescales_and_long_history(d):
+    """Scores that keep growing along the sequence, so that the running maximum of a row is raised again and
+    again (the kernel then rescales its accumulator in tensor memory), over 3,000 keys; then a chunk of 200
+    tokens whose history is the rest."""
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.parts.base import CacheNeeds
+    from cpmcu_b200.ops.ops import PREFILL_TILE_ROWS as TR
+
+    n_heads, n_kv, n = 2, 1, 3000
+    ops = _ops("bfloat16")
+    cache = Cache([CacheNeeds(kv_heads=n_kv, head_dim=d)], max_tokens=64 * 50, dtype=torch.bfloat16, device="cuda:0")
+    slot = cache.open_sequence()
+    cache.reserve(slot, n)
+    cache.set_length(slot, n)
+    cache.sync()
+    lane = cache.lane(0)
+    g = torch.Generator().manual_seed(17)
+    qkv = torch.randn(n, (n_heads + 2 * n_kv) * d, generator=g)
+    rows = qkv.view(n, n_heads + 2 * n_kv, d)
+    direction = torch.randn(d, generator=g)
+    direction /= direction.norm()
+    # every query looks along ``direction``; the keys' component along it grows with the position, so the score of
+    # the newest keys exceeds all earlier ones by more and more (about 0.12 * position / sqrt(d) * |q| in all)
+    rows[:, :n_heads] = 0.3 * rows[:, :n_heads] + 6.0 * direction
+    rows[:, n_heads:n_heads + n_kv] = 0.3 * rows[:, n_heads:n_heads + n_kv] + (torch.arange(n)[:, None, None] * 0.02) * direction
+    qkv = qkv.bfloat16()
+    rows = qkv.float().view(n, n_heads + 2 * n_kv, d)
+    positions = torch.arange(n).int().cuda()
+    token_seq = torch.zeros(n, dtype=torch.int32).cuda()
+    sl = torch.tensor([slot], dtype=torch.int32).cuda()
+    q = ops.rope_store(qkv.cuda(), n_heads, n_kv, d, positions, token_seq, sl, lane.page_table, lane.k, lane.v, None, 1.0, 0)
+    scale = 1 / math.sqrt(d)
+    want = plain.dense_attention(rows[:, :n_heads], rows[:, n_heads:n_heads + n_kv], rows[:, n_heads + n_kv:], scale).reshape(n, -1)
+    # the row maximum in log2 units rises by far more than the kernel's rescaling threshold of 8 along a row
+    s_last = (rows[n - 1, 0] @ rows[:, n_heads].T) * scale * 1.4427
+    assert float(s_last[-1] - s_last[64]) > 30
+    cu = torch.tensor([0, n], dtype=torch.int32).cuda()
+    kv_len = torch.tensor([n], dtype=torch.int32).cuda()
+    tile_row = list(range(0, n, TR))
+    tiles = (torch.zeros(len(tile_row), dtype=torch.int32).cuda(), torch.tensor(tile_row, dtype=torch.int32).cuda(), len(tile_row))
+    got = ops.prefill_attention_tcgen05(q, lane.k, lane.v, tiles, cu, kv_len, sl, lane.page_table, n_kv, scale)
+    assert ops.attention_tcgen05_error() == 0
+    assert _err(got, want) < KTOL["bfloat16"]
+    tail = 200
+    cu2 = torch.tensor([0, tail], dtype=torch.int32).cuda()
+    tr2 = list(range(0, tail, TR))
+    tiles2 = (torch.zeros(len(tr2), dtype=torch.int32).cuda(), torch.tensor(tr2, dtype=torch.int32).cuda(), len(tr2))
+    got2 = ops.prefill_attention_tcgen05(q[n - tail:].contiguous(), lane.k, lane.v, tiles2, cu2, kv_len, sl, lane.page_table,
+                                         n_kv, scale)
+    assert ops.attention_tcgen05_error() == 0
+    assert _err(got2, want[n - tail:]) < KTOL["bfloat16"]
