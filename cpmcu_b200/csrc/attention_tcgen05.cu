@@ -71,7 +71,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                  const int* __restrict__ tile_seq, const int* __restrict__ tile_row,
                                  const int* __restrict__ cu_q, const int* __restrict__ kv_len,
                                  const int* __restrict__ slots, const int* __restrict__ page_table, int max_pages,
-                                 int n_pages, int n_heads, int n_kv, float scale_log2) {
+                                 int n_pages, int n_heads, int n_kv, float scale_log2, float* __restrict__ part_o,
+                                 float* __restrict__ part_ml, int n_splits, int n_tokens) {
     using Z = Sizes<kD>;
     constexpr int kTileBytes = Z::kTileBytes;
     extern __shared__ unsigned char smem_raw[];
@@ -90,8 +91,13 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     const int q_begin = cu_q[seq], q_len = cu_q[seq + 1] - q_begin;
     const int history = kv_len[seq] - q_len;                     // keys cached before this step's tokens
     const int n_keys = history + min(tile_row0 + kTileRows, q_len);
-    const int n_blocks = (n_keys + kBlockKeys - 1) / kBlockKeys;
     const int last_page = (n_keys - 1) / kPageTokens;
+    // With n_splits > 1 (few query tiles, many keys: a short chunk after a long history) the key steps of a tile
+    // are shared out over gridDim.z blocks, which leave unnormalised partial results for a second kernel.
+    const int all_blocks = (n_keys + kBlockKeys - 1) / kBlockKeys;
+    const int per_split = (all_blocks + n_splits - 1) / n_splits;
+    const int j_first = (int)blockIdx.z * per_split;
+    const int n_blocks = max(0, min(all_blocks, j_first + per_split) - j_first);      // key steps of this block
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;          // swizzled tiles want 1 KiB alignment
@@ -133,17 +139,19 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         // ---- TMA producer ----
         if (lane == 0) {
             const int* pages = page_table + (int64_t)slots[seq] * max_pages;
-            mbar_expect_tx(smem_u32(&q_full), 2 * kTileBytes);
-            for (int i = 0; i < 2; ++i)
-                for (int half = 0; half < Z::kHalves; ++half)
-                    tma_load_2d(q_smem + i * kTileBytes + half * kHalfBytes, &map_q, smem_u32(&q_full),
-                                (h0 + i) * kD + half * 64, q_begin + tile_row0);
+            if (n_blocks > 0) {
+                mbar_expect_tx(smem_u32(&q_full), 2 * kTileBytes);
+                for (int i = 0; i < 2; ++i)
+                    for (int half = 0; half < Z::kHalves; ++half)
+                        tma_load_2d(q_smem + i * kTileBytes + half * kHalfBytes, &map_q, smem_u32(&q_full),
+                                    (h0 + i) * kD + half * 64, q_begin + tile_row0);
+            }
             int issued = 0;
             for (int j = 0; j < n_blocks && !aborted(); ++j, ++issued) {
                 const int s = j & 1, ph = (j >> 1) & 1;
                 // the second page of the last step may lie beyond the keys: its scores are masked, any page will do
-                const int pa = min(max(pages[2 * j], 0), n_pages - 1);
-                const int pb = min(max(pages[min(2 * j + 1, last_page)], 0), n_pages - 1);
+                const int pa = min(max(pages[2 * (j_first + j)], 0), n_pages - 1);
+                const int pb = min(max(pages[min(2 * (j_first + j) + 1, last_page)], 0), n_pages - 1);
                 if (!mbar_wait_bounded(smem_u32(&k_empty[s]), ph ^ 1)) { fail(ERR_K_EMPTY); break; }
                 mbar_expect_tx(smem_u32(&k_full[s]), kTileBytes);
                 for (int half = 0; half < Z::kHalves; ++half) {
@@ -158,7 +166,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             }
             if (aborted()) {
                 // copies that nobody consumed: wait for them (bounded), so that none is in flight at the exit
-                mbar_wait_bounded(smem_u32(&q_full), 0);
+                if (n_blocks > 0) mbar_wait_bounded(smem_u32(&q_full), 0);
                 for (int j = max(0, issued - kKvStages); j < issued; ++j) {
                     mbar_wait_bounded(smem_u32(&k_full[j & 1]), (j >> 1) & 1);
                     mbar_wait_bounded(smem_u32(&v_full[j & 1]), (j >> 1) & 1);
@@ -188,8 +196,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                                            Z::kIdescPV, accumulate || (page | k) != 0);
                 }
             };
-            bool ok = mbar_wait_bounded(smem_u32(&q_full), 0);
-            if (!ok) fail(ERR_Q);
+            bool ok = n_blocks > 0;
+            if (ok && !mbar_wait_bounded(smem_u32(&q_full), 0)) { fail(ERR_Q); ok = false; }
             if (ok && !mbar_wait_bounded(smem_u32(&k_full[0]), 0)) { fail(ERR_K_FULL); ok = false; }
             if (ok) {
                 tcgen05_fence_after();
@@ -242,7 +250,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
             for (int c = 0; c < 4; ++c) tmem_load_32cols(s_addr + c * 32, v[c]);
             tmem_load_wait();
-            const int key0 = j * kBlockKeys;
+            const int key0 = (j_first + j) * kBlockKeys;
             if (key0 + kBlockKeys - 1 > history + tile_row0) {   // the diagonal, or the end of the keys
 #pragma unroll
                 for (int c = 0; c < 4; ++c)
@@ -299,7 +307,28 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 ok = false;
             }
         }
-        if (ok && n_blocks > 0) {
+        if (n_splits > 1) {
+            // this block's share of the keys: the accumulator as it is, the maximum it refers to, and the sum
+            const int64_t at = (((int64_t)blockIdx.z * n_tokens + q_begin + min(row, q_len - 1)) * n_heads + h0 + i);
+            if (ok && n_blocks > 0) {
+                tcgen05_fence_after();
+#pragma unroll 1
+                for (int c = 0; c < kD / 32; ++c) {
+                    uint32_t o[32];
+                    tmem_load_32cols(o_addr + c * 32, o);
+                    tmem_load_wait();
+                    if (row < q_len) {
+#pragma unroll
+                        for (int e = 0; e < 32; e += 4)
+                            *reinterpret_cast<uint4*>(part_o + at * kD + c * 32 + e) = make_uint4(o[e], o[e + 1], o[e + 2], o[e + 3]);
+                    }
+                }
+            }
+            if (row < q_len) {
+                part_ml[2 * at] = n_blocks > 0 ? m_ref : -INFINITY;
+                part_ml[2 * at + 1] = n_blocks > 0 ? l : 0.f;
+            }
+        } else if (ok && n_blocks > 0) {
             tcgen05_fence_after();
             const float inv = l > 0.f ? 1.f / l : 0.f;
             bf16* orow = out + ((int64_t)(q_begin + min(row, q_len - 1)) * n_heads + h0 + i) * kD;
@@ -333,10 +362,34 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 }  // namespace fa5
 
 namespace fa5 {
+// out[t, h, :] = sum_s o_s * 2^(m_s - M) / sum_s l_s * 2^(m_s - M), M = max_s m_s, over the shares s of the keys.
+__global__ void combine_key_shares_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                          bf16* __restrict__ out, int n_tokens, int n_heads, int D, int n_splits) {
+    const int64_t th = (int64_t)blockIdx.x * n_heads + blockIdx.y;
+    const int64_t stride = (int64_t)n_tokens * n_heads;
+    float mx = -INFINITY;
+    for (int s = 0; s < n_splits; ++s) mx = fmaxf(mx, part_ml[2 * (s * stride + th)]);
+    float denom = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+        const float m = part_ml[2 * (s * stride + th)];
+        if (m != -INFINITY) denom += part_ml[2 * (s * stride + th) + 1] * exp2f(m - mx);
+    }
+    const float inv = denom > 0.f ? 1.f / denom : 0.f;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) {
+        float acc = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float m = part_ml[2 * (s * stride + th)];
+            if (m != -INFINITY) acc += part_o[(s * stride + th) * D + c] * exp2f(m - mx);
+        }
+        out[th * D + c] = __float2bfloat16_rn(acc * inv);
+    }
+}
+
 template <int D>
 static int launch(const void* q, const void* k_cache, const void* v_cache, void* out, const int* tile_seq, const int* tile_row,
                   int n_tiles, const int* cu_q, const int* kv_len, const int* slots, const int* page_table, int max_pages,
-                  int n_tokens, int n_pages, int n_heads, int n_kv, float scale, cudaStream_t stream) {
+                  int n_tokens, int n_pages, int n_heads, int n_kv, float scale, float* scratch, int n_splits,
+                  cudaStream_t stream) {
     CUtensorMap map_q, map_k, map_v;
     if (!tc5::make_map_2d_bf16(&map_q, q, (uint64_t)n_tokens, (uint64_t)n_heads * D, (uint64_t)n_heads * D * 2, 64, kTileRows) ||
         !tc5::make_map_2d_bf16(&map_k, k_cache, (uint64_t)n_pages * n_kv * kPageTokens, D, D * 2, 64, kPageTokens) ||
@@ -349,29 +402,38 @@ static int launch(const void* q, const void* k_cache, const void* v_cache, void*
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    kern<<<dim3(n_heads / 2, n_tiles), kThreads, Sizes<D>::kSmemBytes, stream>>>(map_q, map_k, map_v, (bf16*)out, tile_seq,
-        tile_row, cu_q, kv_len, slots, page_table, max_pages, n_pages, n_heads, n_kv, scale * 1.4426950408889634f);
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (int64_t)n_splits * n_tokens * n_heads * D : nullptr;
+    kern<<<dim3(n_heads / 2, n_tiles, n_splits), kThreads, Sizes<D>::kSmemBytes, stream>>>(map_q, map_k, map_v, (bf16*)out,
+        tile_seq, tile_row, cu_q, kv_len, slots, page_table, max_pages, n_pages, n_heads, n_kv, scale * 1.4426950408889634f,
+        part_o, part_ml, n_splits, n_tokens);
+    if (n_splits > 1)
+        combine_key_shares_kernel<<<dim3(n_tokens, n_heads), D / 2, 0, stream>>>(part_o, part_ml, (bf16*)out, n_tokens, n_heads,
+                                                                               D, n_splits);
     return launch_status();
 }
 }  // namespace fa5
 
 // q, out [tokens, heads, d] bf16 with d = 128 or 64, tokens packed by sequence (cu_q); the cache (n_pages pages of 64
 // tokens, K pages [n_kv][64][d], V pages [n_kv][d][64]) already holds this step's keys.  The tile lists are those of the
-// 64-token prefill tiles.  Needs an even number of query heads per key/value head.
+// 64-token prefill tiles.  Needs an even number of query heads per key/value head.  n_splits > 1: the keys of every
+// tile are shared out over that many blocks (for few tiles and many keys) and scratch holds
+// n_splits * n_tokens * n_heads * (d + 2) floats.
 CPM_API int cpm_prefill_attention_tcgen05(const void* q, const void* k_cache, const void* v_cache, void* out,
                                           const int* tile_seq, const int* tile_row, int n_tiles, const int* cu_q,
                                           const int* kv_len, const int* slots, const int* page_table, int max_pages,
                                           int n_tokens, int n_pages, int n_heads, int n_kv, int d, float scale,
-                                          cudaStream_t stream) {
+                                          float* scratch, int n_splits, cudaStream_t stream) {
     if (n_tiles <= 0 || n_tokens <= 0) return CPM_OK;
+    if (n_splits < 1 || n_splits > 64 || (n_splits > 1 && !scratch) || n_tokens > 65535 * 1024) return CPM_BAD_ARGUMENT;
     if ((d != 128 && d != 64) || n_kv <= 0 || n_heads % n_kv || (n_heads / n_kv) % 2 || n_tiles > 65535 || n_pages <= 0 ||
         ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 15))
         return CPM_BAD_ARGUMENT;
     if (d == 128)
         return fa5::launch<128>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table, max_pages,
-                                n_tokens, n_pages, n_heads, n_kv, scale, stream);
+                                n_tokens, n_pages, n_heads, n_kv, scale, scratch, n_splits, stream);
     return fa5::launch<64>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table, max_pages,
-                           n_tokens, n_pages, n_heads, n_kv, scale, stream);
+                           n_tokens, n_pages, n_heads, n_kv, scale, scratch, n_splits, stream);
 }
 
 // Error code recorded by the kernel since the last call (0 = none), and reset.  Synchronises the device.

@@ -44,7 +44,7 @@ _SIGNATURES = {
                                   c_int, _P],
     "cpm_gemm_bf16_tcgen05": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
     "cpm_prefill_attention_tcgen05": [_P, _P, _P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
-                                      c_float, _P],
+                                      c_float, _P, c_int, _P],
     "cpm_gemm_bf16_tcgen05_pair": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
     "cpm_sample_rows": [_P, c_int64, c_int, c_int, _P, _P, _P, c_uint64, _P, _P, _P],
 }

@@ -269,7 +269,8 @@ class Ops:
             if (tiles is not None and self.use_tcgen05_attention and (n_heads // n_kv) % 2 == 0
                     and (d == 128 or (d == 64 and ctx.max_kv_len >= 1024))):      # short prompts of head size 64: the smaller tiles win
                 return self.prefill_attention_tcgen05(q, lane.k, lane.v, tiles, ctx.cu_q, ctx.kv_len_dev, ctx.slot_dev,
-                                                      lane.page_table, n_kv, scale)
+                                                      lane.page_table, n_kv, scale,
+                                                      self.prefill_key_shares(ctx.q_lens, ctx.max_kv_len, n_heads))
             if tiles is not None:
                 return self.prefill_attention(q, lane.k, lane.v, tiles, ctx.cu_q, ctx.kv_len_dev, ctx.slot_dev,
                                               lane.page_table, n_kv, scale)
@@ -353,19 +354,30 @@ class Ops:
 
     def prefill_attention_tcgen05(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tiles,
                                   cu_q: torch.Tensor, kv_len: torch.Tensor, slots: torch.Tensor,
-                                  page_table: torch.Tensor, n_kv: int, scale: float) -> torch.Tensor:
+                                  page_table: torch.Tensor, n_kv: int, scale: float, n_splits: int = 1) -> torch.Tensor:
         """The same as ``prefill_attention`` on the tcgen05 tensor cores: head size 128 or 64 and an even number
-        of query heads per key/value head."""
+        of query heads per key/value head.  ``n_splits`` > 1 shares the keys of every tile out over that many
+        blocks (a short chunk after a long history would otherwise keep few SMs busy for long)."""
         self._act(q, "q")
         n, n_heads, d = q.shape
         tile_seq, tile_row, n_tiles = tiles
         out = self.empty(n, n_heads * d)
+        scratch = self.empty(n_splits * n * n_heads * (d + 2), dtype=torch.float32) if n_splits > 1 else None
         check(self.lib.cpm_prefill_attention_tcgen05(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(tile_seq),
                                                      _ptr(tile_row), n_tiles, _ptr(cu_q), _ptr(kv_len), _ptr(slots),
                                                      _ptr(page_table), page_table.shape[1], n, k_cache.shape[0],
-                                                     n_heads, n_kv, d, float(scale), _stream()),
+                                                     n_heads, n_kv, d, float(scale), _ptr(scratch), n_splits, _stream()),
               f"tcgen05 prefill attention (head_dim {d})")
         return out
+
+    def prefill_key_shares(self, q_lens, max_kv_len: int, n_heads: int) -> int:
+        """How many blocks share the keys of a query tile in the tcgen05 attention: one, unless the step's 128-token
+        tiles times head pairs leave most SMs idle and there are enough keys (at least 8 steps of 128 per share)."""
+        blocks = sum((int(n) + 127) // 128 for n in q_lens) * max(1, n_heads // 2)
+        steps = (int(max_kv_len) + 127) // 128
+        if blocks * 2 > self.sm_count or steps < 16:
+            return 1
+        return max(1, min(self.sm_count // blocks, steps // 8, 16))
 
     def attention_tcgen05_error(self) -> int:
         """Error code the tcgen05 attention kernel recorded since the last call (0 = none); synchronises."""

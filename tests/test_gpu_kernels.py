@@ -486,7 +486,10 @@ def test_tcgen05_prefill_attention_rescales_and_long_history(d):
     cu2 = torch.tensor([0, tail], dtype=torch.int32).cuda()
     tr2 = list(range(0, tail, TR))
     tiles2 = (torch.zeros(len(tr2), dtype=torch.int32).cuda(), torch.tensor(tr2, dtype=torch.int32).cuda(), len(tr2))
-    got2 = ops.prefill_attention_tcgen05(q[n - tail:].contiguous(), lane.k, lane.v, tiles2, cu2, kv_len, sl, lane.page_table,
-                                         n_kv, scale)
-    assert ops.attention_tcgen05_error() == 0
-    assert _err(got2, want[n - tail:]) < KTOL["bfloat16"]
+    for shares in (1, 2, 5, 16, 40):                               # the keys of a tile shared out over several blocks
+        got2 = ops.prefill_attention_tcgen05(q[n - tail:].contiguous(), lane.k, lane.v, tiles2, cu2, kv_len, sl, lane.page_table,
+                                             n_kv, scale, n_splits=shares)
+        assert ops.attention_tcgen05_error() == 0
+        assert _err(got2, want[n - tail:]) < KTOL["bfloat16"], shares
+    # two tiles of 16 head pairs leave most SMs idle: the keys are shared out; a whole 2,048-token prompt is not
+    assert 1 < ops.prefill_key_shares([tail], n, 32) <= ops.sm_count // 32 and ops.prefill_key_shares([2048], 2048, 32) == 1
