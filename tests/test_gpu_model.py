@@ -180,3 +180,40 @@ def test_long_prompts_through_the_tcgen05_kernels(model_folders, dtype):
     st2.close(s3)
     st.ops.raise_on_kernel_error()
     st.cache.check_consistent()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_random_configurations(tmp_path, dtype):
+    """A dozen configurations drawn at random (head sizes in steps of 16 up to 160, one to three key-value
+    heads with one to eight query heads each, widths and vocabularies that are no power of two, one to three
+    layers, tied or untied head): a prompt, chunked or whole, then five tokens one by one, against the plain
+    implementation."""
+    import random
+
+    from cpmcu_b200.engine import SequenceStep
+
+    rng = random.Random(20)
+    for case in range(12):
+        d = rng.choice([16, 32, 48, 64, 80, 96, 128, 160])
+        kv = rng.choice([1, 2, 3])
+        heads = kv * rng.choice([1, 2, 3, 4, 8])
+        hidden = rng.choice([40, 64, 72, 96, 128, 200, 256])
+        vocab = rng.choice([97, 300, 777, 1024])
+        cfgd = {"architectures": ["MiniCPMForCausalLM"], "num_hidden_layers": rng.choice([1, 2, 3]), "hidden_size": hidden,
+                "num_attention_heads": heads, "num_key_value_heads": kv, "head_dim": d,
+                "intermediate_size": rng.choice([24, 56, 100, 176, 320]), "vocab_size": vocab,
+                "max_position_embeddings": 4096, "rms_norm_eps": rng.choice([1e-5, 1e-6]),
+                "rope_theta": rng.choice([1e4, 1e6]), "scale_emb": rng.choice([1, 7]),
+                "dim_model_base": rng.choice([hidden, 32]), "scale_depth": rng.choice([1.0, 1.4]),
+                "tie_word_embeddings": rng.choice([True, False])}
+        n = rng.choice([3, 70, 200, 330])
+        folder = helpers.make_folder(cfgd, str(tmp_path / f"c{case}"), case, dtype, std=0.05)
+        cfg, st = _stepper(folder, dtype, max_tokens=1024, chunk_tokens=rng.choice([64, 2048]))
+        ids = helpers.random_ids(vocab, n, case)
+        slot = st.open(1)[0]
+        cut = max(1, n - 5)
+        rows = [st.step([SequenceStep(slot, ids[:cut], list(range(cut)))])]
+        for i in range(cut, n):
+            rows.append(st.step([SequenceStep(slot, ids[i:i + 1], [0])]))
+        helpers.check_rows(torch.cat(rows), folder, ids, range(n), dtype, (case, cfgd))
+        st.ops.raise_on_kernel_error()
