@@ -58,6 +58,32 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
+// Two-wide fp32 arithmetic and the three-input maximum of sm_100: the softmax threads are short of issue
+// slots, and these halve the instructions for scaling, summing and the row maximum.
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    unsigned long long ra, rb, rc, rd;
+    float2 d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rc) : "f"(c.x), "f"(c.y));
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(rd) : "l"(ra), "l"(rb), "l"(rc));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+    return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    unsigned long long ra, rb, rd;
+    float2 d;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(ra) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(rb) : "f"(b.x), "f"(b.y));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(rd) : "l"(ra), "l"(rb));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(d.x), "=f"(d.y) : "l"(rd));
+    return d;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -262,7 +288,7 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 #pragma unroll
             for (int c = 0; c < 4; ++c)
 #pragma unroll
-                for (int e = 0; e < 32; ++e) mx = fmaxf(mx, __uint_as_float(v[c][e]));
+                for (int e = 0; e < 32; e += 2) mx = max3(mx, __uint_as_float(v[c][e]), __uint_as_float(v[c][e + 1]));
             const float m_new = mx * scale_log2;
             const bool grow = m_new > m_ref + kRescaleThreshold || (m_ref == -INFINITY && m_new > -INFINITY);
             if (__any_sync(0xffffffffu, grow)) {
@@ -282,20 +308,22 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
                 if (grow) m_ref = m_new;
             }
             const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-            float sum = 0.f;
+            float2 sum2 = make_float2(0.f, 0.f);
+            const float2 scale2 = make_float2(scale_log2, scale_log2), minus_m2 = make_float2(-m_use, -m_use);
 #pragma unroll
             for (int c = 0; c < 2; ++c) {
                 uint32_t packed[32];
 #pragma unroll
                 for (int e = 0; e < 32; ++e) {
-                    const float p0 = ex2(fmaf(__uint_as_float(v[2 * c + (e >> 4)][(2 * e) & 31]), scale_log2, -m_use));
-                    const float p1 = ex2(fmaf(__uint_as_float(v[2 * c + (e >> 4)][(2 * e + 1) & 31]), scale_log2, -m_use));
-                    sum += p0 + p1;
-                    packed[e] = pack_bf16(p0, p1);
+                    const float2 x = fma2(make_float2(__uint_as_float(v[2 * c + (e >> 4)][(2 * e) & 31]),
+                                                      __uint_as_float(v[2 * c + (e >> 4)][(2 * e + 1) & 31])), scale2, minus_m2);
+                    const float2 pp = make_float2(ex2(x.x), ex2(x.y));
+                    sum2 = add2(sum2, pp);
+                    packed[e] = pack_bf16(pp.x, pp.y);
                 }
                 tmem_store_32cols(s_addr + c * 32, packed);
             }
-            l += sum;
+            l += sum2.x + sum2.y;
             tmem_store_wait();
             tcgen05_fence_before();
             __syncwarp();
