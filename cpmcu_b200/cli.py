@@ -59,6 +59,13 @@ def create_cli_parser() -> argparse.ArgumentParser:
     g.add_argument("--dtype", type=str, default="bfloat16", choices=["bfloat16", "float32"],
                    help="Model dtype (default: bfloat16)")
 
+    g.add_argument("--random-weights", "--random_weights", type=int, default=None, metavar="SEED",
+                   help="Write config.json and model.safetensors with seeded random weights into --model-path "
+                        "from the configuration given by --config, then generate from that folder")
+    g.add_argument("--config", type=str, default=None, help="config.json for --random-weights")
+    g.add_argument("--dense", default=False, **flag,
+                   help="Ignore the configuration's sparse_config and attend to all keys (default: False)")
+
     g = parser.add_argument_group("System Configuration")
     g.add_argument("--cuda-graph", "--cuda_graph", default=True, **flag, help="Use CUDA graph optimization (default: True)")
     g.add_argument("--memory-limit", "--memory_limit", type=float, default=0.9, help="Memory limit (default: 0.9)")
@@ -97,11 +104,37 @@ def make_prompts(args, tokenizer) -> List[List[int]]:
     return [list(tokenizer(text, add_special_tokens=False)["input_ids"])]
 
 
+def write_random_folder(config_path: Optional[str], out_dir: str, seed: int, dtype: str) -> str:
+    """The random-weights mode: a model folder from a configuration file and a seed."""
+    import json
+
+    from .loading import parse_dtype
+    from .models.model import Model
+    from .registry import architecture
+    from .weights import write_model_folder
+
+    if not config_path:
+        raise ValueError("--random-weights needs --config (a config.json to take the sizes from)")
+    with open(config_path, "r", encoding="utf-8") as f:
+        raw = json.load(f)
+    names = raw.get("architectures") or []
+    if not names:
+        raise ValueError(f"{config_path} names no architecture")
+    arch = architecture(names[0])
+    config = arch.config_class.from_dict(raw)
+    specs = Model(arch.model_spec(config), None).weight_specs()
+    folder = write_model_folder(config, specs, out_dir, int(seed), parse_dtype(dtype))
+    print(f"[cpmcu_b200] wrote random weights (seed {seed}) to {folder}", file=sys.stderr)
+    return folder
+
+
 def run_generation(args) -> int:
     from .llm import LLM
 
+    if args.random_weights is not None:
+        write_random_folder(args.config, args.model_path, args.random_weights, args.dtype)
     tokenizer = None if args.prompt_ids else _load_tokenizer(args.model_path)
-    llm = LLM(args.model_path, memory_limit=args.memory_limit, chunk_length=args.chunk_length, dtype=args.dtype,
+    llm = LLM(args.model_path, apply_sparse=not args.dense, memory_limit=args.memory_limit, chunk_length=args.chunk_length, dtype=args.dtype,
               cuda_graph=args.cuda_graph, temperature=args.temperature, random_seed=args.random_seed,
               top_p=args.top_p, max_batch=args.max_batch, max_tokens=args.max_tokens)
     llm.tokenizer = tokenizer

@@ -36,9 +36,14 @@ class LLM:
     def __init__(self, path: str, memory_limit: float = 0.8, chunk_length: int = 1024, dtype=None,
                  cuda_graph: bool = False, temperature: float = 0.0, random_seed: Optional[int] = None,
                  top_p: float = 1.0, max_batch: int = 64, max_tokens: Optional[int] = None,
-                 max_seq_tokens: Optional[int] = None, device: str = "cuda:0"):
+                 max_seq_tokens: Optional[int] = None, device: str = "cuda:0", apply_sparse: bool = True):
+        """``apply_sparse`` False runs a model whose configuration has a ``sparse_config`` with dense attention
+        (the reference's switch of the same name, cpmcu/llm.py:32, chooses the other way round)."""
         self.path = path
         self.arch, self.config = load_config(path)
+        if not apply_sparse and getattr(self.config, "sparse_config", None) is not None:
+            import dataclasses
+            self.config = dataclasses.replace(self.config, sparse_config=None)
         self.dtype = parse_dtype(dtype if dtype is not None else getattr(self.config, "torch_dtype", "bfloat16"))
         self.device = device
         self.memory_limit = float(memory_limit)

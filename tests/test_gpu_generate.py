@@ -133,6 +133,33 @@ def test_stream_and_cli(model_folders):
     assert out.stdout.strip() == "[0] " + " ".join(map(str, toks))
 
 
+def test_cli_random_weights_mode_and_dense_switch(tmp_path):
+    """The command line's random-weights mode writes a model folder from a config.json and a seed and generates
+    from it; with --dense the configuration's sparse attention is left out, and the tokens are those of the
+    plain implementation on the same folder with the sparse_config taken away."""
+    import json
+
+    cfgd = configs.tiny_b()
+    cfg_path, folder = str(tmp_path / "config.json"), str(tmp_path / "model")
+    with open(cfg_path, "w") as f:
+        json.dump(cfgd, f)
+    prompt = helpers.random_ids(cfgd["vocab_size"], 150, 4)              # longer than dense_len: sparse would differ
+    out = subprocess.run([sys.executable, "-m", "cpmcu_b200.cli", "--random-weights", "9", "--config", cfg_path,
+                          "--model-path", folder, "--dtype", "float32", "--dense", "true", "--prompt-ids",
+                          ",".join(map(str, prompt)), "--num-generate", "5", "--use-stream", "false", "--ignore-eos", "true",
+                          "--max-tokens", "512"], cwd=ROOT, capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr
+    assert sorted(os.listdir(folder)) == ["config.json", "model.safetensors"]
+    got = [int(x) for x in out.stdout.strip().split("] ")[1].split()]
+    cfg, w = helpers.read_folder(folder)
+    cfg = dict(cfg)
+    cfg.pop("sparse_config", None)
+    ids = list(prompt)
+    for tok in got:
+        assert tok == plain.sample_token(plain.forward(cfg, w, ids)[-1], 0.0, 0.0)
+        ids.append(tok)
+
+
 def test_trace_run_program(model_folders, tmp_path):
     """bin/trace_run end to end: two requests start together, the shorter ends first."""
     import json
