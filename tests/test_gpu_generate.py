@@ -189,3 +189,42 @@ def test_trace_run_program(model_folders, tmp_path):
         got = torch.from_numpy(np.fromfile(out_dir / f"{t + 1}.f32", dtype="<f4").reshape(-1, 512))
         want = [wa[30 + t]] + ([wb[70 + t]] if t < 5 else [])
         assert helpers.rel_err(got, torch.stack(want)) < helpers.TOL["float32"]
+
+
+@pytest.mark.parametrize("name,make,dtype", [("tiny_b", configs.tiny_b, "bfloat16"), ("tiny_a", configs.tiny_a, "float32")])
+def test_many_random_batches_leave_the_cache_clean(model_folders, name, make, dtype):
+    """Forty batches of random sizes (more prompts than the batch limit, lengths from 1 to 300, stop tokens, greedy
+    and temperature, one to thirty new tokens): every result obeys its stop rule, no slot or page is lost, and
+    greedy float32 tokens are those of the plain implementation."""
+    import random
+
+    from cpmcu_b200 import LLM
+
+    cfgd = make()
+    folder = model_folders(name, cfgd, 0, dtype)
+    llm = LLM(folder, dtype=dtype, cuda_graph=True, max_tokens=64 * 160, max_batch=16, chunk_length=64)
+    cfg, w = helpers.read_folder(folder)
+    rng = random.Random(5)
+    vocab = cfgd["vocab_size"]
+    for b in range(40):
+        n = rng.randint(1, 24)
+        prompts = [helpers.random_ids(vocab, rng.choice([1, 2, 5, 17, 63, 64, 65, 100, 130, 300]), rng.randint(0, 10 ** 6))
+                   for _ in range(n)]
+        gen = rng.choice([1, 2, 7, 30])
+        temp = rng.choice([0.0, 0.0, 0.8])
+        stops = [rng.randrange(vocab) for _ in range(rng.choice([0, 3, 40]))]
+        res = llm.generate_batch(prompts, generation_length=gen, terminators=stops, temperature=temp)
+        assert len(res) == n
+        for r in res:
+            assert 1 <= len(r.tokens) <= gen
+            assert all(t not in stops for t in r.tokens[:-1])
+            assert len(r.tokens) == gen or r.tokens[-1] in stops
+        llm.cache.check_consistent()
+        assert llm.cache.slots.n_held == 1                      # only the decode runner's scratch sequence
+        if temp == 0.0 and dtype == "float32" and b % 8 == 0:
+            i = rng.randrange(n)
+            ids = list(prompts[i])
+            for tok in res[i].tokens:
+                assert tok == plain.sample_token(plain.forward(cfg, w, ids)[-1], 0.0, 0.0), (b, i, len(ids))
+                ids.append(tok)
+    llm.ops.raise_on_kernel_error()
