@@ -44,9 +44,12 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
 
 // The second launch bound (one block per SM suffices) matters: it lets the compiler spend registers on
 // keeping the loads of eight K steps in flight instead of saving them for occupancy; with it the kernel
-// went from 4.5 to 6.1 TB/s on the down projection.
+// went from 4.5 to 6.1 TB/s on the down projection.  With two tiles of token columns (9 to 16 rows) the
+// kernel would take 166 registers and lose the second block per SM, so there the bound is two blocks (53
+// instead of 59 us on the gate_up shape, which is what cuBLAS with the activation kernel takes: the engine
+// leaves more than 8 rows to cuBLAS).
 template <int NT, int EPI, int kSkinnyWarps>
-__global__ void __launch_bounds__(kSkinnyWarps * 32, 1)
+__global__ void __launch_bounds__(kSkinnyWarps * 32, NT == 1 ? 1 : 2)
 skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, void* __restrict__ out, int M, int N, int K,
                    float alpha, int prefetch_lines) {
     constexpr int MT = NT * 8;                          // token columns
