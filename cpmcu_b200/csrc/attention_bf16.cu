@@ -443,11 +443,11 @@ static int launch_decode(const void* q, const void* k_cache, const void* v_cache
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    cpm_launch(kern, grid, kDecodeWarps * 32, smem, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
+    cpm_launch(kLaunchAttention, kern, grid, kDecodeWarps * 32, smem, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
                kv_len, slots, page_table, max_pages, part_o, part_ml, (bf16*)out, n_heads, n_kv, m_tiles, n_splits,
                scale * 1.4426950408889634f);
     if (n_splits > 1)
-        cpm_launch(combine_splits_kernel, dim3(n_heads, n_seqs), D >= 128 ? 128 : 64, 0, stream, (const float*)part_o,
+        cpm_launch(kLaunchCombine, combine_splits_kernel, dim3(n_heads, n_seqs), D >= 128 ? 128 : 64, 0, stream, (const float*)part_o,
                    (const float*)part_ml, (bf16*)out, n_heads, n_kv, m_tiles, n_splits, (int)D);
     return launch_status();
 }

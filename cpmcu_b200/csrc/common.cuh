@@ -120,11 +120,18 @@ __device__ __forceinline__ int64_t value_offset(int page, int kv_head, int dim, 
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
-extern int g_cpm_pdl;      // 1: kernels of the decode chain are launched with the attribute (default 0)
+// Which kernels are launched with the attribute: a mask over the classes below (bit = 1 << class).  Measured on
+// the 8B decode step (batch 8, 3.64 ms without): norms and products 3.47 ms, with the rotary kernel and the decode
+// attention as well 3.45 ms; the kernel that combines the attention's shares must stay out (with it the gain is
+// gone: 3.66 ms), and so does everything else (embedding, sampling, the step's bookkeeping).
+enum LaunchClass : int { kLaunchOther = 0, kLaunchNorm = 1, kLaunchProduct = 2, kLaunchRope = 3, kLaunchAttention = 4,
+                         kLaunchCombine = 5 };
+constexpr int kDefaultPdlMask = (1 << kLaunchNorm) | (1 << kLaunchProduct) | (1 << kLaunchRope) | (1 << kLaunchAttention);
+extern int g_cpm_pdl;      // the mask in force (cpm_set_pdl)
 
 template <typename... KArgs, typename... Args>
-static inline void cpm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
-                              Args... args) {
+static inline void cpm_launch(LaunchClass cls, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                              cudaStream_t stream, Args... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
     cfg.blockDim = block;
@@ -134,7 +141,7 @@ static inline void cpm_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, s
     attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
-    cfg.numAttrs = g_cpm_pdl ? 1 : 0;
+    cfg.numAttrs = ((g_cpm_pdl >> (int)cls) & 1) ? 1 : 0;
     cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 

@@ -3,11 +3,11 @@
 // All arithmetic is fp32; only loads and stores touch the storage type.
 #include "common.cuh"
 
-int g_cpm_pdl = 0;
+int g_cpm_pdl = kDefaultPdlMask;
 
-// Switches programmatic dependent launch of the decode chain on or off.  Off by default: measured on
-// the 8B decode step, the earlier start of a kernel did not pay for the dearer launch.
-CPM_API void cpm_set_pdl(int enabled) { g_cpm_pdl = enabled ? 1 : 0; }
+// Which classes of kernels are launched with programmatic dependent launch (a mask over LaunchClass; 0: none;
+// negative: the default mask).
+CPM_API void cpm_set_pdl(int mask) { g_cpm_pdl = mask < 0 ? kDefaultPdlMask : mask; }
 
 // ---------------------------------------------------------------------------
 // Embedding rows times a scale, into the fp32 residual stream.
@@ -31,9 +31,9 @@ CPM_API int cpm_embed_rows(const int* ids, const void* table, float* out, int n_
     if (n_tokens <= 0) return CPM_OK;
     const int threads = hidden >= 1024 ? 256 : 128;
     if (dtype == CPM_BF16)
-        cpm_launch(embed_rows_kernel<bf16>, n_tokens, threads, 0, stream, ids, (const bf16*)table, out, hidden, scale);
+        cpm_launch(kLaunchOther, embed_rows_kernel<bf16>, n_tokens, threads, 0, stream, ids, (const bf16*)table, out, hidden, scale);
     else
-        cpm_launch(embed_rows_kernel<float>, n_tokens, threads, 0, stream, ids, (const float*)table, out, hidden, scale);
+        cpm_launch(kLaunchOther, embed_rows_kernel<float>, n_tokens, threads, 0, stream, ids, (const float*)table, out, hidden, scale);
     return launch_status();
 }
 
@@ -127,7 +127,7 @@ static int launch_add_rmsnorm(float* x, const void* delta, float alpha, const vo
         if (e != cudaSuccess) return (int)e;
     }
     const int threads = hidden >= 4096 ? 512 : (hidden >= 1024 ? 256 : 128);
-    cpm_launch(kern, n_rows, threads, smem, stream, x, (const T*)delta, alpha, (const W*)w, (T*)y, rows, hidden, eps, write_back);
+    cpm_launch(kLaunchNorm, kern, n_rows, threads, smem, stream, x, (const T*)delta, alpha, (const W*)w, (T*)y, rows, hidden, eps, write_back);
     return launch_status();
 }
 
@@ -394,7 +394,7 @@ CPM_API int cpm_rope_store(const void* qkv, void* q_out, void* k_cache, void* v_
         const int threads = items >= 256 ? 256 : ((items + 31) / 32) * 32;
         dim3 vgrid(n_tokens, (n_all + heads_per_block - 1) / heads_per_block);
         if (vgrid.y > 65535) return CPM_BAD_ARGUMENT;
-        cpm_launch(rope_store_vec_kernel, vgrid, threads, (size_t)d * sizeof(float), stream, (const bf16*)qkv, (bf16*)q_out,
+        cpm_launch(kLaunchRope, rope_store_vec_kernel, vgrid, threads, (size_t)d * sizeof(float), stream, (const bf16*)qkv, (bf16*)q_out,
                    (bf16*)k_cache, (bf16*)v_cache, positions, token_seq, slots, page_table, max_pages, inv_freq, magnitude,
                    n_heads, n_kv, d, heads_per_block);
         return launch_status();
@@ -404,10 +404,10 @@ CPM_API int cpm_rope_store(const void* qkv, void* q_out, void* k_cache, void* v_
     const int threads = d >= 128 ? 64 : 32;
     const size_t smem = (size_t)(rot_dim > 0 ? rot_dim : 2) * sizeof(float);
     if (dtype == CPM_BF16)
-        cpm_launch(rope_store_kernel<bf16>, grid, threads, smem, stream, (const bf16*)qkv, (bf16*)q_out, (bf16*)k_cache,
+        cpm_launch(kLaunchRope, rope_store_kernel<bf16>, grid, threads, smem, stream, (const bf16*)qkv, (bf16*)q_out, (bf16*)k_cache,
             (bf16*)v_cache, positions, token_seq, slots, page_table, max_pages, inv_freq, magnitude, n_heads, n_kv, d, rot_dim);
     else
-        cpm_launch(rope_store_kernel<float>, grid, threads, smem, stream, (const float*)qkv, (float*)q_out, (float*)k_cache,
+        cpm_launch(kLaunchRope, rope_store_kernel<float>, grid, threads, smem, stream, (const float*)qkv, (float*)q_out, (float*)k_cache,
             (float*)v_cache, positions, token_seq, slots, page_table, max_pages, inv_freq, magnitude, n_heads, n_kv, d, rot_dim);
     return launch_status();
 }
@@ -435,6 +435,6 @@ __global__ void advance_decode_kernel(int* __restrict__ ids, int* __restrict__ p
 CPM_API int cpm_advance_decode(int* ids, int* positions, int* kv_len, int* step_key, const int* sampled,
                                const int* live, int n, cudaStream_t stream) {
     if (n <= 0) return CPM_OK;
-    cpm_launch(advance_decode_kernel, (n + 127) / 128, 128, 0, stream, ids, positions, kv_len, step_key, sampled, live, n);
+    cpm_launch(kLaunchOther, advance_decode_kernel, (n + 127) / 128, 128, 0, stream, ids, positions, kv_len, step_key, sampled, live, n);
     return launch_status();
 }

@@ -138,7 +138,7 @@ static int launch_skinny_epi(const void* W, const void* X, void* out, int M, int
                              cudaStream_t stream) {
     // Few row tiles (a narrow output): more warps per tile, so that enough loads are in flight.
     const unsigned blocks = (unsigned)((N + 15) / 16);
-    cpm_launch(skinny_gemm_kernel<NT, EPI, 8>, blocks, 256, 0, stream, (const bf16*)W, (const bf16*)X, out, M, N, K, alpha, g_skinny_prefetch_lines);
+    cpm_launch(kLaunchProduct, skinny_gemm_kernel<NT, EPI, 8>, blocks, 256, 0, stream, (const bf16*)W, (const bf16*)X, out, M, N, K, alpha, g_skinny_prefetch_lines);
     return launch_status();
 }
 

@@ -131,7 +131,7 @@ CPM_API int cpm_sample_rows(const float* logits, int64_t ld, int n_rows, int voc
     if (n_rows <= 0) return CPM_OK;
     if (vocab <= 0) return CPM_BAD_ARGUMENT;
     if (temperature && (!seq_key || !step_key)) return CPM_BAD_ARGUMENT;
-    cpm_launch(sample_rows_kernel, n_rows, kSampleThreads, 0, stream, logits, ld, vocab, out, temperature, top_p, seed,
+    cpm_launch(kLaunchOther, sample_rows_kernel, n_rows, kSampleThreads, 0, stream, logits, ld, vocab, out, temperature, top_p, seed,
                seq_key, step_key);
     return launch_status();
 }

@@ -76,8 +76,8 @@ def load() -> ctypes.CDLL:
             raise KernelLibraryError(f"the CUDA kernel library {path} could not be loaded: {e}") from None
         lib.cpm_set_pdl.argtypes = [c_int]
         lib.cpm_set_pdl.restype = None
-        if os.environ.get("CPMCU_PDL", "0") == "1":
-            lib.cpm_set_pdl(1)
+        if os.environ.get("CPMCU_PDL") is not None:      # a mask over the kernel classes; 0 switches it off
+            lib.cpm_set_pdl(int(os.environ["CPMCU_PDL"]))
         lib.cpm_set_skinny_prefetch_lines.argtypes = [c_int]
         lib.cpm_set_skinny_prefetch_lines.restype = None
         if os.environ.get("CPMCU_SKINNY_PREFETCH"):
