@@ -331,7 +331,7 @@ __global__ void rope_store_vec_kernel(const bf16* __restrict__ qkv, bf16* __rest
     __syncthreads();
 
     int64_t k_base = 0, v_base = 0;
-    if (k_cache) {
+    if (k_cache && h_end > n_heads) {                            // only blocks with key or value heads look the page up
         const int slot = slots[token_seq[t]];
         const int page = page_table[(int64_t)slot * max_pages + pos / kPageTokens];
         k_base = page_row_offset(page, 0, pos % kPageTokens, n_kv, d);
