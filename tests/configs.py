@@ -76,3 +76,15 @@ def tiny_e() -> dict:
         "rope_theta": 50000.0, "max_position_embeddings": 2048, "rms_norm_eps": 2e-6,
         "scale_emb": 6, "dim_model_base": 96, "scale_depth": 1.1, "tie_word_embeddings": False,
     }
+
+
+def tiny_f() -> dict:
+    """Head size 64 with four query heads per key-value head: the tcgen05 attention's other head size, which the
+    engine takes from 1,024 keys on."""
+    return {
+        "architectures": ["MiniCPMForCausalLM"], "model_type": "minicpm",
+        "num_hidden_layers": 2, "hidden_size": 128, "num_attention_heads": 8, "num_key_value_heads": 2,
+        "head_dim": 64, "intermediate_size": 96, "vocab_size": 500,
+        "rope_theta": 10000.0, "max_position_embeddings": 4096, "rms_norm_eps": 1e-5,
+        "scale_emb": 3, "dim_model_base": 64, "scale_depth": 1.3, "tie_word_embeddings": True,
+    }

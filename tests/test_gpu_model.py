@@ -217,3 +217,26 @@ def test_random_configurations(tmp_path, dtype):
             rows.append(st.step([SequenceStep(slot, ids[i:i + 1], [0])]))
         helpers.check_rows(torch.cat(rows), folder, ids, range(n), dtype, (case, cfgd))
         st.ops.raise_on_kernel_error()
+
+
+@pytest.mark.parametrize("name,make,seed", [("tiny_e", configs.tiny_e, 6), ("tiny_f", configs.tiny_f, 7)])
+def test_short_chunks_after_a_long_history(model_folders, name, make, seed):
+    """A prompt of 2,300 tokens in chunks of 256 (bf16): from 1,024 keys on the head-size-64 model changes to the
+    tcgen05 attention, and from 2,048 keys on the keys of a chunk's tiles are shared out over several blocks and
+    combined by a second kernel.  Logits at places spread over the prompt, then ten decoded tokens."""
+    from cpmcu_b200.engine import SequenceStep
+
+    dtype = "bfloat16"
+    folder = model_folders(name, make(), seed, dtype)
+    cfg, st = _stepper(folder, dtype, max_tokens=4096, chunk_tokens=256)
+    n = 2300
+    ids = helpers.random_ids(cfg.vocab_size, n + 10, 70 + seed)
+    places = [0, 255, 256, 1023, 1024, 1279, 2047, 2048, 2100, 2299]
+    assert st.ops.prefill_key_shares([256], 2304, cfg.num_attention_heads) > 1
+    slot = st.open(1)[0]
+    got = st.step([SequenceStep(slot, ids[:n], places)])
+    helpers.check_rows(got, folder, ids, places, dtype, (name, "prompt"))
+    tail = torch.cat([st.step([SequenceStep(slot, ids[i:i + 1], [0])]) for i in range(n, n + 10)])
+    helpers.check_rows(tail, folder, ids, range(n, n + 10), dtype, (name, "decoded"))
+    st.close(slot)
+    st.ops.raise_on_kernel_error()
