@@ -493,3 +493,65 @@ def test_tcgen05_prefill_attention_rescales_and_long_history(d):
         assert _err(got2, want[n - tail:]) < KTOL["bfloat16"], shares
     # two tiles of 16 head pairs leave most SMs idle: the keys are shared out; a whole 2,048-token prompt is not
     assert 1 < ops.prefill_key_shares([tail], n, 32) <= ops.sm_count // 32 and ops.prefill_key_shares([2048], 2048, 32) == 1
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_pool_keys_and_select_blocks(dtype):
+    """InfLLM-v2 key pooling (in two steps, so that windows straddle the step boundary) and block selection for
+    every query of a 700-token sequence, at sizes no test model has (head size 64, two key-value heads with four
+    query heads each, windows of 16 keys every 8, blocks of 64, four blocks chosen, a local window of two): the
+    pooled keys against the plain means, the block lists against the plain selection (in bf16 where the choice
+    is not a near tie)."""
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.parts import StepContext
+    from cpmcu_b200.parts.base import CacheNeeds
+
+    ops = _ops(dtype)
+    n_heads, n_kv, d, n = 8, 2, 64, 700
+    sparse = {"kernel_size": 16, "kernel_stride": 8, "block_size": 64, "init_blocks": 1, "topk": 4, "window_size": 128,
+              "dense_len": 0}
+    cache = Cache([CacheNeeds(kv_heads=n_kv, head_dim=d, pooled_stride=8, pooled_kernel=16)], max_tokens=64 * 16,
+                  dtype=DT[dtype], device="cuda:0")
+    junk = cache.open_sequence()
+    cache.reserve(junk, 130)                                 # so that logical and physical pages differ
+    slot = cache.open_sequence()
+    cache.reserve(slot, n)
+    cache.sync()
+    lane = cache.lane(0)
+    g = torch.Generator().manual_seed(23)
+    qkv = torch.randn(n, (n_heads + 2 * n_kv) * d, generator=g).to(DT[dtype])
+    rows = qkv.float().view(n, n_heads + 2 * n_kv, d)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32).cuda()
+    sl = i32([slot])
+    q_all = []
+    for lo, hi in ((0, 300), (300, n)):
+        m = hi - lo
+        ctx = StepContext(m, 1, False, False, [m], [hi], [slot], m, hi, i32([0] * m), i32(list(range(lo, hi))), i32([0] * m),
+                          i32([0, m]), i32([hi]), sl, cache)
+        q_all.append(ops.rope_store(qkv[lo:hi].cuda(), n_heads, n_kv, d, ctx.positions, ctx.token_seq, sl, lane.page_table,
+                                    lane.k, lane.v, None, 1.0, 0))
+        ops.pool_keys(ctx, lane, n_kv, d, 16, 8)
+    want_ck = plain.compress_keys(rows[:, n_heads:n_heads + n_kv], 16, 8)            # [n_c, kv, d]
+    n_c = want_ck.shape[0]
+    pages = cache.groups[0].pages_of_slot[slot]
+    got_ck = torch.stack([lane.pooled[pages[i // 8], :, i % 8].float().cpu() for i in range(n_c)])
+    assert _err(got_ck, want_ck) < 1e-6                      # pooled keys are kept in fp32 in both paths
+    ctx = StepContext(n, 1, False, False, [n], [n], [slot], n, n, i32([0] * n), i32(list(range(n))), i32([0] * n),
+                      i32([0, n]), i32([n]), sl, cache)
+    q = torch.cat(q_all)
+    scale = 1 / math.sqrt(d)
+    lists, bs = ops.select_blocks(ctx, q, lane, n_kv, scale, sparse)
+    assert bs == 64
+    lists = lists.cpu()
+    checked = 0
+    for p in range(n):
+        margins = []
+        want = plain.select_blocks(rows[p, :n_heads], want_ck, p, scale, sparse, margins)
+        for j in range(n_kv):
+            if dtype == "bfloat16" and margins[j] < 0.02:
+                continue
+            row = lists[p, j].tolist()                      # block ids up to the first negative entry
+            got = sorted(row[:next((i for i, b in enumerate(row) if b < 0), len(row))])
+            assert got == want[j], (p, j, got, want[j])
+            checked += 1
+    assert checked > (n * n_kv) * (0.99 if dtype == "float32" else 0.8)
