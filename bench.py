@@ -245,6 +245,34 @@ def time_e2e(cfg, model, steps: int, batch: int):
     }
 
 
+def step_launches(name: str, batch: int, ctx: int, layers: int, reps: int) -> int:
+    """A few eager steps of a model with few layers of the benchmark's sizes, one kernel launch after the other, for
+    a profiler's launch list: decode_step = one token for each of ``batch`` sequences that hold ``ctx`` tokens;
+    prefill_step = a prompt of ``ctx`` tokens."""
+    import torch
+    from cpmcu_b200.engine import SequenceStep
+
+    global CONTEXT
+    CONTEXT = max(CONTEXT, ctx + 64)
+    cfg, model, cache, stepper = build_engine(layers, batch * (ctx + 128) + 128, batch)
+    if name == "decode_step":
+        slots = stepper.open(batch)
+        for i, s in enumerate(slots):
+            stepper.step([SequenceStep(s, random_prompt(cfg.vocab_size, ctx, i), [])])
+        torch.cuda.synchronize()
+        for _ in range(max(1, reps)):
+            out = stepper.step([SequenceStep(s, [5], [0]) for s in slots])
+            torch.cuda.synchronize()
+    else:
+        for r in range(max(1, reps)):
+            slot = stepper.open(1)[0]
+            out = stepper.step([SequenceStep(slot, random_prompt(cfg.vocab_size, ctx, r), [ctx - 1])])
+            torch.cuda.synchronize()
+            stepper.close(slot)
+    print(json.dumps({"kernel": name, "batch": batch, "ctx": ctx, "layers": layers, "logits": list(out.shape)}))
+    return 0
+
+
 def kernel_bench(name: str, batch: int, ctx: int, rows: int, n: int, k: int, reps: int) -> int:
     """One kernel alone at the benchmark's shapes, timed inside a CUDA graph with rotating
     buffers larger than L2 (also the target of the ncu captures under profiles/)."""
@@ -337,7 +365,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="layers built (the full model has 32)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the e2e run")
-    ap.add_argument("--kernel", default=None, help="time one kernel alone: skinny_gemm, decode_attention, prefill_attention (tcgen05), prefill_attention_mma, gemm_tcgen05")
+    ap.add_argument("--kernel", default=None, help="time one kernel alone: skinny_gemm, decode_attention, prefill_attention (tcgen05), prefill_attention_mma, gemm_tcgen05; or run eager steps of a 2-layer model for a launch list: decode_step, prefill_step")
     ap.add_argument("--ctx", type=int, default=CONTEXT, help="--kernel: cached tokens per sequence (or prompt tokens)")
     ap.add_argument("--rows", type=int, default=8, help="--kernel skinny_gemm / gemm_tcgen05: rows of the activation")
     ap.add_argument("--n", type=int, default=4096, help="--kernel skinny_gemm: output features")
@@ -349,6 +377,8 @@ def main() -> int:
     if a.gpus != 1:
         print("bench.py: this library runs on one GPU; --gpus must be 1")
         return 2
+    if a.kernel in ("decode_step", "prefill_step"):
+        return step_launches(a.kernel, a.batch, a.ctx, a.layers if a.layers != FULL_LAYERS else 2, a.reps)
     if a.kernel:
         return kernel_bench(a.kernel, a.batch, a.ctx, a.rows, a.n, a.k, a.reps)
     a.warmup = max(3, a.warmup)
