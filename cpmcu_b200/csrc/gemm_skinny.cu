@@ -136,7 +136,6 @@ skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, void*
 template <int NT, int EPI>
 static int launch_skinny_epi(const void* W, const void* X, void* out, int M, int N, int K, float alpha,
                              cudaStream_t stream) {
-    // Few row tiles (a narrow output): more warps per tile, so that enough loads are in flight.
     const unsigned blocks = (unsigned)((N + 15) / 16);
     cpm_launch(kLaunchProduct, skinny_gemm_kernel<NT, EPI, 8>, blocks, 256, 0, stream, (const bf16*)W, (const bf16*)X, out, M, N, K, alpha, g_skinny_prefetch_lines);
     return launch_status();
