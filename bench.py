@@ -15,6 +15,7 @@ import os
 import statistics
 import subprocess
 import sys
+import tempfile
 import threading
 import time
 
@@ -106,12 +107,35 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
-def reference_arm() -> int:
-    """The reference cannot be installed offline here: its attention sources include
-    cute/tensor.hpp from the cutlass submodule, which is empty in the mounted tree."""
-    print(json.dumps({"impl": "reference",
-                      "unavailable": "pip install of the reference fails offline: src/cutlass submodule is empty "
-                                     "(flash_fwd_kernel.h:7: cute/tensor.hpp: No such file or directory)"}))
+def reference_arm(steps: int, warmup: int) -> int:
+    """Runs the unmodified reference, installed under baseline/_ref, through its own Python API in a process of
+    its own (baseline/run_reference.py; nothing of this package is on that path) and passes its JSON line on.
+    The install: a copy of the reference with its empty ``src/cutlass`` submodule folder filled from the CUTLASS
+    header tree that ships with an installed package, built with CPMCU_CUDA_ARCH=100 CPMCU_DTYPE=bf16."""
+    ref = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(ref, "cpmcu")):
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref holds no installed reference (see DESIGN.md "
+                          "for the install command; it needs the CUTLASS headers of an installed package)"}))
+        return 0
+    cfgd = dict(MODEL)
+    cfgd["rope_scaling"] = {"rope_type": "longrope", "long_factor": long_factors(64), "short_factor": [1.0] * 64,
+                            "original_max_position_embeddings": 32768}
+    env = dict(os.environ, PYTHONPATH=ref + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    cmd = [sys.executable, os.path.join(ROOT, "baseline", "run_reference.py"), "--model-json", json.dumps(cfgd),
+           "--steps", str(steps), "--warmup", str(max(3, warmup)), "--context", str(CONTEXT),
+           "--prefill-tokens", str(PREFILL_TOKENS), "--seed", str(SEED)]
+    try:
+        p = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=1500, cwd=tempfile.gettempdir())
+    except subprocess.TimeoutExpired:
+        print(json.dumps({"impl": "reference", "unavailable": "the reference run did not end within 1500 s"}))
+        return 0
+    line = next((l for l in reversed(p.stdout.splitlines()) if l.startswith("{") and '"impl"' in l), None)
+    if p.returncode != 0 or line is None:
+        err = [l for l in (p.stderr or p.stdout).splitlines() if l.strip()]
+        print(json.dumps({"impl": "reference", "unavailable": f"the reference run failed (exit {p.returncode}): "
+                          + (err[-1][:300] if err else "no output")}))
+        return 0
+    print(line)
     return 0
 
 
@@ -373,7 +397,7 @@ def main() -> int:
     ap.add_argument("--reps", type=int, default=5, help="--kernel: graph replays that are timed")
     a = ap.parse_args()
     if a.impl == "reference":
-        return reference_arm()
+        return reference_arm(a.steps, a.warmup)
     if a.gpus != 1:
         print("bench.py: this library runs on one GPU; --gpus must be 1")
         return 2

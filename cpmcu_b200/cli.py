@@ -8,7 +8,8 @@ has them; every flag has a ``--kebab-case`` and a ``--snake_case`` spelling.
 Options the reference has and this library leaves out belong to parts that are not
 built (draft models, quantized weights, the per-flag sparse-attention knobs: those come
 from the folder's config.json here).  Added: ``--prompt-ids`` (token ids, no tokenizer
-needed), ``--top-p``, ``--max-batch``, ``--max-tokens``.
+needed), ``--top-p``, ``--max-batch``, ``--max-tokens``, ``--plugin`` (a module that registers
+parts or an architecture of its own).
 """
 from __future__ import annotations
 
@@ -59,6 +60,9 @@ def create_cli_parser() -> argparse.ArgumentParser:
     g.add_argument("--dtype", type=str, default="bfloat16", choices=["bfloat16", "float32"],
                    help="Model dtype (default: bfloat16)")
 
+    g.add_argument("--plugin", type=str, default=None, action="append",
+                   help="Module to import before the model is built; it registers parts or an architecture the "
+                        "package does not know (may be given several times; also: environment variable CPMCU_PLUGINS)")
     g.add_argument("--random-weights", "--random_weights", type=int, default=None, metavar="SEED",
                    help="Write config.json and model.safetensors with seeded random weights into --model-path "
                         "from the configuration given by --config, then generate from that folder")
@@ -130,7 +134,10 @@ def write_random_folder(config_path: Optional[str], out_dir: str, seed: int, dty
 
 def run_generation(args) -> int:
     from .llm import LLM
+    from .registry import load_plugins
 
+    if args.plugin:
+        load_plugins(args.plugin)
     if args.random_weights is not None:
         write_random_folder(args.config, args.model_path, args.random_weights, args.dtype)
     tokenizer = None if args.prompt_ids else _load_tokenizer(args.model_path)

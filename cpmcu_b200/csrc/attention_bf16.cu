@@ -437,12 +437,8 @@ static int launch_decode(const void* q, const void* k_cache, const void* v_cache
     dim3 grid(n_splits, n_kv * m_tiles, n_seqs);
     auto kern = decode_attention_kernel<D>;
     constexpr int smem = DecodeSmem<D>::kTotal;
-    static bool configured = false;      // per function and per process; setting it again would be harmless
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static bool configured[kMaxDevices] = {};            // per kernel and per device
+    if (int st = ensure_dynamic_smem(kern, smem, configured)) return st;
     cpm_launch(kLaunchAttention, kern, grid, kDecodeWarps * 32, smem, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
                kv_len, slots, page_table, max_pages, part_o, part_ml, (bf16*)out, n_heads, n_kv, m_tiles, n_splits,
                scale * 1.4426950408889634f);
@@ -595,12 +591,8 @@ static int launch_listed(const void* q, const void* k_cache, const void* v_cache
     float* part_ml = scratch ? scratch + (int64_t)n_tokens * n_kv * m_tiles * n_splits * 16 * D : nullptr;
     auto kern = listed_attention_kernel<D>;
     constexpr int smem = DecodeSmem<D>::kTotal;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static bool configured[kMaxDevices] = {};            // per kernel and per device
+    if (int st = ensure_dynamic_smem(kern, smem, configured)) return st;
     kern<<<dim3(n_tokens, n_kv * m_tiles, n_splits), kDecodeWarps * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_cache,
         (const bf16*)v_cache, (bf16*)out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_heads,
         n_kv, m_tiles, scale * 1.4426950408889634f, part_o, part_ml, n_splits);
@@ -722,12 +714,8 @@ static int launch_prefill(const void* q, const void* k_cache, const void* v_cach
                           cudaStream_t stream) {
     auto kern = prefill_attention_kernel<D>;
     constexpr int smem = 2 * DecodeSmem<D>::kStageBytes;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static bool configured[kMaxDevices] = {};            // per kernel and per device
+    if (int st = ensure_dynamic_smem(kern, smem, configured)) return st;
     kern<<<dim3(n_heads, n_tiles), kPrefillWarps * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_cache,
         (const bf16*)v_cache, (bf16*)out, tile_seq, tile_row, cu_q, kv_len, slots, page_table, max_pages, n_heads, n_kv,
         scale * 1.4426950408889634f);
@@ -762,7 +750,6 @@ CPM_API int cpm_prefill_attention_bf16(const void* q, const void* k_cache, const
 // looked up below and that pointer is what the kernels get.
 static __device__ __align__(256) float g_static_scratch[CPM_STATIC_SCRATCH_FLOATS];
 
-static constexpr int kMaxDevices = 64;
 static float* g_static_scratch_ptr[kMaxDevices] = {nullptr};
 static std::mutex g_static_scratch_mutex;
 

@@ -424,12 +424,8 @@ static int launch(const void* q, const void* k_cache, const void* v_cache, void*
         !tc5::make_map_2d_bf16(&map_v, v_cache, (uint64_t)n_pages * n_kv * D, kPageTokens, kPageTokens * 2, 64, D))
         return CPM_BAD_ARGUMENT;
     auto kern = prefill_attention_tcgen05_kernel<D>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Sizes<D>::kSmemBytes);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static bool configured[kMaxDevices] = {};            // per kernel and per device
+    if (int st = ensure_dynamic_smem(kern, Sizes<D>::kSmemBytes, configured)) return st;
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (int64_t)n_splits * n_tokens * n_heads * D : nullptr;
     kern<<<dim3(n_heads / 2, n_tiles, n_splits), kThreads, Sizes<D>::kSmemBytes, stream>>>(map_q, map_k, map_v, (bf16*)out,

@@ -145,6 +145,23 @@ static inline void cpm_launch(LaunchClass cls, void (*kernel)(KArgs...), dim3 gr
     cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
 }
 
+// Raises a kernel's dynamic shared-memory limit once per device (the attribute belongs to the device's
+// context, so a process that uses several GPUs has to set it on each).  ``done`` is a zero-initialised
+// array of kMaxDevices flags, one array per kernel.  Returns CPM_OK or the CUDA error.
+constexpr int kMaxDevices = 64;
+template <typename Kernel>
+static inline int ensure_dynamic_smem(Kernel kernel, int bytes, bool* done) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= kMaxDevices) return CPM_BAD_ARGUMENT;
+    if (done[dev]) return CPM_OK;
+    e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return (int)e;
+    done[dev] = true;
+    return CPM_OK;
+}
+
 static inline int launch_status() {
     cudaError_t e = cudaPeekAtLastError();
     return e == cudaSuccess ? CPM_OK : (int)e;

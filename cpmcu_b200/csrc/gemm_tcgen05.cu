@@ -409,12 +409,8 @@ static int launch(const void* A, const void* W, void* out, int M, int N, int K, 
     CUtensorMap map_a, map_w;
     if (!make_map(&map_a, A, M, K, kBlockM) || !make_map(&map_w, W, N, K, kBlockN)) return CPM_BAD_ARGUMENT;
     auto kern = gemm_tcgen05_kernel<EPI>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static bool configured[kMaxDevices] = {};            // per kernel and per device
+    if (int st = ensure_dynamic_smem(kern, kSmemBytes, configured)) return st;
     const int tiles = ((M + kBlockM - 1) / kBlockM) * ((N + kBlockN - 1) / kBlockN);
     kern<<<tiles < n_blocks ? tiles : n_blocks, kThreads, kSmemBytes, stream>>>(map_a, map_w, (bf16*)out, M, N, K);
     return launch_status();
@@ -426,12 +422,8 @@ static int launch_pair(const void* A, const void* W, void* out, int M, int N, in
     CUtensorMap map_a, map_w;
     if (!make_map(&map_a, A, M, K, kBlockM) || !make_map(&map_w, W, N, K, kHalfN)) return CPM_BAD_ARGUMENT;
     auto kern = gemm_tcgen05_pair_kernel<EPI>;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes2);
-        if (e != cudaSuccess) return (int)e;
-        configured = true;
-    }
+    static bool configured[kMaxDevices] = {};            // per kernel and per device
+    if (int st = ensure_dynamic_smem(kern, kSmemBytes2, configured)) return st;
     const int tiles = ((M + 2 * kBlockM - 1) / (2 * kBlockM)) * ((N + kBlockN - 1) / kBlockN);
     int pairs = n_blocks / 2;
     if (pairs < 1) return CPM_BAD_ARGUMENT;

@@ -59,73 +59,116 @@ CPM_API int cpm_pool_keys(const void* k_cache, float* pooled, const int* positio
     return launch_status();
 }
 
-// From the scores of the visible pooled keys to the list of blocks: block score = max over the
-// pooled keys that overlap the block; the leading blocks and the blocks of the local window are
-// always taken; of the others the topk - init_blocks best are chosen (ties to the lower index) by
-// sorting (score, index) keys in shared memory.  score: [n_vis]; flags: [>= candidates] scratch;
-// keys: [power of two >= candidates] scratch.  All threads of the block call this.
-__device__ void finish_selection(const float* __restrict__ score, float* __restrict__ flags,
-                                 unsigned long long* __restrict__ keys, int* __restrict__ list, int list_cap, int p,
-                                 int n_vis, int kernel, int stride, int block_size, int init_blocks, int topk,
-                                 int local_blocks) {
-    const int tid = threadIdx.x, n_threads = blockDim.x;
-    const int qb = p / block_size;
-    const int last_choice = qb - local_blocks;
-    const int per_block = block_size / stride;
-    const int reach_back = kernel / stride - 1;
-    const int n_cand = max(0, last_choice + 1 - init_blocks);
-    int n_sort = 1;
-    while (n_sort < n_cand) n_sort <<= 1;
-    // key: score bits made monotonic, then the inverted index, so that a descending sort puts the
-    // higher score first and among equal scores the lower index
-    for (int i = tid; i < n_sort; i += n_threads) {
-        unsigned long long key = 0ull;                       // below every real key
-        if (i < n_cand) {
-            const int k = init_blocks + i;
-            const int lo = max(0, k * per_block - reach_back), hi = min(n_vis, (k + 1) * per_block);
-            float b = -INFINITY;
-            for (int e = lo; e < hi; ++e) b = fmaxf(b, score[e]);
-            if (b > -INFINITY) {
-                const unsigned bits = __float_as_uint(b);
-                const unsigned mono = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
-                key = ((unsigned long long)mono << 32) | (unsigned)(0x7fffffff - i);
-            }
-            flags[i] = 0.f;
-        }
-        keys[i] = key;
+// From the scores of the visible pooled keys to the list of blocks.  The block score is the
+// maximum over the pooled keys that overlap the block; the leading blocks and the blocks of the
+// local window are always taken; of the others the topk - init_blocks best are chosen (ties to
+// the lower index).  Nothing here is sized by the number of pooled keys: every pooled key's score
+// goes straight into the sort keys of the blocks it overlaps (note_score, an atomic maximum in
+// shared memory), so the shared arrays grow with the number of candidate blocks only.
+//
+// A sort key is the score's bits made monotonic, then the inverted candidate index, so that a
+// descending sort puts the higher score first and among equal scores the lower index; 0 is below
+// every real key and stands for "no pooled key overlaps this block".
+struct Selection {
+    int qb;             // block of the query
+    int last_choice;    // last block that can be chosen (those after it are the local window)
+    int n_cand;         // candidates: blocks init_blocks .. last_choice
+    int n_sort;         // power of two >= n_cand
+    int per_block;      // pooled keys that start inside one block
+    int reach_back;     // pooled keys before a block's first that still overlap it
+};
+
+__device__ __forceinline__ Selection selection_of(int p, int kernel, int stride, int block_size, int init_blocks,
+                                                  int local_blocks, int sort_cap) {
+    Selection s;
+    s.qb = p / block_size;
+    s.last_choice = s.qb - local_blocks;
+    s.per_block = block_size / stride;
+    s.reach_back = kernel / stride - 1;
+    s.n_cand = min(max(0, s.last_choice + 1 - init_blocks), sort_cap);
+    s.n_sort = 1;
+    while (s.n_sort < s.n_cand) s.n_sort <<= 1;
+    return s;
+}
+
+// Clears the sort keys and the chosen bits; all threads call it, a barrier must follow.
+__device__ __forceinline__ void clear_selection(const Selection& s, unsigned long long* __restrict__ keys,
+                                                unsigned* __restrict__ chosen) {
+    for (int i = threadIdx.x; i < s.n_sort; i += blockDim.x) keys[i] = 0ull;
+    for (int i = threadIdx.x; i < (s.n_cand + 31) / 32; i += blockDim.x) chosen[i] = 0u;
+}
+
+// Pooled key ``entry`` has the score ``v`` (>= 0): raises the key of every candidate block it overlaps.
+__device__ __forceinline__ void note_score(const Selection& s, unsigned long long* __restrict__ keys, int init_blocks,
+                                           int entry, float v) {
+    const unsigned bits = __float_as_uint(v);
+    const unsigned long long mono = (unsigned long long)((bits & 0x80000000u) ? ~bits : (bits | 0x80000000u)) << 32;
+    const int k_hi = min((entry + s.reach_back) / s.per_block, init_blocks + s.n_cand - 1);
+    for (int k = max(entry / s.per_block, init_blocks); k <= k_hi; ++k) {
+        const int i = k - init_blocks;
+        atomicMax(&keys[i], mono | (unsigned)(0x7fffffff - i));
     }
-    __syncthreads();
-    for (int k = 2; k <= n_sort; k <<= 1) {
-        for (int j = k >> 1; j > 0; j >>= 1) {
-            for (int i = tid; i < n_sort; i += n_threads) {
-                const int partner = i ^ j;
-                if (partner > i) {
-                    const unsigned long long a = keys[i], b = keys[partner];
-                    const bool descending = (i & k) == 0;
-                    if (descending ? a < b : a > b) {
-                        keys[i] = b;
-                        keys[partner] = a;
+}
+
+// keys: [n_sort] filled by note_score; chosen: [(n_cand + 31) / 32] cleared.  All threads call this
+// after a barrier that follows the last note_score.
+__device__ void finish_selection(const Selection& s, unsigned long long* __restrict__ keys, unsigned* __restrict__ chosen,
+                                 int* __restrict__ list, int list_cap, int init_blocks, int topk) {
+    const int tid = threadIdx.x, n_threads = blockDim.x;
+    const int n_sort = s.n_sort, n_cand = s.n_cand;
+    const int room = min(max(0, topk - init_blocks), n_cand);
+    if (n_cand > room) {                  // with room for every candidate there is nothing to sort
+        for (int k = 2; k <= n_sort; k <<= 1) {
+            for (int j = k >> 1; j > 0; j >>= 1) {
+                for (int i = tid; i < n_sort; i += n_threads) {
+                    const int partner = i ^ j;
+                    if (partner > i) {
+                        const unsigned long long a = keys[i], b = keys[partner];
+                        const bool descending = (i & k) == 0;
+                        if (descending ? a < b : a > b) {
+                            keys[i] = b;
+                            keys[partner] = a;
+                        }
                     }
                 }
+                __syncthreads();
             }
-            __syncthreads();
         }
     }
-    const int room = min(max(0, topk - init_blocks), n_cand);
-    for (int r = tid; r < room; r += n_threads) {
+    for (int r = tid; r < (n_cand > room ? room : n_cand); r += n_threads) {
         const unsigned long long key = keys[r];
-        if (key != 0ull) flags[0x7fffffff - (int)(unsigned)(key & 0xffffffffull)] = 1.f;
+        if (key != 0ull) {
+            const int i = 0x7fffffff - (int)(unsigned)(key & 0xffffffffull);
+            atomicOr(&chosen[i >> 5], 1u << (i & 31));
+        }
     }
     __syncthreads();
     if (tid == 0) {
         int n = 0;
-        const int n_init = min(init_blocks, qb + 1);
+        const int n_init = min(init_blocks, s.qb + 1);
         for (int k = 0; k < n_init && n < list_cap - 1; ++k) list[n++] = k;
-        for (int i = 0; i < n_cand && n < list_cap - 1; ++i)
-            if (flags[i] != 0.f) list[n++] = init_blocks + i;
-        for (int k = max(n_init, last_choice + 1); k <= qb && n < list_cap - 1; ++k) list[n++] = k;
+        for (int w = 0; w < (n_cand + 31) / 32; ++w) {
+            unsigned bits = chosen[w];
+            while (bits && n < list_cap - 1) {
+                const int b = __ffs(bits) - 1;
+                bits &= bits - 1;
+                list[n++] = init_blocks + 32 * w + b;
+            }
+        }
+        for (int k = max(n_init, s.last_choice + 1); k <= s.qb && n < list_cap - 1; ++k) list[n++] = k;
         list[n] = -1;
     }
+}
+
+// Set when a query had more candidate blocks than the launch made room for (the caller's bound on the
+// longest sequence was too small); the lists of such a query are not valid.
+__device__ int g_select_overflow = 0;
+
+CPM_API int cpm_select_blocks_error() {
+    int v = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&v, g_select_overflow, sizeof(int)) != cudaSuccess) return -1;
+    if (v) cudaMemcpyToSymbol(g_select_overflow, &zero, sizeof(int));
+    return v;
 }
 
 // One block per (token, kv head): writes the ascending list of key blocks the query
@@ -176,15 +219,14 @@ select_blocks_kernel(const T* __restrict__ q, const float* __restrict__ pooled, 
                      const int* __restrict__ token_seq, const int* __restrict__ slots,
                      const int* __restrict__ page_table, int max_pages, int* __restrict__ lists, int list_cap,
                      int n_heads, int n_kv, int d, float scale, int kernel, int stride, int block_size,
-                     int init_blocks, int topk, int local_blocks, int dense_len, int max_entries) {
-    extern __shared__ __align__(16) float sm[];
-    float* score = sm;                                   // [max_entries]
-    float* tmp = sm + max_entries;                       // [max_entries]: chosen flags of the blocks
-    float* qs = tmp + max_entries;                       // [group][d]
+                     int init_blocks, int topk, int local_blocks, int dense_len, int sort_cap) {
+    extern __shared__ __align__(16) unsigned char sm_raw[];
+    unsigned long long* keys = (unsigned long long*)sm_raw;                    // [sort_cap]
+    unsigned* chosen = (unsigned*)(keys + sort_cap);                          // [sort_cap / 32 + 1]
+    float* qs = (float*)(chosen + ((sort_cap / 32 + 4) & ~3));               // [group][d]
     const int group = n_heads / n_kv;
     float* stat_m = qs + group * d;                      // [warps][kMaxGroup]
     float* stat_l = stat_m + kSelectWarps * kMaxGroup;   // [warps][kMaxGroup]
-    unsigned long long* keys = (unsigned long long*)(stat_l + kSelectWarps * kMaxGroup);   // [sort_size]
     const int t = blockIdx.x, kvh = blockIdx.y, tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31;
     int* list = lists + ((int64_t)t * n_kv + kvh) * list_cap;
@@ -195,8 +237,10 @@ select_blocks_kernel(const T* __restrict__ q, const float* __restrict__ pooled, 
     }
     const int* pages = page_table + (int64_t)slots[token_seq[t]] * max_pages;
     const int per_page = kPageTokens / stride;
-    int n_vis = p + 1 >= kernel ? (p + 1 - kernel) / stride + 1 : 0;
-    n_vis = min(n_vis, max_entries);
+    const int n_vis = p + 1 >= kernel ? (p + 1 - kernel) / stride + 1 : 0;
+    const Selection sel = selection_of(p, kernel, stride, block_size, init_blocks, local_blocks, sort_cap);
+    if (tid == 0 && p / block_size - local_blocks + 1 - init_blocks > sort_cap) g_select_overflow = 1;
+    clear_selection(sel, keys, chosen);
 
     for (int i = tid; i < group * d; i += kSelectThreads)
         qs[i] = to_f32(q[((int64_t)t * n_heads + kvh * group) * d + i]);
@@ -239,11 +283,11 @@ select_blocks_kernel(const T* __restrict__ q, const float* __restrict__ pooled, 
             if (h == lane) mine = dots[h];
         const float prob = lane < group ? expf(mine - head_m) * head_inv : 0.f;
         const float total = warp_sum(prob);
-        if (lane == 0) score[i] = total;
+        if (lane == 0) note_score(sel, keys, init_blocks, i, total);
     }
     __syncthreads();
 
-    finish_selection(score, tmp, keys, list, list_cap, p, n_vis, kernel, stride, block_size, init_blocks, topk, local_blocks);
+    finish_selection(sel, keys, chosen, list, list_cap, init_blocks, topk);
 }
 
 // ---------------------------------------------------------------------------
@@ -310,13 +354,12 @@ select_blocks_mma_kernel(const bf16* __restrict__ q, const float* __restrict__ p
                          const int* __restrict__ token_seq, const int* __restrict__ slots,
                          const int* __restrict__ page_table, int max_pages, int* __restrict__ lists, int list_cap,
                          int n_heads, int n_kv, float scale_log2, int kernel, int stride, int block_size,
-                         int init_blocks, int topk, int local_blocks, int dense_len, int max_entries) {
-    extern __shared__ __align__(16) float sm[];
-    float* score = sm;                                        // [max_entries]
-    float* flags = sm + max_entries;                          // [max_entries]
-    float* stat_m = flags + max_entries;                      // [warps][16]
-    float* stat_l = stat_m + kSelMmaWarps * 16;               // [warps][16]
-    unsigned long long* keys = (unsigned long long*)(stat_l + kSelMmaWarps * 16);
+                         int init_blocks, int topk, int local_blocks, int dense_len, int sort_cap) {
+    extern __shared__ __align__(16) unsigned char sm_raw[];
+    unsigned long long* keys = (unsigned long long*)sm_raw;                   // [sort_cap]
+    unsigned* chosen = (unsigned*)(keys + sort_cap);                         // [sort_cap / 32 + 1]
+    float* stat_m = (float*)(chosen + ((sort_cap / 32 + 4) & ~3));          // [warps][16]
+    float* stat_l = stat_m + kSelMmaWarps * 16;                              // [warps][16]
     const int t = blockIdx.x, kvh = blockIdx.y, tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, j = lane & 3;
     int* list = lists + ((int64_t)t * n_kv + kvh) * list_cap;
@@ -328,9 +371,11 @@ select_blocks_mma_kernel(const bf16* __restrict__ q, const float* __restrict__ p
     const int group = n_heads / n_kv;
     const int* pages = page_table + (int64_t)slots[token_seq[t]] * max_pages;
     const int per_page = kPageTokens / stride;
-    int n_vis = p + 1 >= kernel ? (p + 1 - kernel) / stride + 1 : 0;
-    n_vis = min(n_vis, max_entries);
+    const int n_vis = p + 1 >= kernel ? (p + 1 - kernel) / stride + 1 : 0;
     const int n_tiles = (n_vis + 7) / 8;
+    const Selection sel = selection_of(p, kernel, stride, block_size, init_blocks, local_blocks, sort_cap);
+    if (tid == 0 && p / block_size - local_blocks + 1 - init_blocks > sort_cap) g_select_overflow = 1;
+    clear_selection(sel, keys, chosen);                       // the barrier between the two walks orders it
 
     uint4 qf[2][D / 32];
 #pragma unroll
@@ -412,12 +457,12 @@ select_blocks_mma_kernel(const bf16* __restrict__ q, const float* __restrict__ p
         }
         const int c0 = tile * 8 + 2 * j;
         if (g == 0) {
-            if (c0 < n_vis) score[c0] = col0;
-            if (c0 + 1 < n_vis) score[c0 + 1] = col1;
+            if (c0 < n_vis) note_score(sel, keys, init_blocks, c0, col0);
+            if (c0 + 1 < n_vis) note_score(sel, keys, init_blocks, c0 + 1, col1);
         }
     }
     __syncthreads();
-    finish_selection(score, flags, keys, list, list_cap, p, n_vis, kernel, stride, block_size, init_blocks, topk, local_blocks);
+    finish_selection(sel, keys, chosen, list, list_cap, init_blocks, topk);
 }
 
 static int next_pow2(int n) {
@@ -430,9 +475,9 @@ template <int D>
 static int launch_select_mma(const void* q, const float* pooled, const int* positions, const int* token_seq,
                              const int* slots, const int* page_table, int max_pages, int* lists, int list_cap,
                              int n_tokens, int n_heads, int n_kv, float scale, int kernel, int stride, int block_size,
-                             int init_blocks, int topk, int local_blocks, int dense_len, int max_entries, int sort_cap,
+                             int init_blocks, int topk, int local_blocks, int dense_len, int sort_cap,
                              cudaStream_t stream) {
-    const size_t smem = ((size_t)2 * max_entries + 2 * 16 * 16) * sizeof(float) + (size_t)sort_cap * 8;
+    const size_t smem = (size_t)sort_cap * 8 + (size_t)((sort_cap / 32 + 4) & ~3) * 4 + 2 * 16 * 16 * sizeof(float);
     if (smem > 227 * 1024) return CPM_BAD_ARGUMENT;
     const bool few = n_tokens * n_kv < 148;
     auto kern = few ? select_blocks_mma_kernel<D, 16> : select_blocks_mma_kernel<D, 4>;
@@ -442,10 +487,12 @@ static int launch_select_mma(const void* q, const float* pooled, const int* posi
     }
     kern<<<dim3(n_tokens, n_kv), few ? 512 : 128, smem, stream>>>((const bf16*)q, pooled, positions, token_seq, slots,
         page_table, max_pages, lists, list_cap, n_heads, n_kv, scale * 1.4426950408889634f, kernel, stride, block_size,
-        init_blocks, topk, local_blocks, dense_len, max_entries);
+        init_blocks, topk, local_blocks, dense_len, sort_cap);
     return launch_status();
 }
 
+// max_entries: an upper bound on the pooled keys any query of the step sees (longest sequence / stride + 1); it
+// sizes the sort of the candidate blocks, 8 bytes of shared memory per block.
 CPM_API int cpm_select_blocks(const void* q, const float* pooled, const int* positions, const int* token_seq,
                               const int* slots, const int* page_table, int max_pages, int* lists, int list_cap,
                               int n_tokens, int n_heads, int n_kv, int d, float scale, int kernel, int stride,
@@ -455,21 +502,20 @@ CPM_API int cpm_select_blocks(const void* q, const float* pooled, const int* pos
     if (stride <= 0 || kernel % stride || block_size % stride || kPageTokens % stride || n_kv > 65535 ||
         n_heads % n_kv || n_heads / n_kv > kMaxGroup || d % 4 || list_cap < topk + local_blocks + 1 || max_entries < 1)
         return CPM_BAD_ARGUMENT;
-    max_entries = (max_entries + 3) & ~3;            // keeps the arrays behind it 16-byte aligned
     const int sort_cap = next_pow2(max_entries / (block_size / stride) + 2);
     const int group = n_heads / n_kv;
     if (dtype == CPM_BF16 && group <= 16) {
 #define CPM_SELECT_MMA(DD) return launch_select_mma<DD>(q, pooled, positions, token_seq, slots, page_table, max_pages, lists, \
         list_cap, n_tokens, n_heads, n_kv, scale, kernel, stride, block_size, init_blocks, topk, local_blocks, dense_len, \
-        max_entries, sort_cap, stream)
+        sort_cap, stream)
         if (d == 32) CPM_SELECT_MMA(32);
         if (d == 64) CPM_SELECT_MMA(64);
         if (d == 96) CPM_SELECT_MMA(96);
         if (d == 128) CPM_SELECT_MMA(128);
 #undef CPM_SELECT_MMA
     }
-    const size_t smem = ((size_t)2 * max_entries + (size_t)group * d + 2 * kSelectWarps * kMaxGroup) * sizeof(float)
-                        + (size_t)sort_cap * 8;
+    const size_t smem = (size_t)sort_cap * 8 + (size_t)((sort_cap / 32 + 4) & ~3) * 4
+                        + ((size_t)group * d + 2 * kSelectWarps * kMaxGroup) * sizeof(float);
     if (smem > 227 * 1024) return CPM_BAD_ARGUMENT;
     dim3 grid(n_tokens, n_kv);
     cudaError_t e = cudaSuccess;
@@ -479,14 +525,14 @@ CPM_API int cpm_select_blocks(const void* q, const float* pooled, const int* pos
         if (e != cudaSuccess) return (int)e;
         kern<<<grid, kSelectThreads, smem, stream>>>((const bf16*)q, pooled, positions, token_seq, slots, page_table, max_pages,
             lists, list_cap, n_heads, n_kv, d, scale, kernel, stride, block_size, init_blocks, topk, local_blocks,
-            dense_len, max_entries);
+            dense_len, sort_cap);
     } else {
         auto kern = select_blocks_kernel<float>;
         if (smem > 48 * 1024) e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
         kern<<<grid, kSelectThreads, smem, stream>>>((const float*)q, pooled, positions, token_seq, slots, page_table, max_pages,
             lists, list_cap, n_heads, n_kv, d, scale, kernel, stride, block_size, init_blocks, topk, local_blocks,
-            dense_len, max_entries);
+            dense_len, sort_cap);
     }
     return launch_status();
 }

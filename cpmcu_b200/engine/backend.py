@@ -19,6 +19,7 @@ class EngineBackend:
         self.runner = DecodeRunner(stepper, use_graph=use_graph, seed=seed)
         self._max_batch = int(max_batch)
         self.slots: List[int] = []
+        self.open: set = set()              # slots of the current batch that are not finished yet
         self.h2d_bytes = 0
         self.d2h_bytes = 0
 
@@ -42,14 +43,31 @@ class EngineBackend:
         self.d2h_bytes += 4 * n
         return out.cpu().tolist()
 
+    def max_sequence_pages(self) -> int:
+        return self.stepper.cache.max_pages_per_seq
+
+    def vocab_size(self) -> int:
+        return self.stepper.vocab_size
+
     def prefill(self, prompts, keys, sampling) -> List[int]:
         self.slots = self.stepper.open(len(prompts))
-        batch = [SequenceStep(s, list(p), [len(p) - 1]) for s, p in zip(self.slots, prompts)]
-        self.h2d_bytes += 4 * sum(len(p) for p in prompts)
-        logits = self.stepper.step(batch)
-        tokens = self._sample(logits, keys, [0] * len(prompts), sampling)
-        self.ops.raise_on_kernel_error()                # the host has just waited for the tokens anyway
+        self.open = set(self.slots)
+        try:
+            batch = [SequenceStep(s, list(p), [len(p) - 1]) for s, p in zip(self.slots, prompts)]
+            self.h2d_bytes += 4 * sum(len(p) for p in prompts)
+            logits = self.stepper.step(batch)
+            tokens = self._sample(logits, keys, [0] * len(prompts), sampling)
+            self.ops.raise_on_kernel_error()            # the host has just waited for the tokens anyway
+        except BaseException:
+            self.abort()
+            raise
         return tokens
+
+    def abort(self) -> None:
+        """Closes every sequence of the current batch that is still open (a step failed)."""
+        for s in sorted(self.open):
+            self.stepper.close(s)
+        self.open = set()
 
     def decode(self, live, last_tokens, keys, steps_done, sampling, changed) -> List[int]:
         if changed:
@@ -64,3 +82,4 @@ class EngineBackend:
 
     def finish(self, index: int) -> None:
         self.stepper.close(self.slots[index])
+        self.open.discard(self.slots[index])

@@ -71,11 +71,21 @@ class DecodeRunner:
         self.pinned_in = None
 
     # ---- one step's work on the device ----
-    def _body(self, b: _Bucket, captured: bool) -> None:
-        capacity = self.cache.max_pages_per_seq * 64
+    def _body(self, b: _Bucket, captured: bool, slots: Sequence[int] = ()) -> None:
+        """One step on the bucket's buffers.  Captured: the host lists of the context are empty and the longest
+        sequence is given as the cache's capacity, because the same recording runs for any lengths.  Not captured:
+        the host lists describe the live sequences (``slots``) followed by the padding entries, as the step
+        function's do, so a part that decides on the host works here too."""
+        if captured:
+            kv_lens, slot_list, longest = [], [], self.cache.max_pages_per_seq * 64
+        else:
+            pad = b.size - len(slots)
+            kv_lens = [self.cache.length(s) + 1 for s in slots] + [1] * pad
+            slot_list = list(slots) + [self.pad_slot] * pad
+            longest = max(kv_lens)
         ctx = StepContext(
             n_tokens=b.size, n_seqs=b.size, is_decode=True, captured=captured,
-            q_lens=[1] * b.size, kv_lens=[], slots=[], max_q_len=1, max_kv_len=capacity,
+            q_lens=[1] * b.size, kv_lens=kv_lens, slots=slot_list, max_q_len=1, max_kv_len=longest,
             token_ids=b.ids, positions=b.positions, token_seq=b.token_seq, cu_q=b.cu_q,
             kv_len_dev=b.kv_len, slot_dev=b.slot, cache=self.cache,
         )
@@ -160,7 +170,7 @@ class DecodeRunner:
         if b.graph is not None:
             b.graph.replay()
         else:
-            self._body(b, captured=False)
+            self._body(b, captured=False, slots=self.slots)
         for s in self.slots:
             self.cache.set_length(s, self.cache.length(s) + 1)
         return b.sampled[:len(self.slots)]

@@ -38,6 +38,12 @@ class Backend(Protocol):
     def finish(self, index: int) -> None:
         """The sequence at ``index`` of the batch is done; what it holds is given back."""
 
+    def abort(self) -> None:
+        """Something failed in the middle of a batch: every sequence of it that is still open is closed."""
+
+    # Optional: ``max_sequence_pages()`` (the most pages one sequence may hold) and ``vocab_size()``; with them
+    # a request that cannot run is refused before anything is opened.
+
 
 @dataclass
 class Request:
@@ -64,9 +70,12 @@ class GenerationStats:
     batches: int = 0
 
 
-def plan_batches(requests: Sequence[Request], max_batch: int, capacity_pages: int) -> List[List[int]]:
+def plan_batches(requests: Sequence[Request], max_batch: int, capacity_pages: int,
+                 max_sequence_pages: Optional[int] = None, vocab_size: Optional[int] = None) -> List[List[int]]:
     """Cuts the requests, in order, into batches that fit: at most ``max_batch`` sequences,
-    and pages for every sequence grown to its full length."""
+    and pages for every sequence grown to its full length.  A request that can never run (longer than
+    the cache or than one sequence may be, a token id outside the vocabulary) is refused here, before
+    any sequence is opened."""
     batches: List[List[int]] = []
     cur: List[int] = []
     pages = 0
@@ -75,6 +84,13 @@ def plan_batches(requests: Sequence[Request], max_batch: int, capacity_pages: in
         if need > capacity_pages:
             raise CacheFull(f"request {i}: {len(r.prompt)} prompt + {r.max_new_tokens} new tokens need {need} pages, "
                             f"the cache has {capacity_pages}")
+        if max_sequence_pages is not None and need > max_sequence_pages:
+            raise CacheFull(f"request {i}: {len(r.prompt)} prompt + {r.max_new_tokens} new tokens need {need} pages, "
+                            f"one sequence may hold {max_sequence_pages}")
+        if vocab_size is not None:
+            bad = next((t for t in r.prompt if not 0 <= int(t) < vocab_size), None)
+            if bad is not None:
+                raise ValueError(f"request {i}: token id {bad} is outside the vocabulary [0, {vocab_size})")
         if cur and (len(cur) >= max_batch or pages + need > capacity_pages):
             batches.append(cur)
             cur, pages = [], 0
@@ -96,7 +112,22 @@ def run_requests(backend: Backend, requests: Sequence[Request],
     results = [Finished() for _ in requests]
     stats = GenerationStats()
     sync = sync or (lambda: None)
-    for batch in plan_batches(requests, backend.max_batch(), backend.capacity_pages()):
+    per_seq = getattr(backend, "max_sequence_pages", None)
+    vocab = getattr(backend, "vocab_size", None)
+    plan = plan_batches(requests, backend.max_batch(), backend.capacity_pages(),
+                        per_seq() if per_seq else None, vocab() if vocab else None)
+    try:
+        _run_batches(backend, requests, plan, results, stats, on_token, sync)
+    except BaseException:
+        abort = getattr(backend, "abort", None)
+        if abort:
+            abort()                      # nothing of a failed batch stays held for the next call
+        raise
+    return results, stats
+
+
+def _run_batches(backend, requests, plan, results, stats, on_token, sync) -> None:
+    for batch in plan:
         stats.batches += 1
         reqs = [requests[i] for i in batch]
         keys = [r.key for r in reqs]
@@ -151,4 +182,3 @@ def run_requests(backend: Backend, requests: Sequence[Request],
             live = still
         sync()
         stats.decode_time += time.perf_counter() - t0
-    return results, stats

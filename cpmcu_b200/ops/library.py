@@ -86,6 +86,8 @@ def load() -> ctypes.CDLL:
         lib.cpm_gemm_tcgen05_error.restype = c_int
         lib.cpm_attention_tcgen05_error.argtypes = []
         lib.cpm_attention_tcgen05_error.restype = c_int
+        lib.cpm_select_blocks_error.argtypes = []
+        lib.cpm_select_blocks_error.restype = c_int
         lib.cpm_decode_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int, c_int]
         lib.cpm_decode_attention_scratch_floats.restype = c_int64
         for name, argtypes in _SIGNATURES.items():

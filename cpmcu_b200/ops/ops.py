@@ -294,6 +294,8 @@ class Ops:
         bs, stride = sparse["block_size"], sparse["kernel_stride"]
         local_blocks = sparse["window_size"] // bs
         cap = sparse["topk"] + local_blocks + 2
+        # an upper bound on the pooled keys a query sees; it sizes the sort of the candidate blocks (8 bytes of shared
+        # memory per block), not the walk over the pooled keys, which follows each query's own position
         longest = lane.page_table.shape[1] * PAGE_TOKENS if ctx.captured else ctx.max_kv_len
         max_entries = max(1, longest // stride + 1)
         lists = self.empty(n, n_kv, cap, dtype=torch.int32)
@@ -390,6 +392,9 @@ class Ops:
         if gemm or attn:
             raise RuntimeError(f"a tcgen05 kernel gave up waiting on a barrier (product: code {gemm}, attention: code "
                                f"{attn}); the results of this step are not valid")
+        if int(self.lib.cpm_select_blocks_error()):
+            raise RuntimeError("block selection met a query with more candidate key blocks than the launch made room "
+                               "for (a sequence longer than the bound the step gave); the results of this step are not valid")
 
     def listed_attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, positions: torch.Tensor,
                          token_seq: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,

@@ -23,8 +23,14 @@ from .base import MIXERS, POSITIONS, CacheNeeds, Mixer, PartSpec, WeightSpec, bu
 class GroupedQueryAttention(Mixer):
     def __init__(self, ops, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  position: PartSpec, window: Optional[int] = None, sparse: Optional[Mapping[str, int]] = None,
-                 softmax_scale: Optional[float] = None):
+                 softmax_scale: Optional[float] = None, position_name: str = ""):
+        """``position_name``: infix of the position part's own tensors below this part's prefix (an encoding with
+        learned tables declares them in its ``weight_specs``; the rotary encodings have none)."""
         super().__init__(ops)
+        if window and sparse:
+            # a windowed lane gives pages back that the block selection (leading blocks, chosen far blocks, the
+            # scores over all pooled keys) would still follow
+            raise ValueError("gqa_attention takes a window or a sparse configuration, not both")
         if n_heads % n_kv_heads:
             raise ValueError(f"{n_heads} heads cannot be grouped over {n_kv_heads} key-value heads")
         if head_dim % 16 or head_dim > 256:
@@ -34,20 +40,27 @@ class GroupedQueryAttention(Mixer):
         self.sparse = dict(sparse) if sparse else None
         self.scale = float(softmax_scale) if softmax_scale is not None else 1.0 / math.sqrt(self.d)
         self.position = build_part(POSITIONS, position, ops)
+        self.position_name = str(position_name)
         self.w_qkv: Optional[torch.Tensor] = None
         self.w_o: Optional[torch.Tensor] = None
 
     # ---- weights ----
     def weight_specs(self) -> Dict[str, WeightSpec]:
         h, d = self.hidden_size, self.d
-        return {
+        specs = {
             "q_proj.weight": WeightSpec((self.n_heads * d, h)),
             "k_proj.weight": WeightSpec((self.n_kv * d, h)),
             "v_proj.weight": WeightSpec((self.n_kv * d, h)),
             "o_proj.weight": WeightSpec((h, self.n_heads * d)),
         }
+        for name, spec in self.position.weight_specs().items():
+            specs[self.position_name + name] = spec
+        return specs
 
     def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
+        own = self.position.weight_specs()
+        if own:
+            self.position.load_weights({n: tensors[self.position_name + n] for n in own})
         self.w_qkv = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]],
                                dim=0).contiguous()
         self.w_o = tensors["o_proj.weight"].contiguous()

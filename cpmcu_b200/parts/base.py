@@ -332,9 +332,20 @@ class StepContext:
     """One step's batch, as the parts see it.
 
     Host-side lists describe the batch for Python-level decisions; the device
-    tensors are what kernels read.  In a captured decode step the device tensors
-    are fixed buffers whose contents change between launches, and ``captured`` is
-    True: parts must then not branch on host values that change from step to step.
+    tensors are what kernels read.  Both are filled whenever a step runs eagerly:
+    by the step function, and by the decode runner without a graph (its padding
+    entries appear as sequences of one key in a scratch slot).
+
+    In a captured decode step (``captured`` True) the device tensors are fixed
+    buffers whose contents change between replays; the recording is made once, on
+    padding entries only, and replayed for any batch.  A part may then read only:
+    ``n_tokens``, ``n_seqs`` (the bucket size), ``is_decode`` (True), ``q_lens`` (all 1),
+    ``max_q_len`` (1), ``max_kv_len`` (the cache's capacity per sequence, an upper
+    bound), the device tensors, ``cache`` and its lanes.  ``kv_lens`` and ``slots`` are
+    empty; everything that depends on a sequence (its slot, its length, its state
+    in ``lane.state[name][slot]``) has to be reached on the device through
+    ``slot_dev`` and ``kv_len_dev``, with operations that can be recorded (no
+    host read, no data-dependent shapes).
     """
 
     n_tokens: int

@@ -34,7 +34,30 @@ def unregister_architecture(name: str) -> None:
     _ARCHITECTURES.pop(name, None)
 
 
+_plugins_loaded: set = set()
+
+
+def load_plugins(modules=None) -> List[str]:
+    """Imports the named modules (default: the comma-separated list in the environment variable
+    ``CPMCU_PLUGINS``), each once.  A plug-in is any importable module that registers parts or architectures when
+    it is imported; this is how a model that the package does not know is reached from the command line and
+    from ``bin/trace_run`` without a change to the package."""
+    import importlib
+    import os
+
+    if modules is None:
+        modules = [m.strip() for m in os.environ.get("CPMCU_PLUGINS", "").split(",") if m.strip()]
+    done = []
+    for m in modules:
+        if m not in _plugins_loaded:
+            _plugins_loaded.add(m)
+            importlib.import_module(m)
+            done.append(m)
+    return done
+
+
 def architecture(name: str) -> Architecture:
+    load_plugins()
     try:
         return _ARCHITECTURES[name]
     except KeyError:
@@ -42,6 +65,7 @@ def architecture(name: str) -> Architecture:
 
 
 def known_architectures() -> List[str]:
+    load_plugins()
     return sorted(_ARCHITECTURES)
 
 

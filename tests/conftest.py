@@ -25,3 +25,12 @@ def model_folders(tmp_path_factory):
         return cache[key]
 
     return get
+
+
+@pytest.fixture(scope="session", autouse=True)
+def sparse_comparisons_compare_enough():
+    """After the last test: no bf16 comparison of a model with sparse attention may have passed on near ties alone."""
+    yield
+    from tests import helpers
+
+    helpers.check_sparse_rows_kept()

@@ -197,3 +197,79 @@ def test_window_group_gives_pages_back_as_the_window_moves():
     c.close_sequence(s)
     assert win.pages.n_held == 0 and full.pages.n_held == 0
     c.check_consistent()
+
+
+class FailingBackend(FakeBackend):
+    """Holds slots like an engine does; its n-th call of ``fail_at`` raises."""
+
+    def __init__(self, fail_at, **kw):
+        super().__init__(**kw)
+        self.fail_at, self.aborted = fail_at, 0
+
+    def max_sequence_pages(self): return 4
+    def vocab_size(self): return 50
+
+    def prefill(self, prompts, keys, sampling):
+        out = super().prefill(prompts, keys, sampling)
+        if self.fail_at == "prefill":
+            raise RuntimeError("a step failed")
+        return out
+
+    def decode(self, live, last_tokens, keys, steps_done, sampling, changed):
+        if self.fail_at == "decode":
+            raise RuntimeError("a step failed")
+        return super().decode(live, last_tokens, keys, steps_done, sampling, changed)
+
+    def abort(self):
+        self.aborted += 1
+        self.open = {}
+
+
+def test_a_failing_request_leaves_nothing_held():
+    good = [Request([1] * 5, 4, key=0), Request([1] * 9, 3, key=1)]
+    for where in ("prefill", "decode"):
+        be = FailingBackend(where)
+        with pytest.raises(RuntimeError, match="a step failed"):
+            run_requests(be, good)
+        assert be.aborted == 1 and not be.open
+    # requests that can never run are refused before any sequence is opened
+    be = FailingBackend(None)
+    with pytest.raises(CacheFull, match="one sequence may hold 4"):
+        run_requests(be, good + [Request([1] * 300, 10, key=2)])
+    with pytest.raises(ValueError, match="token id 50 is outside"):
+        run_requests(be, good + [Request([1, 50], 10, key=2)])
+    assert be.log == [] and not be.open
+    res, _ = run_requests(be, good)                                 # and the backend is still usable
+    assert [r.tokens for r in res] == [[0, 1, 2, 3], [100, 101, 102]]
+
+
+def test_engine_backend_gives_slots_back_when_a_step_fails():
+    """The device backend over a stand-in stepper: a prompt's step raises; the slots opened for the batch, and the
+    pages reserved for its earlier sequences, are all given back."""
+    from cpmcu_b200.engine.backend import EngineBackend
+
+    cache = Cache([CacheNeeds(kv_heads=1, head_dim=16)], max_tokens=64 * 8, dtype=torch.float32, device="cpu", n_slots=6,
+                  max_seq_tokens=64 * 3)
+
+    class Ops:
+        device = "cpu"
+        def raise_on_kernel_error(self): pass
+
+    class StandInStepper:
+        ops, vocab_size = Ops(), 50
+        def __init__(self): self.cache = cache
+        def open(self, n): return cache.open_sequences(n)
+        def close(self, s): cache.close_sequence(s)
+        def step(self, batch):
+            for b in batch:
+                cache.reserve(b.slot, len(b.tokens))        # the second sequence is too long for one sequence
+            return None
+
+    be = EngineBackend.__new__(EngineBackend)
+    be.stepper, be.ops, be.seed, be._max_batch = StandInStepper(), Ops(), 0, 4
+    be.slots, be.open, be.h2d_bytes, be.d2h_bytes = [], set(), 0, 0
+    with pytest.raises(CacheFull, match="pages"):
+        be.prefill([[1] * 70, [1] * 400, [1] * 5], [0, 1, 2], [SamplingParams()] * 3)
+    cache.check_consistent()
+    assert cache.slots.n_held == 0 and cache.tokens_held() == 0
+    assert be.max_sequence_pages() == 3 and be.vocab_size() == 50

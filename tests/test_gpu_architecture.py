@@ -1,0 +1,133 @@
+"""A whole architecture that the package does not know (tests/toy_arch.py: a mixer with state of its own that
+is updated on the device, a feed-forward that routes tokens to experts, a position encoding with a learned tensor
+of its own) is registered from outside the package, written as a model folder, and run through every way into
+the model: the step function, the generation loop of ``LLM`` with and without a CUDA graph, the command line and
+the replay program, each against the architecture's plain implementation."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from tests import helpers, toy_arch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+@pytest.fixture(scope="module")
+def toy_folder(tmp_path_factory):
+    def get(dtype):
+        out = tmp_path_factory.mktemp(f"toy-{dtype}")
+        return helpers.make_folder(toy_arch.config_dict(), str(out), 5, dtype, std=0.12)
+    made = {}
+    return lambda dtype: made.setdefault(dtype, get(dtype))
+
+
+def test_registered_from_outside_and_loaded_by_name(toy_folder):
+    from cpmcu_b200.loading import load_model
+    from cpmcu_b200.registry import known_architectures
+
+    assert toy_arch.NAME in known_architectures()
+    arch, cfg, model = load_model(toy_folder("float32"), "float32")
+    assert arch.name == toy_arch.NAME and isinstance(cfg, toy_arch.ToyConfig)
+    names = model.weight_specs()
+    assert "L0.mix.pos.rate" in names and names["L0.mix.pos.rate"].role == "vector"      # the encoding's own tensor
+    needs = model.cache_needs()
+    assert needs[1].kv_heads == 0 and "s" in needs[1].state and needs[0].kv_heads == 1
+
+
+@pytest.mark.parametrize("graph", [False, True])
+def test_generates_through_llm_like_the_plain_implementation(toy_folder, graph):
+    """fp32: the very tokens of the plain implementation, for a batch of unequal prompts whose sequences end at
+    different steps, twice in a row (slots and their state are used again)."""
+    from cpmcu_b200 import LLM
+
+    folder = toy_folder("float32")
+    cfg, w = helpers.read_folder(folder)
+    llm = LLM(folder, dtype="float32", cuda_graph=graph, max_tokens=64 * 12, chunk_length=16)
+    prompts = [helpers.random_ids(cfg["vocab_size"], n, 20 + n) for n in (23, 3, 40)]
+    want = [toy_arch.plain_greedy(cfg, w, p, 9) for p in prompts]
+    stop = want[1][4]
+    for _ in range(2):
+        res = llm.generate_batch(prompts, generation_length=9, terminators=[stop])
+        for r, wt in zip(res, want):
+            cut = wt.index(stop) + 1 if stop in wt else len(wt)
+            assert r.tokens == wt[:cut]
+    llm.cache.check_consistent()
+    assert llm.cache.slots.n_held == 1
+
+
+@pytest.mark.parametrize("graph", [False, True])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_runner_logits_of_the_toy_architecture(toy_folder, dtype, graph):
+    """The decode runner fed with given tokens, logits of every step against the plain implementation; in bf16
+    up to the first position whose routing decision is a near tie."""
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.engine import Stepper
+    from cpmcu_b200.loading import load_model
+
+    folder = toy_folder(dtype)
+    cfg, w = helpers.read_folder(folder)
+    _, _, model = load_model(folder, dtype)
+    st = Stepper(model, Cache(model.cache_needs(), 64 * 8, DT[dtype], "cuda:0"), chunk_tokens=16)
+    lens, extra = (30, 2, 11), (14, 20, 6)
+    seqs = [helpers.random_ids(cfg["vocab_size"], L + e, 70 + L) for L, e in zip(lens, extra)]
+    refs = [toy_arch.plain_logits(cfg, w, ids) for ids in seqs]
+    firm_upto = []
+    for ids, (_, margin) in zip(seqs, refs):
+        firm = margin > (0.0 if dtype == "float32" else 0.05)
+        firm_upto.append(len(ids) if bool(firm.all()) else int((~firm).nonzero()[0]))
+    compared = [0]
+
+    def check(i, rows, positions):
+        if positions[0] >= firm_upto[i]:
+            return
+        err = helpers.rel_err(rows, refs[i][0][positions])
+        assert err < {"float32": 2e-5, "bfloat16": 2e-2}[dtype], (i, positions, err)
+        compared[0] += 1
+
+    helpers.runner_parity(st, seqs, lens, check, graph)
+    assert compared[0] >= (3 + sum(extra)) * (1.0 if dtype == "float32" else 0.5)
+
+
+@pytest.mark.parametrize("graph", ["true", "false"])
+def test_command_line_with_a_plugin(toy_folder, graph):
+    folder = toy_folder("float32")
+    cfg, w = helpers.read_folder(folder)
+    prompts = [helpers.random_ids(cfg["vocab_size"], n, 90 + n) for n in (12, 5)]
+    cmd = [sys.executable, "-m", "cpmcu_b200.cli", "--plugin", "tests.toy_arch", "--model-path", folder, "--dtype", "float32",
+           "--num-generate", "6", "--cuda-graph", graph, "--max-tokens", "512", "--use-stream", "false"]
+    for p in prompts:
+        cmd += ["--prompt-ids", ",".join(map(str, p))]
+    out = subprocess.run(cmd, cwd=ROOT, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    got = {int(l[1:l.index("]")]): [int(x) for x in l[l.index("]") + 1:].split()] for l in out.stdout.splitlines()
+           if l.startswith("[")}
+    for i, p in enumerate(prompts):
+        assert got[i] == toy_arch.plain_greedy(cfg, w, p, 6)
+
+
+def test_replay_program_with_a_plugin(toy_folder, tmp_path):
+    folder = toy_folder("float32")
+    cfg, w = helpers.read_folder(folder)
+    ids = helpers.random_ids(cfg["vocab_size"], 26, 7)
+    steps = [{"step": 0, "entries": [{"id": "x", "tokens": ids[:20], "want": [0, 19]}], "end": []}]
+    steps += [{"step": 1 + i, "entries": [{"id": "x", "tokens": [ids[20 + i]], "want": [0]}], "end": ["x"] if i == 5 else []}
+              for i in range(6)]
+    env = dict(os.environ, CPMCU_PLUGINS="tests.toy_arch", PYTHONPATH=ROOT + os.pathsep + os.environ.get("PYTHONPATH", ""))
+    out = subprocess.run([os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", "float32", "--out",
+                          str(tmp_path), "--max-tokens", "128"], input="\n".join(json.dumps(s) for s in steps) + "\n",
+                         cwd=ROOT, env=env, capture_output=True, text=True, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    assert [l for l in out.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(7)]
+    want, _ = toy_arch.plain_logits(cfg, w, ids)
+    first = torch.from_numpy(np.fromfile(tmp_path / "0.f32", dtype="<f4").reshape(2, -1))
+    assert helpers.rel_err(first, want[[0, 19]]) < 2e-5
+    for i in range(6):
+        row = torch.from_numpy(np.fromfile(tmp_path / f"{1 + i}.f32", dtype="<f4").reshape(1, -1))
+        assert helpers.rel_err(row, want[20 + i:21 + i]) < 2e-5

@@ -555,3 +555,81 @@ def test_pool_keys_and_select_blocks(dtype):
             assert got == want[j], (p, j, got, want[j])
             checked += 1
     assert checked > (n * n_kv) * (0.99 if dtype == "float32" else 0.8)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_select_blocks_at_long_context_sizes(dtype):
+    """Block selection at the sizes of a long-context model: head size 128, sixteen query heads per key-value head,
+    windows of 32 keys every 16, blocks of 64, 64 blocks chosen among about 600, a local window of 32 blocks, 40,960
+    cached tokens.  Every block's keys lean along one direction by an amount of their own and the queries look along
+    it, so that block scores are spread out and the choice is firm; queries are a sample of positions (the first
+    sparse one, page and block edges, the last).  The launch is sized once by the longest sequence of the step and
+    once, as inside a captured step, by the cache's capacity per sequence (here 524,288 tokens)."""
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.parts import StepContext
+    from cpmcu_b200.parts.base import CacheNeeds
+
+    ops = _ops(dtype)
+    n_heads, n_kv, d, n = 32, 2, 128, 40960
+    sparse = {"kernel_size": 32, "kernel_stride": 16, "block_size": 64, "init_blocks": 1, "topk": 64,
+              "window_size": 2048, "dense_len": 8192}
+    cache = Cache([CacheNeeds(kv_heads=n_kv, head_dim=d, pooled_stride=16, pooled_kernel=32)], max_tokens=n + 256,
+                  dtype=DT[dtype], device="cuda:0", n_slots=3, max_seq_tokens=8 * 65536)
+    junk = cache.open_sequence()
+    cache.reserve(junk, 130)
+    slot = cache.open_sequence()
+    cache.reserve(slot, n)
+    cache.sync()
+    lane = cache.lane(0)
+    g = torch.Generator().manual_seed(31)
+    direction = torch.randn(n_kv, d, generator=g)
+    direction /= direction.norm(dim=-1, keepdim=True)
+    n_blocks = n // 64
+    lean = (torch.rand(n_blocks, n_kv, generator=g) * 16 - 8)                      # per block and kv head
+    k_all = 0.05 * torch.randn(n, n_kv, d, generator=g) + lean.repeat_interleave(64, dim=0)[:, :, None] * direction
+    k_all = k_all.to(DT[dtype])
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32).cuda()
+    sl = i32([slot])
+    for lo in range(0, n, 4096):
+        m = 4096
+        qkv = torch.zeros(m, n_heads + 2 * n_kv, d, dtype=DT[dtype])
+        qkv[:, n_heads:n_heads + n_kv] = k_all[lo:lo + m]
+        ctx = StepContext(m, 1, False, False, [m], [lo + m], [slot], m, lo + m, i32([0] * m), i32(list(range(lo, lo + m))),
+                          i32([0] * m), i32([0, m]), i32([lo + m]), sl, cache)
+        ops.rope_store(qkv.view(m, -1).cuda(), n_heads, n_kv, d, ctx.positions, ctx.token_seq, sl, lane.page_table,
+                       lane.k, lane.v, None, 1.0, 0)
+        ops.pool_keys(ctx, lane, n_kv, d, 32, 16)
+    ck = plain.compress_keys(k_all.float(), 32, 16)
+    sample = sorted({8191, 8192, 8193, 8255, 8256, 10239, 10240, 16383, 16384, 30000, 32767, 32768, n - 65, n - 64, n - 1}
+                    | set(torch.randint(8192, n, (33,), generator=g).tolist()))
+    m = len(sample)
+    q_rows = (0.05 * torch.randn(m, n_heads, d, generator=g)
+              + 40.0 * direction.repeat_interleave(n_heads // n_kv, dim=0)[None]).to(DT[dtype])
+    qkv = torch.zeros(m, n_heads + 2 * n_kv, d, dtype=DT[dtype])
+    qkv[:, :n_heads] = q_rows
+    scale = 1 / math.sqrt(d)
+    for captured in (False, True):
+        ctx = StepContext(m, 1, False, captured, [m], [n], [slot], m, n, i32([0] * m), i32(sample), i32([0] * m),
+                          i32([0, m]), i32([n]), sl, cache)
+        q = ops.rope_store(qkv.view(m, -1).cuda(), n_heads, n_kv, d, ctx.positions, ctx.token_seq, sl, lane.page_table,
+                           None, None, None, 1.0, 0)
+        lists, bs = ops.select_blocks(ctx, q, lane, n_kv, scale, sparse)
+        ops.raise_on_kernel_error()
+        lists = lists.cpu()
+        checked = 0
+        for i, p in enumerate(sample):
+            if p + 1 <= sparse["dense_len"]:
+                assert lists[i, :, 0].tolist() == [-2] * n_kv                      # "dense": every key up to the query
+                checked += n_kv
+                continue
+            margins = []
+            want = plain.select_blocks(q_rows[i].float(), ck, p, scale, sparse, margins)
+            for j in range(n_kv):
+                if margins[j] < (1e-4 if dtype == "float32" else 5e-3):
+                    continue
+                row = lists[i, j].tolist()
+                got = row[:next((x for x, b in enumerate(row) if b < 0), len(row))]
+                assert got == want[j], (captured, p, j, got, want[j])
+                assert len(got) == 64 + 32              # the leading block and 63 chosen ones, then the local window
+                checked += 1
+        assert checked >= 0.8 * m * n_kv, (checked, m * n_kv)

@@ -50,6 +50,15 @@ def _case(ops, lens, n_heads, n_kv, d, seed):
     sl = torch.tensor(slots, dtype=torch.int32).cuda()
     q = ops.rope_store(qkv, n_heads, n_kv, d, positions, token_seq, sl, lane.page_table, lane.k, lane.v, None, 1.0, 0)
     last = (torch.tensor(lens).cumsum(0) - 1).cuda()
+    # the same attention in plain fp32 torch, from the rows that went into the cache (no rotation was applied)
+    rows = qkv.float().cpu().view(T, n_heads + 2 * n_kv, d)
+    group, want, o = n_heads // n_kv, [], 0
+    for n in lens:
+        qs, ks, vs = rows[o + n - 1, :n_heads], rows[o:o + n, n_heads:n_heads + n_kv], rows[o:o + n, n_heads + n_kv:]
+        heads = [torch.softmax((ks[:, h // group] @ qs[h]) / math.sqrt(d), dim=0) @ vs[:, h // group] for h in range(n_heads)]
+        want.append(torch.cat(heads))
+        o += n
+    _case.reference = torch.stack(want)
     return cache, lane, q[last].contiguous(), torch.tensor(lens, dtype=torch.int32).cuda(), sl
 
 
@@ -80,6 +89,8 @@ def test_static_scratch_entry_matches_the_ordinary_one_twice():
         assert status == 0, msg
         err = float((got.float() - want.float()).abs().max() / want.float().abs().max())
         assert err < TOL, err
+        ref = _case.reference                      # not only the two entry points against each other
+        assert float((got.float().cpu() - ref).abs().max() / ref.abs().max()) < TOL
 
 
 def test_static_scratch_entry_refuses_what_does_not_fit():
