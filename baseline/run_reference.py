@@ -55,6 +55,11 @@ def write_folder(folder: str, m: dict, rope_scaling) -> None:
               os.path.join(folder, "model.safetensors"))
 
 
+def stage(what: str) -> None:
+    """A line on standard error before every stage, so that a crash inside the reference's native code shows where."""
+    print(f"[run_reference] {what}", file=sys.stderr, flush=True)
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--model-json", required=True, help="the benchmark's model sizes, as JSON")
@@ -97,8 +102,14 @@ def main() -> int:
             if rs is None and m.get("rope_scaling"):
                 notes.append("plain rotary factors (the long factors change no timing)")
             break
+    stage("constructing cpmcu.llm.LLM")
     llm = LLM(tmp, memory_limit=0.8, chunk_length=a.prefill_tokens, dtype=torch.bfloat16, cuda_graph=True)
+    if os.environ.get("CPMCU_BT"):                            # a native backtrace on a crash, for finding where it is
+        import ctypes
+        ctypes.CDLL(os.environ["CPMCU_BT"]).install()
+    stage("init_storage")
     llm.init_storage()
+    stage(f"max_total_length {llm.max_total_length}; load_from_hf")
     if stock_rope:
         llm.load_from_hf()                                    # the final norm from the file, then the rotary table
     else:
@@ -115,6 +126,7 @@ def main() -> int:
               "gate_proj": (I, H), "up_proj": (I, H), "down_proj": (H, I)}
     rand = {k: (torch.randn(s, generator=g) * 0.02).to(torch.bfloat16) for k, s in shapes.items()}
     norm = (1.0 + 0.02 * torch.randn(H, generator=g)).to(torch.bfloat16)
+    stage("loading random matrices through LLM._load")
     with torch.no_grad():
         llm._load("model.embed_tokens.weight", (torch.randn(V, H, generator=g) * 0.02).to(torch.bfloat16))
         llm._load("lm_head.weight", (torch.randn(V, H, generator=g) * 0.02).to(torch.bfloat16))
@@ -142,12 +154,14 @@ def main() -> int:
         return e0.elapsed_time(e1)
 
     # prefill of one prompt, last-row logits (the reference's prefill), median of three after a warm-up
+    stage("prefill")
     P = a.prefill_tokens
     pos = torch.arange(P, dtype=torch.int32, device="cuda")
     times = [event_ms(lambda r=r: llm.prefill(ids(P, 500 + r), pos)) for r in range(4)][1:]
     prefill_ms = statistics.median(times)
 
     # decode, one sequence: the timed steps end at the context length
+    stage("decode")
     start = a.context - a.steps - a.warmup - 1
     llm.prefill(ids(start, 100), torch.arange(start, dtype=torch.int32, device="cuda"))
     tok = torch.tensor([5], dtype=torch.int32, device="cuda")
@@ -167,6 +181,7 @@ def main() -> int:
     decode_ms = event_ms(lambda: steps(a.steps)) / a.steps
 
     # end to end: the reference's own generate(), host ids in, host tokens out
+    stage("generate")
     prompt = ids(a.context - a.steps - 1, 900)
     llm.generate(prompt[:64], generation_length=4)
     tokens, decode_time, prefill_time = llm.generate(prompt, generation_length=a.steps + 1, terminators=[])

@@ -31,6 +31,12 @@ MODEL = {
     "scale_emb": 12, "dim_model_base": 256, "scale_depth": 1.4, "tie_word_embeddings": False,
     "hidden_act": "silu", "torch_dtype": "bfloat16",
 }
+# MiniCPM4-0.5B layer sizes; random weights seed 3; tied head.
+MODEL_HALF_B = dict(MODEL, num_hidden_layers=24, hidden_size=1024, num_attention_heads=16, num_key_value_heads=2,
+                    head_dim=64, intermediate_size=4096, tie_word_embeddings=True)
+# InfLLM-v2 knobs of the long-context workload (8B sizes).
+SPARSE_8B = {"kernel_size": 32, "kernel_stride": 16, "block_size": 64, "init_blocks": 1, "topk": 64,
+             "window_size": 2048, "dense_len": 8192}
 FULL_LAYERS = 32
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
@@ -131,15 +137,18 @@ def reference_arm(steps: int, warmup: int) -> int:
         return 0
     line = next((l for l in reversed(p.stdout.splitlines()) if l.startswith("{") and '"impl"' in l), None)
     if p.returncode != 0 or line is None:
-        err = [l for l in (p.stderr or p.stdout).splitlines() if l.strip()]
+        err = [l.strip() for l in (p.stderr + "\n" + p.stdout).splitlines() if l.strip() and not l.startswith("{")]
+        picked = [l for l in err if "error" in l.lower() or "Error" in l or "Signal" in l][-3:] or err[-2:]
         print(json.dumps({"impl": "reference", "unavailable": f"the reference run failed (exit {p.returncode}): "
-                          + (err[-1][:300] if err else "no output")}))
+                          + (" | ".join(picked)[:400] if picked else "no output")}))
+        sys.stderr.write(p.stderr[-6000:])
         return 0
     print(line)
     return 0
 
 
-def build_engine(n_layers: int, max_tokens: int, max_batch: int):
+def build_engine(n_layers: int, max_tokens: int, max_batch: int, model: dict = None, seed: int = SEED,
+                 max_seq_tokens: int = None, chunk_tokens: int = None, sparse: dict = None):
     import torch
     from cpmcu_b200.cache import Cache
     from cpmcu_b200.engine import Stepper
@@ -147,18 +156,22 @@ def build_engine(n_layers: int, max_tokens: int, max_batch: int):
     from cpmcu_b200.registry import architecture
     from cpmcu_b200.weights import random_tensors
 
-    cfgd = dict(MODEL, num_hidden_layers=n_layers)
-    cfgd["rope_scaling"] = {"rope_type": "longrope", "long_factor": long_factors(64), "short_factor": [1.0] * 64,
+    cfgd = dict(model or MODEL, num_hidden_layers=n_layers)
+    half = cfgd["head_dim"] // 2
+    cfgd["rope_scaling"] = {"rope_type": "longrope", "long_factor": long_factors(half), "short_factor": [1.0] * half,
                             "original_max_position_embeddings": 32768}
+    if sparse:
+        cfgd["sparse_config"] = dict(sparse)
     arch = architecture("MiniCPMForCausalLM")
     cfg = arch.config_class.from_dict(cfgd)
     # the residual scale of the full depth, whatever number of layers is built
     model = build_model(arch, cfg, torch.bfloat16, "cuda:0")
     specs = model.weight_specs()
-    model.load_weights(random_tensors(specs, SEED, torch.bfloat16, std=0.02, norm_mean=1.0, device="cuda:0"))
+    model.load_weights(random_tensors(specs, seed, torch.bfloat16, std=0.02, norm_mean=1.0, device="cuda:0"))
+    chunk = chunk_tokens or PREFILL_TOKENS
     cache = Cache(model.cache_needs(), max_tokens=max_tokens, dtype=torch.bfloat16, device="cuda:0",
-                  n_slots=max_batch + 2, max_seq_tokens=CONTEXT + 64)
-    return cfg, model, cache, Stepper(model, cache, chunk_tokens=PREFILL_TOKENS)
+                  n_slots=max_batch + 2, max_seq_tokens=max_seq_tokens or CONTEXT + 64, max_step_tokens=chunk)
+    return cfg, model, cache, Stepper(model, cache, chunk_tokens=chunk)
 
 
 def random_prompt(vocab: int, n: int, seed: int) -> list:
@@ -167,7 +180,8 @@ def random_prompt(vocab: int, n: int, seed: int) -> list:
     return torch.randint(0, vocab, (n,), generator=g).tolist()
 
 
-def time_decode(stepper, batch: int, steps: int, warmup: int, vocab: int, sample_clocks: bool = False):
+def time_decode(stepper, batch: int, steps: int, warmup: int, vocab: int, sample_clocks: bool = False,
+                context: int = None):
     """Sequences are prefilled so that the timed steps end at the context length; returns
     (ms per step, clocks, launches in the timed region, bytes of cache read per step)."""
     import torch
@@ -176,7 +190,8 @@ def time_decode(stepper, batch: int, steps: int, warmup: int, vocab: int, sample
     from cpmcu_b200.ops import library
     from cpmcu_b200.sampling import SamplingParams
 
-    start_len = CONTEXT - steps - warmup - 1
+    context = context or CONTEXT
+    start_len = context - steps - warmup - 1
     slots = stepper.open(batch)
     first = []
     for i, s in enumerate(slots):                       # one prompt per step keeps the workspace small
@@ -199,7 +214,7 @@ def time_decode(stepper, batch: int, steps: int, warmup: int, vocab: int, sample
     torch.cuda.synchronize()
     ms = e0.elapsed_time(e1) / steps
     clocks = sampler.stop() if sample_clocks else None
-    mean_ctx = CONTEXT - 1 - steps / 2
+    mean_ctx = context - 1 - steps / 2
     cache_bytes = sum(stepper.model.blocks[e.layer].mixer.cache_bytes_read(int(mean_ctx)) for e in stepper.model.schedule) * batch
     launches = runner.launches_per_graph * steps
     for s in slots:
@@ -267,6 +282,120 @@ def time_e2e(cfg, model, steps: int, batch: int):
         "d2h_bytes_per_step": (backend.d2h_bytes - d0) / (decode_steps + 1),
         "prefill_tokens_per_s": stats.prompt_tokens / stats.prefill_time,
     }
+
+
+def loop_prefill(stepper, prompts, max_batch: int):
+    """Prompts of one batch through the generation loop's backend (chunked as the stepper is set up), one new token
+    each; returns (tokens per second, milliseconds)."""
+    import torch
+    from cpmcu_b200.engine.backend import EngineBackend
+    from cpmcu_b200.engine.generate import Request, run_requests
+    from cpmcu_b200.sampling import SamplingParams
+
+    backend = EngineBackend(stepper, max_batch=max_batch, use_graph=True, seed=SEED)
+    reqs = [Request(p, 1, SamplingParams(), (), key=i) for i, p in enumerate(prompts)]
+    run_requests(backend, [Request(p[:64], 1, SamplingParams(), (), key=i) for i, p in enumerate(prompts)],
+                 sync=torch.cuda.synchronize)                                   # warm-up
+    best = None
+    for _ in range(2):
+        _, stats = run_requests(backend, reqs, sync=torch.cuda.synchronize)
+        best = stats.prefill_time if best is None else min(best, stats.prefill_time)
+    stepper.close(backend.runner.pad_slot)
+    return sum(len(p) for p in prompts) / best, best * 1e3
+
+
+def workload_half_b(steps: int, warmup: int) -> int:
+    """MiniCPM4-0.5B layer sizes: 64 prompts of unequal lengths (uniform in [64, 2048]) prefilled in chunks of 512
+    packed tokens, and decode steps of the 64 sequences that end at a context of 8,192 tokens."""
+    import torch
+
+    batch, context, chunk = 64, 8192, 512
+    pk = peaks()
+    cfg, model, cache, stepper = build_engine(MODEL_HALF_B["num_hidden_layers"], batch * (context + 64) + 128, batch,
+                                              model=MODEL_HALF_B, seed=3, max_seq_tokens=context + 64, chunk_tokens=chunk)
+    g = torch.Generator().manual_seed(3)
+    lens = torch.randint(64, 2049, (batch,), generator=g).tolist()
+    prompts = [random_prompt(cfg.vocab_size, n, 300 + i) for i, n in enumerate(lens)]
+    prefill_tps, prefill_ms = loop_prefill(stepper, prompts, batch)
+    stepper.chunk_tokens = 2048                                                 # the long warm-up prompts in larger pieces
+    ms, clocks, launches, cache_bytes = time_decode(stepper, batch, steps, warmup, cfg.vocab_size, True, context=context)
+    weight_bytes = model.weight_bytes_per_step()
+    achieved = (weight_bytes + cache_bytes) / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "workload": "half_b", "metric": "decode tokens/s (MiniCPM4-0.5B sizes, bf16, batch 64, context 8192)",
+        "value": batch * 1000.0 / ms, "unit": "tokens/s", "ms_per_step": ms, "steps": steps, "warmup": warmup,
+        "dtype": "bf16", "data": "synthetic: uniform-random token ids, random weights N(0,0.02) seed 3",
+        "config": {"model": "MiniCPM4-0.5B sizes", "layers": cfg.num_hidden_layers, "hidden": cfg.hidden_size,
+                   "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+                   "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "tied_head": True, "global_batch": batch,
+                   "seq_len": context, "prompt_lengths": "uniform in [64, 2048]", "chunk_length": chunk, "cuda_graph": True,
+                   "peaks": pk["source"]},
+        "prefill": {"value": prefill_tps, "tokens": sum(lens), "ms": prefill_ms, "through": "generation loop"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "weight_bytes": weight_bytes, "cache_bytes": cache_bytes},
+        "clocks": clocks, "gpu_launches": launches,
+    }))
+    return 0
+
+
+def workload_sparse8b(steps: int, warmup: int, layers: int) -> int:
+    """MiniCPM4-8B layer sizes with InfLLM-v2 block-sparse attention: prompts of 16,384 and 30,000 tokens in one
+    batch, prefilled in chunks of 2,048 packed tokens through the generation loop, then decode steps of the two
+    sequences under a CUDA graph."""
+    import torch
+    from cpmcu_b200.engine import SequenceStep
+    from cpmcu_b200.engine.decode import DecodeRunner
+    from cpmcu_b200.sampling import SamplingParams
+
+    lens, context = [16384, 30000], 32768
+    pk = peaks()
+    cfg, model, cache, stepper = build_engine(layers, 3 * context + 256, 2, seed=4, max_seq_tokens=context + 64,
+                                              chunk_tokens=2048, sparse=SPARSE_8B)
+    prompts = [random_prompt(cfg.vocab_size, n, 40 + i) for i, n in enumerate(lens)]
+    prefill_tps, prefill_ms = loop_prefill(stepper, prompts, 2)
+    stepper.ops.raise_on_kernel_error()
+    slots = stepper.open(2)
+    first = []
+    for s_, p_ in zip(slots, prompts):
+        out = stepper.step([SequenceStep(s_, p_, [len(p_) - 1])])
+        first.append(int(out.argmax(dim=-1)[0]))
+    runner = DecodeRunner(stepper, use_graph=True, seed=SEED)
+    runner.start(slots, first, [0, 1], [1, 1], [SamplingParams()] * 2)
+    for _ in range(max(3, warmup)):
+        runner.step()
+    torch.cuda.synchronize()
+    sampler = ClockSampler()
+    sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        runner.step()
+    e1.record()
+    torch.cuda.synchronize()
+    clocks = sampler.stop()
+    stepper.ops.raise_on_kernel_error()
+    ms = e0.elapsed_time(e1) / steps
+    mean_ctx = [n + max(3, warmup) + steps // 2 for n in lens]
+    cache_bytes = sum(stepper.model.blocks[e.layer].mixer.cache_bytes_read(c) for e in stepper.model.schedule for c in mean_ctx)
+    dense_bytes = sum(2 * c * cfg.num_key_value_heads * cfg.head_dim * 2 * layers for c in mean_ctx)
+    weight_bytes = model.weight_bytes_per_step()
+    achieved = (weight_bytes + cache_bytes) / (ms * 1e-3) / 1e9
+    print(json.dumps({
+        "workload": "sparse8b", "metric": "decode ms/step and prefill tokens/s (MiniCPM4-8B sizes, InfLLM-v2, batch 2, context 32768)",
+        "value": 2 * 1000.0 / ms, "unit": "tokens/s", "ms_per_step": ms, "steps": steps, "warmup": max(3, warmup),
+        "dtype": "bf16", "data": "synthetic: uniform-random token ids, random weights N(0,0.02) seed 4",
+        "config": {"model": "MiniCPM4-8B sizes", "layers": layers, "layers_full": FULL_LAYERS, "hidden": cfg.hidden_size,
+                   "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads, "head_dim": cfg.head_dim,
+                   "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size, "global_batch": 2, "seq_len": context,
+                   "prompt_lengths": "16384 and 30000", "chunk_length": 2048, "attention": "InfLLM-v2 32/16/64/1/64/2048/8192",
+                   "cuda_graph": True, "peaks": pk["source"]},
+        "prefill": {"value": prefill_tps, "tokens": sum(lens), "ms": prefill_ms, "through": "generation loop"},
+        "roofline": {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": achieved / pk["hbm_gbs"], "weight_bytes": weight_bytes, "cache_bytes": cache_bytes,
+                     "cache_bytes_if_dense": dense_bytes},
+        "clocks": clocks, "gpu_launches": runner.launches_per_graph * steps,
+    }))
+    return 0
 
 
 def step_launches(name: str, batch: int, ctx: int, layers: int, reps: int) -> int:
@@ -388,6 +517,10 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="layers built (the full model has 32)")
     ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--workload", default="dense8b", choices=["dense8b", "half_b", "sparse8b"],
+                    help="dense8b: the headline line (8B sizes, batch 8, context 4096); half_b: 0.5B sizes, batch 64, prompts "
+                         "uniform in [64, 2048] chunked at 512, decode at context 8192 (256 steps by default); sparse8b: 8B "
+                         "sizes with InfLLM-v2, prompts of 16384 and 30000 tokens chunked at 2048, then decode steps")
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 / 64 points and the e2e run")
     ap.add_argument("--kernel", default=None, help="time one kernel alone: skinny_gemm, decode_attention, prefill_attention (tcgen05), prefill_attention_mma, gemm_tcgen05; or run eager steps of a 2-layer model for a launch list: decode_step, prefill_step")
     ap.add_argument("--ctx", type=int, default=CONTEXT, help="--kernel: cached tokens per sequence (or prompt tokens)")
@@ -401,6 +534,10 @@ def main() -> int:
     if a.gpus != 1:
         print("bench.py: this library runs on one GPU; --gpus must be 1")
         return 2
+    if a.workload == "half_b":
+        return workload_half_b(a.steps if a.steps != 128 else 256, max(3, a.warmup))
+    if a.workload == "sparse8b":
+        return workload_sparse8b(a.steps, a.warmup, a.layers)
     if a.kernel in ("decode_step", "prefill_step"):
         return step_launches(a.kernel, a.batch, a.ctx, a.layers if a.layers != FULL_LAYERS else 2, a.reps)
     if a.kernel:

@@ -245,6 +245,30 @@ class Cache:
     def length(self, slot: int) -> int:
         return self.lengths[slot]
 
+    def grow_by_one(self, slots: Sequence[int]) -> bool:
+        """Room for one more token in each of ``slots`` (what a decode step needs): a page is taken only where the
+        sequence's last page is full.  Returns True if a page table changed (``sync`` is then due).  All or nothing."""
+        full = [s for s in slots if self.lengths[s] % PAGE_TOKENS == 0]
+        if not full:
+            return False
+        for g in self.groups:
+            need = sum(max(0, pages_for(self.lengths[s] + 1) - len(g.pages_of_slot.get(s, []))) for s in full)
+            if need > g.pages.n_free:
+                raise CacheFull(f"the step needs {need} more pages, {g.pages.n_free} of {g.n_pages} are free "
+                                f"(this group of layers holds {g.n_pages * PAGE_TOKENS} tokens)")
+        for s in full:
+            self.reserve(s, self.lengths[s] + 1)
+        return True
+
+    def grown_by_one(self, slots: Sequence[int]) -> None:
+        """The step is over: every sequence of ``slots`` holds one token more."""
+        windowed = [g for g in self.groups if g.needs.window]
+        for s in slots:
+            n = self.lengths[s] + 1
+            self.lengths[s] = n
+            for g in windowed:
+                g.trim(s, n)
+
     def close_sequence(self, slot: int) -> None:
         if not self.slots.is_held(slot):
             raise HandleError(f"slot {slot} is not open (closed twice?)")

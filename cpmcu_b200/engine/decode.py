@@ -69,6 +69,7 @@ class DecodeRunner:
         self.slots: List[int] = []
         self.pinned = None
         self.pinned_in = None
+        self.feed_done = None
 
     # ---- one step's work on the device ----
     def _body(self, b: _Bucket, captured: bool, slots: Sequence[int] = ()) -> None:
@@ -89,6 +90,8 @@ class DecodeRunner:
             token_ids=b.ids, positions=b.positions, token_seq=b.token_seq, cu_q=b.cu_q,
             kv_len_dev=b.kv_len, slot_dev=b.slot, cache=self.cache,
         )
+        if not captured and self.stepper.taps is not None:
+            ctx.extras["taps"] = self.stepper.taps
         b.logits = self.model.forward(ctx, b.want_rows)
         self.ops.sample(b.logits, b.temperature, b.top_p, self.seed, b.seq_key, b.step_key, out=b.sampled)
         self.ops.advance_decode(b.ids, b.positions, b.kv_len, b.step_key, b.sampled, b.live)
@@ -157,22 +160,25 @@ class DecodeRunner:
         n = len(tokens)
         if self.pinned_in is None or self.pinned_in.numel() < self.current.size:
             self.pinned_in = torch.empty(max(64, self.current.size), dtype=torch.int32).pin_memory()
-        self.pinned_in[:n] = torch.tensor(list(tokens), dtype=torch.int32)
+            self.pinned_in_np = self.pinned_in.numpy()          # the same memory, written without building a tensor
+            self.feed_done = torch.cuda.Event()
+        else:
+            self.feed_done.synchronize()        # the last copy out of the pinned buffer must be over before it is rewritten
+        self.pinned_in_np[:n] = tokens
         self.current.ids[:n].copy_(self.pinned_in[:n], non_blocking=True)
+        self.feed_done.record()
 
     def step(self) -> torch.Tensor:
         """Runs one decode step of the current batch; returns the sampled tokens (device,
         int32, one per live sequence; valid until the next step)."""
         b = self.current
-        for s in self.slots:
-            self.cache.reserve(s, self.cache.length(s) + 1)
-        self.cache.sync()
+        if self.cache.grow_by_one(self.slots):
+            self.cache.sync()
         if b.graph is not None:
             b.graph.replay()
         else:
             self._body(b, captured=False, slots=self.slots)
-        for s in self.slots:
-            self.cache.set_length(s, self.cache.length(s) + 1)
+        self.cache.grown_by_one(self.slots)
         return b.sampled[:len(self.slots)]
 
     @property
@@ -188,6 +194,9 @@ class DecodeRunner:
         n = len(self.slots)
         if self.pinned is None or self.pinned.numel() < self.current.size:
             self.pinned = torch.empty(max(64, self.current.size), dtype=torch.int32).pin_memory()
+            self.pinned_np = self.pinned.numpy()
+            self.read_done = torch.cuda.Event()
         self.pinned[:n].copy_(self.current.sampled[:n], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return self.pinned[:n].tolist()
+        self.read_done.record()
+        self.read_done.synchronize()
+        return self.pinned_np[:n].tolist()

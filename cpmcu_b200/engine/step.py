@@ -74,6 +74,7 @@ class Stepper:
         self.ops = model.ops
         self.chunk_tokens = int(chunk_tokens)
         self.vocab_size = model.spec.vocab_size
+        self.taps: Optional[dict] = None      # when set, parts may leave intermediate results in it (ctx.extras["taps"])
 
     # ---- sequences ----
     def open(self, n: int) -> List[int]:
@@ -183,4 +184,6 @@ class Stepper:
         )
         rows = cut(len(want_rows)) if want_rows else None
         ctx.extras["q_tiles"] = (cut(len(tile_seq)), cut(len(tile_row)), len(tile_seq))
+        if self.taps is not None:
+            ctx.extras["taps"] = self.taps
         return self.model.forward(ctx, rows)

@@ -77,7 +77,14 @@ class GroupedQueryAttention(Mixer):
 
     def cache_bytes_read(self, kv_len: int) -> int:
         keys = min(kv_len, self.window) if self.window else kv_len
-        return 2 * keys * self.n_kv * self.d * self.ops.element_size
+        pooled = 0
+        if self.sparse is not None and kv_len > self.sparse.get("dense_len", 0):
+            # the leading and chosen blocks (topk of them) and the local window, and every visible pooled key (fp32)
+            sp = self.sparse
+            blocks = sp["topk"] + sp["window_size"] // sp["block_size"]
+            keys = min(kv_len, blocks * sp["block_size"])
+            pooled = max(0, (kv_len - sp["kernel_size"]) // sp["kernel_stride"] + 1) * self.n_kv * self.d * 4
+        return 2 * keys * self.n_kv * self.d * self.ops.element_size + pooled
 
     # ---- forward ----
     def forward(self, ctx, y: torch.Tensor, lane, writes_cache: bool) -> torch.Tensor:
@@ -99,5 +106,11 @@ class GroupedQueryAttention(Mixer):
                 ops.pool_keys(ctx, lane, self.n_kv, self.d, self.sparse["kernel_size"], self.sparse["kernel_stride"])
             if ctx.captured or ctx.max_kv_len > self.sparse.get("dense_len", 0):
                 block_list, block_size = ops.select_blocks(ctx, q, lane, self.n_kv, self.scale, self.sparse)
+                taps = ctx.extras.get("taps")
+                if taps is not None and not ctx.captured:
+                    # a caller that wants to see the choice (tests do): lane, the step's slots, and per token its
+                    # sequence, position and block lists
+                    taps.setdefault("block_lists", []).append(
+                        (lane.index, list(ctx.slots), ctx.token_seq.clone(), ctx.positions.clone(), block_list.clone()))
         out = ops.attention(ctx, q, lane, self.n_kv, self.scale, self.window, block_list, block_size)
         return ops.linear(out, self.w_o)

@@ -187,11 +187,55 @@ def select_blocks(q_p: Tensor, ck: Tensor, p: int, scale: float, sparse: dict,
     return result
 
 
+def selection_slack(q_p: Tensor, ck: Tensor, p: int, scale: float, sparse: dict, lists: List[List[int]]) -> float:
+    """How far a given choice of blocks (one ascending list per kv head, as an engine made it) is from the
+    rule of ``select_blocks``: 0 if it is the plain choice or differs from it only among equal scores; else the
+    largest relative amount by which a chosen block's score lies below the score of the last block the plain rule
+    takes (a choice between nearly equal scores that rounding turned the other way gives a tiny number).  The
+    forced leading blocks and the blocks of the local window must be exactly those of the rule, and the number
+    of chosen blocks too: infinity otherwise."""
+    ks, st, bs = sparse["kernel_size"], sparse["kernel_stride"], sparse["block_size"]
+    init_blocks, topk = sparse.get("init_blocks", 1), sparse["topk"]
+    local_blocks = sparse["window_size"] // bs
+    nh, n_kv = q_p.shape[0], ck.shape[1]
+    group = nh // n_kv
+    n_vis = (p + 1 - ks) // st + 1 if p + 1 >= ks else 0
+    qb = p // bs
+    last_choice = qb - local_blocks
+    per_block, reach_back = bs // st, ks // st - 1
+    worst = 0.0
+    for j in range(n_kv):
+        score = torch.zeros(n_vis, dtype=q_p.dtype)
+        if n_vis > 0:
+            for h in range(j * group, (j + 1) * group):
+                score += torch.softmax((ck[:n_vis, j] @ q_p[h]) * scale, dim=0)
+        forced = set(range(min(init_blocks, qb + 1))) | set(range(max(0, last_choice + 1), qb + 1))
+        cand = {}
+        for k in range(init_blocks, last_choice + 1):
+            lo, hi = max(0, k * per_block - reach_back), min(n_vis, (k + 1) * per_block)
+            if hi > lo:
+                cand[k] = float(score[lo:hi].max())
+        room = min(max(0, topk - init_blocks), len(cand))
+        got = set(lists[j])
+        far = got - forced
+        if not forced <= got or len(far) != room or not far <= set(cand):
+            return float("inf")
+        if room == 0 or room == len(cand):
+            continue
+        cutoff = sorted(cand.values(), reverse=True)[room - 1]
+        for k in far:
+            worst = max(worst, (cutoff - cand[k]) / max(abs(cutoff), 1e-30))
+    return worst
+
+
 def sparse_attention(q: Tensor, k: Tensor, v: Tensor, scale: float, sparse: dict,
-                     margins: Optional[List[float]] = None) -> Tensor:
+                     margins: Optional[List[float]] = None, chosen: Optional[Dict[int, List[List[int]]]] = None,
+                     slack: Optional[List[float]] = None) -> Tensor:
     """Per query: dense if it sees at most dense_len keys (the reference's sparse_switch,
     src/model/minicpm4/minicpm4_attn.cuh:116), else attention over the keys of its
-    selected blocks that are at or before it (src/flash_attn/src/flash_blockmask.h:15-93)."""
+    selected blocks that are at or before it (src/flash_attn/src/flash_blockmask.h:15-93).
+    ``chosen`` (position -> one block list per kv head) replaces the selection for the positions beyond
+    dense_len; it must then name every such position."""
     S, nh, d = q.shape
     n_kv = k.shape[1]
     group = nh // n_kv
@@ -203,8 +247,15 @@ def sparse_attention(q: Tensor, k: Tensor, v: Tensor, scale: float, sparse: dict
         if p + 1 <= sparse.get("dense_len", 0):
             continue
         here: Optional[List[float]] = [] if margins is not None else None
-        blocks = select_blocks(q[p], ck, p, scale, sparse, here)
-        if margins is not None:
+        if chosen is not None:
+            # the blocks an engine chose for this query: attended as given; how far the choice is from the
+            # rule goes into ``slack`` (see selection_slack)
+            blocks = chosen[p]
+            if slack is not None:
+                slack.append(selection_slack(q[p], ck, p, scale, sparse, blocks))
+        else:
+            blocks = select_blocks(q[p], ck, p, scale, sparse, here)
+        if margins is not None and chosen is None:
             margins[p] = min(margins[p], min(here))
         for h in range(nh):
             keys = [j for b in blocks[h // group] for j in range(b * bs, min((b + 1) * bs, p + 1))]
@@ -216,7 +267,7 @@ def sparse_attention(q: Tensor, k: Tensor, v: Tensor, scale: float, sparse: dict
 
 def attention_layer(y: Tensor, w: Dict[str, Tensor], prefix: str, cfg: dict, positions: Tensor,
                     shared_kv: Optional[Tuple[Tensor, Tensor]] = None,
-                    margins: Optional[List[float]] = None) -> Tuple[Tensor, Tuple[Tensor, Tensor]]:
+                    margins: Optional[List[float]] = None, chosen=None, slack=None) -> Tuple[Tensor, Tuple[Tensor, Tensor]]:
     """src/model/attn.cuh:185-229: q, k, v projections without bias, rotary on q and k (keys
     are kept rotated), attention, output projection.  Returns (output, (k, v))."""
     nh, nkv, d = cfg["num_attention_heads"], cfg.get("num_key_value_heads") or cfg["num_attention_heads"], head_dim(cfg)
@@ -232,7 +283,7 @@ def attention_layer(y: Tensor, w: Dict[str, Tensor], prefix: str, cfg: dict, pos
         k, v = shared_kv
     scale = 1.0 / math.sqrt(d)
     sparse = cfg.get("sparse_config")
-    o = sparse_attention(q, k, v, scale, sparse, margins) if sparse else dense_attention(q, k, v, scale)
+    o = sparse_attention(q, k, v, scale, sparse, margins, chosen, slack) if sparse else dense_attention(q, k, v, scale)
     return o.reshape(S, nh * d) @ w[prefix + "o_proj.weight"].T, (k, v)
 
 
@@ -257,7 +308,8 @@ def lm_head(y: Tensor, w: Dict[str, Tensor], cfg: dict, scale: float) -> Tensor:
 
 def forward(cfg: dict, weights: Dict[str, Tensor], ids: Sequence[int], dtype: torch.dtype = torch.float32,
             schedule: Optional[Sequence[Tuple[int, int, bool]]] = None,
-            margins: Optional[List[float]] = None) -> Tensor:
+            margins: Optional[List[float]] = None, chosen: Optional[Dict[int, Dict[int, List[List[int]]]]] = None,
+            slack: Optional[List[float]] = None) -> Tensor:
     """Logits [S, vocab] at every position of one sequence.
 
     Order of operations as src/model/model.cuh:145-153 and src/model/layer.cuh:47-67:
@@ -265,7 +317,9 @@ def forward(cfg: dict, weights: Dict[str, Tensor], ids: Sequence[int], dtype: to
     logits = head(norm(x)).  ``schedule`` lists runs (layer, cache lane, writes): a run
     that does not write uses the keys and values an earlier run stored in that lane.
     ``margins``, if given, must be a list of len(ids) infinities; it receives, per position, the
-    smallest block-choice gap over all layers and kv heads (see select_blocks).
+    smallest block-choice gap over all layers and kv heads (see select_blocks).  ``chosen`` (cache lane ->
+    position -> block lists) makes the sparse attention use an engine's block choice instead of its own, and
+    ``slack`` receives how far each such choice is from the rule (see selection_slack).
     """
     w = {k: v.to(dtype) for k, v in weights.items()}
     se, rs, sl = scales(cfg)
@@ -279,7 +333,8 @@ def forward(cfg: dict, weights: Dict[str, Tensor], ids: Sequence[int], dtype: to
     for layer, lane, writes in schedule:
         p = f"model.layers.{layer}."
         y = rms_norm(x, w[p + "input_layernorm.weight"], eps)
-        a, kv = attention_layer(y, w, p + "self_attn.", cfg, positions, None if writes else lanes[lane], margins)
+        a, kv = attention_layer(y, w, p + "self_attn.", cfg, positions, None if writes else lanes[lane], margins,
+                                None if chosen is None else chosen[lane], slack)
         if writes:
             lanes[lane] = kv
         x = x + rs * a

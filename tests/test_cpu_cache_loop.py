@@ -273,3 +273,29 @@ def test_engine_backend_gives_slots_back_when_a_step_fails():
     cache.check_consistent()
     assert cache.slots.n_held == 0 and cache.tokens_held() == 0
     assert be.max_sequence_pages() == 3 and be.vocab_size() == 50
+
+
+def test_decode_steps_take_pages_only_at_page_edges():
+    c = _cache(64 * 12, n_slots=4)
+    a, b = c.open_sequence(), c.open_sequence()
+    c.reserve(a, 63); c.set_length(a, 63)
+    c.reserve(b, 64); c.set_length(b, 64)
+    assert c.grow_by_one([a, b]) is True           # b's last page is full
+    c.grown_by_one([a, b])
+    assert (c.length(a), c.length(b)) == (64, 65)
+    assert c.grow_by_one([b]) is False             # room left in b's second page
+    assert c.grow_by_one([a, b]) is True           # now a's page is full
+    c.grown_by_one([a, b])
+    c.check_consistent()
+    for g in c.groups:
+        if not g.needs.window:
+            assert g.pages_held(a) == 2 and g.pages_held(b) == 2
+    # all or nothing: a step that cannot get its pages takes none
+    small = Cache([CacheNeeds(kv_heads=1, head_dim=16)], max_tokens=64 * 3, dtype=torch.float32, device="cpu", n_slots=3)
+    x, y = small.open_sequence(), small.open_sequence()
+    small.reserve(x, 64); small.set_length(x, 64)
+    small.reserve(y, 128); small.set_length(y, 128)
+    with pytest.raises(CacheFull):
+        small.grow_by_one([x, y])
+    assert small.groups[0].pages.n_held == 3
+    small.check_consistent()

@@ -65,8 +65,7 @@ def test_generates_through_llm_like_the_plain_implementation(toy_folder, graph):
 @pytest.mark.parametrize("graph", [False, True])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_runner_logits_of_the_toy_architecture(toy_folder, dtype, graph):
-    """The decode runner fed with given tokens, logits of every step against the plain implementation; in bf16
-    up to the first position whose routing decision is a near tie."""
+    """The decode runner fed with given tokens, logits of every step against the plain implementation."""
     from cpmcu_b200.cache import Cache
     from cpmcu_b200.engine import Stepper
     from cpmcu_b200.loading import load_model
@@ -76,23 +75,30 @@ def test_runner_logits_of_the_toy_architecture(toy_folder, dtype, graph):
     _, _, model = load_model(folder, dtype)
     st = Stepper(model, Cache(model.cache_needs(), 64 * 8, DT[dtype], "cuda:0"), chunk_tokens=16)
     lens, extra = (30, 2, 11), (14, 20, 6)
-    seqs = [helpers.random_ids(cfg["vocab_size"], L + e, 70 + L) for L, e in zip(lens, extra)]
-    refs = [toy_arch.plain_logits(cfg, w, ids) for ids in seqs]
-    firm_upto = []
-    for ids, (_, margin) in zip(seqs, refs):
-        firm = margin > (0.0 if dtype == "float32" else 0.05)
-        firm_upto.append(len(ids) if bool(firm.all()) else int((~firm).nonzero()[0]))
+    # A routing decision between two nearly equal router logits may fall the other way in bf16, and every later
+    # position of that sequence then differs (through the state and the attention).  So the sequences are
+    # picked, by trying seeds, such that the two best router logits are at least 0.03 apart at every position
+    # (the logits are of order 1, their bf16 noise of order 0.005).
+    seqs, refs = [], []
+    for L, e in zip(lens, extra):
+        for seed in range(70 + L, 70 + L + 400):
+            ids = helpers.random_ids(cfg["vocab_size"], L + e, seed)
+            ref = toy_arch.plain_logits(cfg, w, ids)
+            if float(ref[1].min()) > 0.03:
+                break
+        else:
+            raise AssertionError("no sequence with firm routing found")
+        seqs.append(ids)
+        refs.append(ref)
     compared = [0]
 
-    def check(i, rows, positions):
-        if positions[0] >= firm_upto[i]:
-            return
+    def check(i, rows, positions, blocks):
         err = helpers.rel_err(rows, refs[i][0][positions])
         assert err < {"float32": 2e-5, "bfloat16": 2e-2}[dtype], (i, positions, err)
-        compared[0] += 1
+        compared[0] += len(positions)
 
     helpers.runner_parity(st, seqs, lens, check, graph)
-    assert compared[0] >= (3 + sum(extra)) * (1.0 if dtype == "float32" else 0.5)
+    assert compared[0] == 3 + sum(extra)
 
 
 @pytest.mark.parametrize("graph", ["true", "false"])

@@ -81,3 +81,187 @@ def test_real_layer_sizes_bf16_against_float32(name, cfgd):
         # bound is the bf16 bound of the small models with room for that tail.
         err = helpers.rel_err(g, w)
         assert err < 2 * helpers.TOL["bfloat16"], (name, i, err)
+
+
+# ---------------------------------------------------------------------------
+# the two long workloads, through the Python entry point's own storage sizing and the decode runner under a graph
+# ---------------------------------------------------------------------------
+
+SPARSE_8B = {"kernel_size": 32, "kernel_stride": 16, "block_size": 64, "init_blocks": 1, "topk": 64, "window_size": 2048,
+             "dense_len": 8192}
+
+
+def _llm(cfgd, dtype, seed, tmp, chunk, max_tokens, max_batch, apply_sparse=True):
+    """An ``LLM`` over a folder that holds the configuration only; the weights are made on the device (the same
+    bf16-rounded values for both precisions)."""
+    import json
+    import os
+
+    from cpmcu_b200 import LLM
+    from cpmcu_b200.weights import random_tensors
+
+    half = cfgd["head_dim"] // 2
+    cfgd = dict(cfgd, rope_scaling={"rope_type": "longrope", "long_factor": _long_factors(half), "short_factor": [1.0] * half,
+                                    "original_max_position_embeddings": 32768})
+    os.makedirs(tmp, exist_ok=True)
+    with open(os.path.join(tmp, "config.json"), "w") as f:
+        json.dump(cfgd, f)
+    llm = LLM(tmp, dtype=dtype, cuda_graph=True, chunk_length=chunk, max_tokens=max_tokens, max_batch=max_batch,
+              apply_sparse=apply_sparse)
+    llm.init_storage()                                           # default sizing per sequence: nothing about the length is said
+    w = random_tensors(llm.model.weight_specs(), seed, torch.bfloat16, std=0.02, device="cuda:0")
+    llm.load_tensors({k: v.to(llm.dtype) for k, v in w.items()})
+    return llm
+
+
+def _prompt_rows_and_decode(llm, seqs, lens, want, n_steps, use_graph=True, record=False):
+    """Prompts in one (chunked) step with logits at ``want[i]``, then ``n_steps`` decode steps of the whole batch,
+    fed with the sequences' own next tokens.  Returns (prompt rows per sequence, decode rows [steps, seqs, vocab],
+    block choices): with ``record`` (steps that are not recorded into a graph only) the sparse attention's block
+    lists at the wanted prompt rows and at every decode step, as {(lane, sequence, position): int32 [kv heads, cap]}."""
+    from cpmcu_b200.engine import SequenceStep
+    from cpmcu_b200.engine.decode import DecodeRunner
+    from cpmcu_b200.sampling import SamplingParams
+
+    st = llm.stepper
+    if record:
+        helpers.record_blocks(st)
+    slots = st.open(len(seqs))
+    out = st.step([SequenceStep(s, ids[:L], w) for s, ids, L, w in zip(slots, seqs, lens, want)])
+    rows, o = [], 0
+    for w in want:
+        rows.append(out[o:o + len(w)].cpu())
+        o += len(w)
+    runner = DecodeRunner(st, use_graph=use_graph, seed=0)
+    n = len(seqs)
+    runner.start(slots, [ids[L] for ids, L in zip(seqs, lens)], list(range(n)), [0] * n, [SamplingParams()] * n)
+    decoded = []
+    for t in range(n_steps):
+        if t:
+            runner.feed([ids[L + t] for ids, L in zip(seqs, lens)])
+        runner.step()
+        decoded.append(runner.logits().cpu())
+    llm.ops.raise_on_kernel_error()
+    chosen = {}
+    if record:
+        for lane, step_slots, token_seq, positions, lists in st.taps["block_lists"]:
+            for i, slot in enumerate(slots):
+                if slot not in step_slots:
+                    continue
+                mine = token_seq == step_slots.index(slot)
+                keep = torch.zeros_like(mine)
+                for p in list(want[i]) + list(range(lens[i], lens[i] + n_steps)):
+                    keep |= mine & (positions == p)
+                for t in keep.nonzero().flatten().tolist():
+                    chosen[(lane, i, int(positions[t]))] = lists[t].cpu()
+    for s in slots:
+        st.close(s)
+    st.close(runner.pad_slot)
+    return rows, torch.stack(decoded), chosen
+
+
+def _overlap(a, b, keys):
+    """Smallest share of blocks that two runs chose alike, over ``keys`` and kv heads (lists are read up to their
+    terminator); 1.0 = the same choice everywhere."""
+    def cut(row):
+        return set(row[:next((x for x, v in enumerate(row) if v < 0), len(row))])
+    worst = 1.0
+    for k in keys:
+        for ra, rb in zip(a[k].tolist(), b[k].tolist()):
+            sa, sb = cut(ra), cut(rb)
+            assert len(sa) == len(sb), (k, len(sa), len(sb))
+            worst = min(worst, len(sa & sb) / max(1, len(sa)))
+    return worst
+
+
+def _rms(a, b):
+    return float((a - b).pow(2).mean().sqrt() / b.pow(2).mean().sqrt())
+
+
+def _close(a, b, what, rms_bound=2.5e-2, max_bound=2 * helpers.TOL["bfloat16"]):
+    assert torch.isfinite(a).all(), what
+    assert _rms(a, b) < rms_bound, (what, "rms", _rms(a, b))
+    err = helpers.rel_err(a, b)
+    assert err < max_bound, (what, "max", err)
+
+
+def test_long_context_sparse_workload_at_8b_layer_sizes(tmp_path):
+    """Two layers of the 8B sizes with the long-context sparse configuration (windows of 32 keys every 16, blocks of
+    64, 64 blocks, a local window of 2,048, dense up to 8,192): prompts of 16,384 and 30,000 tokens in one batch in
+    chunks of 2,048, then 128 decode steps, through the storage sizing of the Python entry point (nothing is said
+    about the longest sequence, so a captured step sizes its block selection by the cache's capacity).
+
+    With random weights the 100 to 470 candidate blocks of a query score nearly alike, so the float32 and the
+    bfloat16 run rarely choose exactly the same 63 of them in both layers and both kv heads (measured: 15 rows of
+    262), and a row whose choices differ in a few blocks differs by several percent (0.04 to 0.08 rms).  (That the
+    choice itself is the rule's is tested where it can be firm: the selection kernel alone at these sizes, on
+    scores that are spread out, and the small models row by row against the plain implementation.)  Here the
+    comparison is a chain: decode under a graph equals decode without one (bfloat16, same kernels); without a graph
+    both precisions leave their block choices, which must overlap in at least 85 % of the blocks for every row, layer
+    and head; rows with the same choices agree to the bf16 bound, the others to a loose one (a wrong result is off
+    by about 1.4), half of them within 0.08; rows up to dense_len agree with a run that attends densely."""
+    cfgd = dict(EIGHT_B, sparse_config=SPARSE_8B)
+    lens, steps = [16384, 30000], 128
+    seqs = [helpers.random_ids(cfgd["vocab_size"], n + steps, 5 + n) for n in lens]
+    want = [[0, 2047, 8191, 8192, 12000, 16383], [0, 8191, 8192, 20000, 29999]]
+    runs = {}
+    for key, dtype, sparse, graph in (("f32", torch.float32, True, False), ("bf16", torch.bfloat16, True, False),
+                                      ("bf16_graph", torch.bfloat16, True, True), ("dense", torch.bfloat16, False, True)):
+        llm = _llm(cfgd, dtype, 4, str(tmp_path / key), 2048, 3 * 32768, 2, apply_sparse=sparse)
+        assert llm.cache.max_pages_per_seq * 64 >= 3 * 32768 - 64            # nothing capped the sequences
+        runs[key] = _prompt_rows_and_decode(llm, seqs, lens, want, steps if sparse else 1, use_graph=graph,
+                                            record=sparse and not graph)
+        del llm
+        torch.cuda.empty_cache()
+    f32, bf16, graph, dense = runs["f32"], runs["bf16"], runs["bf16_graph"], runs["dense"]
+    # a graph changes nothing
+    assert helpers.rel_err(graph[1], bf16[1]) < 1e-3
+    for i in range(2):
+        assert helpers.rel_err(graph[0][i], bf16[0][i]) < 1e-3
+    same, loose = 0, []
+    for i in range(2):
+        places = [(bf16[0][i][k], f32[0][i][k], p) for k, p in enumerate(want[i])]
+        places += [(bf16[1][t, i], f32[1][t, i], lens[i] + t) for t in range(steps)]
+        for got, ref, p in places:
+            keys = [(lane, i, p) for lane in (0, 1)]
+            if p + 1 <= SPARSE_8B["dense_len"]:
+                assert keys[0] not in bf16[2] or int(bf16[2][keys[0]][0, 0]) == -2
+                _close(got, ref, ("dense row", i, p))
+                continue
+            share = _overlap(bf16[2], f32[2], keys)
+            assert share >= 0.85, ("block choices of the two precisions", i, p, share)
+            if share == 1.0:
+                _close(got, ref, ("same blocks", i, p))
+                same += 1
+            else:
+                assert _rms(got, ref) < 0.2, ("other blocks", i, p, _rms(got, ref))
+                loose.append(_rms(got, ref))
+    assert same + len(loose) == 2 * steps + 6 and same >= 1
+    assert sorted(loose)[len(loose) // 2] < 0.08, sorted(loose)[len(loose) // 2]
+    for i in range(2):
+        below = [k for k, p in enumerate(want[i]) if p + 1 <= SPARSE_8B["dense_len"]]
+        _close(bf16[0][i][below], dense[0][i][below], ("rows up to dense_len against dense attention", i),
+               rms_bound=1e-2, max_bound=helpers.TOL["bfloat16"])
+        above = [k for k, p in enumerate(want[i]) if p + 1 > SPARSE_8B["dense_len"]]
+        # the sparse rule matters at these lengths: dense attention gives other logits than either sparse run
+        assert _rms(dense[0][i][above], f32[0][i][above]) > 2 * _rms(bf16[0][i][above], f32[0][i][above])
+
+
+def test_half_b_workload_batch_64(tmp_path):
+    """The 0.5B sizes whole: 64 prompts of unequal lengths (uniform in [64, 2048]) in chunks of 512 packed tokens,
+    then 32 decode steps of the batch of 64 under a graph (bf16: the products of 9 to 64 rows).  bfloat16 against
+    the engine's float32 path, logits of every sequence's prompt end and of every decode step."""
+    g = torch.Generator().manual_seed(3)
+    lens = torch.randint(64, 2049, (64,), generator=g).tolist()
+    steps = 32
+    seqs = [helpers.random_ids(HALF_B["vocab_size"], n + steps, 11 + i) for i, n in enumerate(lens)]
+    want = [[n - 1] for n in lens]
+    results = {}
+    for key, dtype in (("f32", torch.float32), ("bf16", torch.bfloat16)):
+        llm = _llm(HALF_B, dtype, 3, str(tmp_path / key), 512, 64 * (2048 + 128), 64)
+        results[key] = _prompt_rows_and_decode(llm, seqs, lens, want, steps)
+        del llm
+        torch.cuda.empty_cache()
+    _close(torch.cat(results["bf16"][0]), torch.cat(results["f32"][0]), "prompt ends")
+    for t in range(0, steps, 8):
+        _close(results["bf16"][1][t:t + 8], results["f32"][1][t:t + 8], ("decode steps", t))

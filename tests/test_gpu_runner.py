@@ -37,13 +37,16 @@ def test_runner_logits_with_padding_and_shrinking_batches(model_folders, name, d
     cfg, st = _stepper(folder, dtype, 64 * 16)
     lens, extra = (70, 9, 33), (5, 20, 12)
     seqs = [helpers.random_ids(cfg.vocab_size, L + e, 50 + L) for L, e in zip(lens, extra)]
-    errs = []
+    helpers.record_blocks(st)                    # eager steps leave their block choices: every sparse row is compared
+    rows_seen = []
 
-    def check(i, rows, positions):
-        errs.append(helpers.check_rows(rows, folder, seqs[i], positions, dtype, label=(name, i, positions)))
+    def check(i, rows, positions, blocks):
+        assert positions == list(range(lens[i] - 1, lens[i] + extra[i]))
+        helpers.check_rows(rows, folder, seqs[i], positions, dtype, label=(name, i), blocks=blocks)
+        rows_seen.append(len(positions))
 
     steps = helpers.runner_parity(st, seqs, lens, check, graph)
-    assert steps == 20 and len(errs) == 3 + sum(extra)
+    assert steps == 20 and sum(rows_seen) == 3 + sum(extra)
     st.cache.check_consistent()
     assert st.cache.tokens_held() == 0
 
@@ -60,9 +63,9 @@ def test_runner_logits_bucket_of_64(model_folders, dtype, graph):
     seqs = [helpers.random_ids(cfg.vocab_size, L + e, 900 + i) for i, (L, e) in enumerate(zip(lens, extra))]
     count = [0]
 
-    def check(i, rows, positions):
-        helpers.check_rows(rows, folder, seqs[i], positions, dtype, label=(i, positions))
-        count[0] += 1
+    def check(i, rows, positions, blocks):
+        helpers.check_rows(rows, folder, seqs[i], positions, dtype, label=i)
+        count[0] += len(positions)
 
     assert helpers.runner_parity(st, seqs, lens, check, graph) == 6
     assert count[0] == 64 + sum(extra)
