@@ -398,8 +398,8 @@ def workload_sparse8b(steps: int, warmup: int, layers: int) -> int:
     return 0
 
 
-def step_launches(name: str, batch: int, ctx: int, layers: int, reps: int) -> int:
-    """A few eager steps of a model with few layers of the benchmark's sizes, one kernel launch after the other, for
+def step_launches(name: str, batch: int, ctx: int, layers: int, reps: int, workload: str = "dense8b") -> int:
+    """A few eager steps of a model with few layers of a workload's sizes, one kernel launch after the other, for
     a profiler's launch list: decode_step = one token for each of ``batch`` sequences that hold ``ctx`` tokens;
     prefill_step = a prompt of ``ctx`` tokens."""
     import torch
@@ -407,7 +407,9 @@ def step_launches(name: str, batch: int, ctx: int, layers: int, reps: int) -> in
 
     global CONTEXT
     CONTEXT = max(CONTEXT, ctx + 64)
-    cfg, model, cache, stepper = build_engine(layers, batch * (ctx + 128) + 128, batch)
+    cfg, model, cache, stepper = build_engine(layers, batch * (ctx + 128) + 128, batch,
+                                              model=MODEL_HALF_B if workload == "half_b" else MODEL,
+                                              sparse=SPARSE_8B if workload == "sparse8b" else None)
     if name == "decode_step":
         slots = stepper.open(batch)
         for i, s in enumerate(slots):
@@ -422,7 +424,7 @@ def step_launches(name: str, batch: int, ctx: int, layers: int, reps: int) -> in
             out = stepper.step([SequenceStep(slot, random_prompt(cfg.vocab_size, ctx, r), [ctx - 1])])
             torch.cuda.synchronize()
             stepper.close(slot)
-    print(json.dumps({"kernel": name, "batch": batch, "ctx": ctx, "layers": layers, "logits": list(out.shape)}))
+    print(json.dumps({"kernel": name, "workload": workload, "batch": batch, "ctx": ctx, "layers": layers, "logits": list(out.shape)}))
     return 0
 
 
@@ -534,12 +536,12 @@ def main() -> int:
     if a.gpus != 1:
         print("bench.py: this library runs on one GPU; --gpus must be 1")
         return 2
+    if a.kernel in ("decode_step", "prefill_step"):
+        return step_launches(a.kernel, a.batch, a.ctx, a.layers if a.layers != FULL_LAYERS else 2, a.reps, a.workload)
     if a.workload == "half_b":
         return workload_half_b(a.steps if a.steps != 128 else 256, max(3, a.warmup))
     if a.workload == "sparse8b":
         return workload_sparse8b(a.steps, a.warmup, a.layers)
-    if a.kernel in ("decode_step", "prefill_step"):
-        return step_launches(a.kernel, a.batch, a.ctx, a.layers if a.layers != FULL_LAYERS else 2, a.reps)
     if a.kernel:
         return kernel_bench(a.kernel, a.batch, a.ctx, a.rows, a.n, a.k, a.reps)
     a.warmup = max(3, a.warmup)
