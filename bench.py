@@ -150,8 +150,8 @@ def reference_arm(steps: int, warmup: int) -> int:
 def build_engine(n_layers: int, max_tokens: int, max_batch: int, model: dict = None, seed: int = SEED,
                  max_seq_tokens: int = None, chunk_tokens: int = None, sparse: dict = None):
     import torch
-    from cpmcu_b200.cache import Cache
     from cpmcu_b200.engine import Stepper
+    from cpmcu_b200.engine.storage import make_storage
     from cpmcu_b200.loading import build_model
     from cpmcu_b200.registry import architecture
     from cpmcu_b200.weights import random_tensors
@@ -166,12 +166,13 @@ def build_engine(n_layers: int, max_tokens: int, max_batch: int, model: dict = N
     cfg = arch.config_class.from_dict(cfgd)
     # the residual scale of the full depth, whatever number of layers is built
     model = build_model(arch, cfg, torch.bfloat16, "cuda:0")
-    specs = model.weight_specs()
-    model.load_weights(random_tensors(specs, seed, torch.bfloat16, std=0.02, norm_mean=1.0, device="cuda:0"))
     chunk = chunk_tokens or PREFILL_TOKENS
-    cache = Cache(model.cache_needs(), max_tokens=max_tokens, dtype=torch.bfloat16, device="cuda:0",
-                  n_slots=max_batch + 2, max_seq_tokens=max_seq_tokens or CONTEXT + 64, max_step_tokens=chunk)
-    return cfg, model, cache, Stepper(model, cache, chunk_tokens=chunk)
+    # one arena: weights, step workspace, per-sequence state and the key-value pages (as the Python entry point does)
+    storage = make_storage(model, chunk, max_batch, max_tokens=max_tokens, max_seq_tokens=max_seq_tokens or CONTEXT + 64,
+                           n_slots=max_batch + 2)
+    model.load_weights(random_tensors(model.weight_specs(), seed, torch.bfloat16, std=0.02, norm_mean=1.0, device="cuda:0"))
+    torch.cuda.empty_cache()                                         # the loader's tensors: their copies live in the arena
+    return cfg, model, storage.cache, Stepper(model, storage.cache, chunk_tokens=chunk)
 
 
 def random_prompt(vocab: int, n: int, seed: int) -> list:
@@ -252,19 +253,14 @@ def prefill_flops(cfg, n_layers: int, tokens: int) -> float:
     return gemm + attn
 
 
-def time_e2e(cfg, model, steps: int, batch: int):
-    """The same decode metric through the Python entry point: host token lists in,
+def time_e2e(cfg, stepper, steps: int, batch: int):
+    """The same decode metric through the Python entry point's loop: host token lists in,
     host token lists out, one device-to-host read of the sampled tokens per step."""
     import torch
-    from cpmcu_b200.cache import Cache
-    from cpmcu_b200.engine import Stepper
     from cpmcu_b200.engine.backend import EngineBackend
     from cpmcu_b200.engine.generate import Request, run_requests
     from cpmcu_b200.sampling import SamplingParams
 
-    cache = Cache(model.cache_needs(), max_tokens=batch * (CONTEXT + 64) + 64, dtype=torch.bfloat16, device="cuda:0",
-                  n_slots=batch + 2, max_seq_tokens=CONTEXT + 64)
-    stepper = Stepper(model, cache, chunk_tokens=PREFILL_TOKENS)
     backend = EngineBackend(stepper, max_batch=batch, use_graph=True, seed=SEED)
     n_new = steps + 1
     prompts = [random_prompt(cfg.vocab_size, CONTEXT - n_new, 900 + i) for i in range(batch)]
@@ -569,9 +565,7 @@ def main() -> int:
         for b in (1, 64):
             pms, _, _, _ = time_decode(stepper, b, min(a.steps, 64), a.warmup, cfg.vocab_size)
             points[f"decode_b{b}"] = b * 1000.0 / pms
-        del stepper, cache
-        torch.cuda.empty_cache()
-        e2e = time_e2e(cfg, model, a.steps, a.batch)
+        e2e = time_e2e(cfg, stepper, a.steps, a.batch)
 
     line = {
         "metric": "decode tokens/s (MiniCPM4-8B sizes, bf16, batch 8, context 4096)",

@@ -38,7 +38,12 @@ class CacheGroup:
     """Storage, pages and page table of the lanes that share one kind of needs."""
 
     def __init__(self, needs: CacheNeeds, lanes: List[int], n_pages: int, n_slots: int, max_pages_per_seq: int,
-                 dtype: torch.dtype, device: torch.device):
+                 dtype: torch.dtype, device: torch.device, make=None):
+        """``make(kind, shape, dtype, zero)`` gives the group its tensors (kind "state" or "pages"); by default they
+        come from torch's allocator."""
+        if make is None:
+            def make(kind, shape, dt, zero):
+                return (torch.zeros if zero else torch.empty)(shape, dtype=dt, device=device)
         self.needs = needs
         self.lanes = list(lanes)
         self.n_pages = n_pages
@@ -46,22 +51,21 @@ class CacheGroup:
         self.pages = FreeList(n_pages, "page")
         self.pages_of_slot: Dict[int, List[int]] = {}     # by logical page; RELEASED where the window has moved on
         self.first_live: Dict[int, int] = {}              # slot -> first logical page still held
-        self.page_table = torch.zeros(n_slots, max_pages_per_seq, dtype=torch.int32, device=device)
+        self.page_table = make("state", (n_slots, max_pages_per_seq), torch.int32, True)
         self._dirty: Dict[int, int] = {}      # slot -> first table column not yet on the device
         n = len(lanes)
         self.k = self.v = self.pooled = None
         if needs.kv_heads > 0:
             # zeros, not empty: a kernel may multiply a masked weight of 0 with whatever a page
             # holds beyond the sequence's end, and that has to be a finite number
-            self.k = torch.zeros((n, n_pages, needs.kv_heads, PAGE_TOKENS, needs.head_dim), dtype=dtype, device=device)
-            self.v = torch.zeros((n, n_pages, needs.kv_heads, needs.head_dim, PAGE_TOKENS), dtype=dtype, device=device)
+            self.k = make("pages", (n, n_pages, needs.kv_heads, PAGE_TOKENS, needs.head_dim), dtype, True)
+            self.v = make("pages", (n, n_pages, needs.kv_heads, needs.head_dim, PAGE_TOKENS), dtype, True)
             if needs.pooled_stride > 0:
                 if PAGE_TOKENS % needs.pooled_stride:
                     raise ValueError(f"pooled-key stride {needs.pooled_stride} must divide the page size {PAGE_TOKENS}")
                 per_page = PAGE_TOKENS // needs.pooled_stride
                 # pooled keys are kept in fp32 whatever the cache's type: block selection compares them
-                self.pooled = torch.empty((n, n_pages, needs.kv_heads, per_page, needs.head_dim),
-                                          dtype=torch.float32, device=device)
+                self.pooled = make("pages", (n, n_pages, needs.kv_heads, per_page, needs.head_dim), torch.float32, False)
 
     def bytes_per_token(self) -> int:
         if self.k is None:
@@ -152,13 +156,23 @@ class Lane:
 class Cache:
     def __init__(self, needs_per_lane: Sequence[CacheNeeds], max_tokens: int, dtype: torch.dtype,
                  device: "torch.device | str", n_slots: Optional[int] = None, max_seq_tokens: Optional[int] = None,
-                 max_step_tokens: Optional[int] = None):
+                 max_step_tokens: Optional[int] = None, state_region=None, page_region=None):
         """max_tokens: the most tokens live sequences hold together, each sequence's count
         rounded up to a whole page.  max_seq_tokens: the longest single sequence (default:
         all of max_tokens).  n_slots: the most live sequences (default: one per page, at
         most 1024).  max_step_tokens: the most tokens one step adds to a sequence; when given,
-        a group with a window is sized for window + step tokens per slot instead of max_tokens."""
+        a group with a window is sized for window + step tokens per slot instead of max_tokens.
+        state_region / page_region: regions of an arena (cpmcu_b200.memory) that hold the page tables and the
+        per-sequence state, and the pages; without them the tensors come from torch's allocator."""
         self.device = torch.device(device)
+        make = None
+        if state_region is not None or page_region is not None:
+            def make(kind, shape, dt, zero):
+                region = state_region if kind == "state" else page_region
+                if region is None:
+                    return (torch.zeros if zero else torch.empty)(shape, dtype=dt, device=self.device)
+                return region.tensor(shape, dt, zero=zero, what="page tables and per-sequence state" if kind == "state"
+                                     else "key-value pages")
         self.dtype = dtype
         n_pages = max(1, pages_for(max_tokens))
         self.n_pages = n_pages
@@ -181,11 +195,12 @@ class Cache:
                 # a sequence holds at most the pages its window and one step's tokens touch
                 per_slot = pages_for(needs.window + int(max_step_tokens)) + 1
                 group_pages = min(n_pages, self.n_slots * per_slot)
-            group = CacheGroup(needs, lane_ids, group_pages, self.n_slots, self.max_pages_per_seq, dtype, self.device)
+            group = CacheGroup(needs, lane_ids, group_pages, self.n_slots, self.max_pages_per_seq, dtype, self.device, make)
             self.groups.append(group)
             for j, lane_id in enumerate(lane_ids):
                 state = {
-                    name: torch.zeros((self.n_slots, *shape), dtype=sdtype, device=self.device)
+                    name: (make("state", (self.n_slots, *shape), sdtype, True) if make is not None
+                           else torch.zeros((self.n_slots, *shape), dtype=sdtype, device=self.device))
                     for name, (shape, sdtype) in needs_per_lane[lane_id].state.items()
                 }
                 self.lanes[lane_id] = Lane(lane_id, group, j, state)

@@ -92,6 +92,11 @@ class DecodeRunner:
         )
         if not captured and self.stepper.taps is not None:
             ctx.extras["taps"] = self.stepper.taps
+        ws = self.ops.workspace
+        if ws is not None:
+            ws.require(b.size, b.size)
+        self.ops.begin_step()
+        ctx.extras["step_begun"] = True
         b.logits = self.model.forward(ctx, b.want_rows)
         self.ops.sample(b.logits, b.temperature, b.top_p, self.seed, b.seq_key, b.step_key, out=b.sampled)
         self.ops.advance_decode(b.ids, b.positions, b.kv_len, b.step_key, b.sampled, b.live)

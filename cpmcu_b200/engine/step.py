@@ -162,12 +162,17 @@ class Stepper:
             q_lens.append(count)
             slots.append(s.slot)
         n_tok, n_seq = len(ids), len(slots)
+        ws = self.ops.workspace
+        if ws is not None:
+            ws.require(n_tok, n_seq)          # a step the workspace was not sized for is refused before anything runs
+        self.ops.begin_step()
         # query tiles of the prefill attention kernel: (sequence, first token of the tile)
         tile_seq = [j for j, n in enumerate(q_lens) for _ in range(0, n, PREFILL_TILE_ROWS)]
         tile_row = [r for n in q_lens for r in range(0, n, PREFILL_TILE_ROWS)]
         packed = torch.tensor(ids + positions + token_seq + cu_q + kv_lens + slots + want_rows + tile_seq + tile_row,
                               dtype=torch.int32)
-        dev = packed.to(self.ops.device)
+        dev = self.ops.empty(packed.numel(), dtype=torch.int32)
+        dev.copy_(packed)                     # pageable staging: the copy is over when this returns
         o = 0
 
         def cut(n: int) -> torch.Tensor:
@@ -184,6 +189,7 @@ class Stepper:
         )
         rows = cut(len(want_rows)) if want_rows else None
         ctx.extras["q_tiles"] = (cut(len(tile_seq)), cut(len(tile_row)), len(tile_seq))
+        ctx.extras["step_begun"] = True
         if self.taps is not None:
             ctx.extras["taps"] = self.taps
         return self.model.forward(ctx, rows)

@@ -36,9 +36,13 @@ class LLM:
     def __init__(self, path: str, memory_limit: float = 0.8, chunk_length: int = 1024, dtype=None,
                  cuda_graph: bool = False, temperature: float = 0.0, random_seed: Optional[int] = None,
                  top_p: float = 1.0, max_batch: int = 64, max_tokens: Optional[int] = None,
-                 max_seq_tokens: Optional[int] = None, device: str = "cuda:0", apply_sparse: bool = True):
+                 max_seq_tokens: Optional[int] = None, device: str = "cuda:0", apply_sparse: bool = True,
+                 use_arena: bool = True):
         """``apply_sparse`` False runs a model whose configuration has a ``sparse_config`` with dense attention
-        (the reference's switch of the same name, cpmcu/llm.py:32, chooses the other way round)."""
+        (the reference's switch of the same name, cpmcu/llm.py:32, chooses the other way round).  ``use_arena``
+        False leaves every tensor to torch's allocator (``max_tokens`` must then be given)."""
+        self.use_arena = bool(use_arena)
+        self.storage = None
         self.path = path
         self.arch, self.config = load_config(path)
         if not apply_sparse and getattr(self.config, "sparse_config", None) is not None:
@@ -75,36 +79,27 @@ class LLM:
             total += n * (es if spec.role == "matrix" else 4)
         return total
 
-    def _workspace_bytes(self) -> int:
-        spec = self.model.spec
-        es = self.ops.element_size
-        widest = max((sum(s[0] for s in [w.shape for w in b.weight_specs().values() if len(w.shape) == 2])
-                      for b in self.model.blocks), default=spec.hidden_size)
-        per_token = spec.hidden_size * 4 * 2 + (spec.hidden_size * 4 + widest * 2) * es
-        return 2 * self.chunk_length * per_token + 3 * self.max_batch * spec.vocab_size * 4 + (256 << 20)
-
     def init_storage(self) -> int:
-        """Sizes the cache from the memory limit; returns the number of tokens it holds
-        (the reference returns its ``max_total_length`` here, cpmcu/llm.py:115-116)."""
-        needs = self.model.cache_needs()
-        probe = Cache(needs, max_tokens=PAGE_TOKENS, dtype=self.dtype, device=self.device, n_slots=2)
-        per_token = max(1, probe.bytes_per_token())
-        del probe
-        tokens = self.max_tokens
-        if tokens is None:
-            free, total = torch.cuda.mem_get_info(torch.device(self.device))
-            budget = min(free, int(total * self.memory_limit)) - self._workspace_bytes()
-            if not self.model.loaded:
-                budget -= self._weight_bytes()
-            tokens = max(0, budget) // per_token
-            if tokens < PAGE_TOKENS * 2:
-                raise MemoryError(f"memory_limit {self.memory_limit} leaves no room for a cache "
-                                  f"(weights {self._weight_bytes() >> 20} MiB, {free >> 20} MiB free)")
-        tokens = (int(tokens) // PAGE_TOKENS) * PAGE_TOKENS
-        per_seq = self.max_seq_tokens or min(tokens, max(self.model.spec.max_positions, 4096) * 8)
-        self.cache = Cache(needs, max_tokens=tokens, dtype=self.dtype, device=self.device,
-                           n_slots=min(max(2, tokens // PAGE_TOKENS), self.max_batch * 2 + 2), max_seq_tokens=per_seq,
-                           max_step_tokens=self.chunk_length)
+        """Lays out the storage (one arena: weights, step workspace, per-sequence state, key-value pages; see
+        cpmcu_b200.engine.storage) and returns the number of tokens the longest sequence may hold (the reference
+        returns its ``max_total_length`` here, cpmcu/llm.py:115-116).  The cache holds ``max_tokens`` tokens, or
+        what ``memory_limit`` leaves.  Raises cpmcu_b200.memory.PoolExhausted (a MemoryError) when something does
+        not fit."""
+        if self.use_arena:
+            from .engine.storage import make_storage
+            self.storage = make_storage(self.model, self.chunk_length, self.max_batch, self.max_tokens,
+                                        None if self.max_tokens is not None else self.memory_limit, self.max_seq_tokens)
+            self.cache = self.storage.cache
+        else:
+            needs = self.model.cache_needs()
+            tokens = self.max_tokens
+            if tokens is None:
+                raise ValueError("without the arena the cache's size has to be given (max_tokens)")
+            tokens = (int(tokens) // PAGE_TOKENS) * PAGE_TOKENS
+            per_seq = self.max_seq_tokens or min(tokens, max(self.model.spec.max_positions, 4096) * 8)
+            self.cache = Cache(needs, max_tokens=tokens, dtype=self.dtype, device=self.device,
+                               n_slots=min(max(2, tokens // PAGE_TOKENS), self.max_batch * 2 + 2), max_seq_tokens=per_seq,
+                               max_step_tokens=self.chunk_length)
         self.stepper = Stepper(self.model, self.cache, chunk_tokens=self.chunk_length)
         self.max_total_length = self.cache.max_pages_per_seq * PAGE_TOKENS
         return self.max_total_length

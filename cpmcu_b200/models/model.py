@@ -81,9 +81,14 @@ class Model:
         or None when no logits are wanted (the cache and the state are updated all the same)."""
         if not self.loaded:
             raise RuntimeError("the model has no weights yet")
-        stream = ResidualStream(self.ops, self.embedding.forward(ctx.token_ids))
-        for e in self.schedule:
+        ops = self.ops
+        if not ctx.extras.get("step_begun"):
+            ops.begin_step()           # the caller did not lay out the step's workspace itself
+        stream = ResidualStream(ops, self.embedding.forward(ctx.token_ids))
+        for k, e in enumerate(self.schedule):
+            ops.begin_layer(k)         # this run's intermediates replace those of the run before the last
             self.blocks[e.layer].forward(ctx, stream, ctx.cache.lane(e.lane), e.writes_cache)
+        ops.end_layers()
         if want_rows is None or want_rows.numel() == 0:
             return None
         y = stream.normed(self.final_norm, rows=want_rows)

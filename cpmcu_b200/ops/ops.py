@@ -34,7 +34,7 @@ def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
 _raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
 
 
-def _stream() -> int:
+def _current_stream() -> int:
     """Handle of the stream torch would launch on now (the raw query is an order of magnitude cheaper than
     building a Stream object for every kernel launch)."""
     if _raw_stream is not None:
@@ -59,6 +59,10 @@ class Ops:
         self.use_tcgen05 = os.environ.get("CPMCU_TCGEN05", "1") != "0"
         self.use_tcgen05_attention = os.environ.get("CPMCU_TCGEN05_ATTENTION", "1") != "0"
         self.tcgen05_pair = os.environ.get("CPMCU_TCGEN05_PAIR", "0") == "1"      # pairs of blocks on 256-row tiles
+        self.workspace = None       # cpmcu_b200.memory.Workspace: where a step's intermediates live (None: torch's allocator)
+        self.weights = None         # cpmcu_b200.memory.Region that holds the weights (None: torch's allocator)
+
+    _stream = staticmethod(_current_stream)
 
     # ---- checks ----
     def _act(self, t: torch.Tensor, what: str) -> torch.Tensor:
@@ -80,7 +84,38 @@ class Ops:
         return t
 
     def empty(self, *shape, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """A tensor for an intermediate of the step: from the workspace when one is attached (it is valid until the
+        workspace reuses its place, at the latest when the next step begins), else from torch's allocator."""
+        if self.workspace is not None:
+            return self.workspace.alloc(shape, dtype or self.dtype)
         return torch.empty(*shape, dtype=dtype or self.dtype, device=self.device)
+
+    def result(self, *shape, dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+        """A tensor the step hands to its caller (logits, sampled tokens): never from the workspace, so that it
+        stays valid after later steps."""
+        return torch.empty(*shape, dtype=dtype or self.dtype, device=self.device)
+
+    def keep(self, t: torch.Tensor) -> torch.Tensor:
+        """A weight for good: copied into the arena's weight region when one is attached (the copy replaces the
+        tensor the loader made), else the tensor itself."""
+        if self.weights is None or t.device.type == "meta":
+            return t
+        own = self.weights.tensor(t.shape, t.dtype, what="weights")
+        own.copy_(t)
+        return own
+
+    # ---- the workspace's lifetimes (no-ops without a workspace) ----
+    def begin_step(self) -> None:
+        if self.workspace is not None:
+            self.workspace.begin_step()
+
+    def begin_layer(self, k: int) -> None:
+        if self.workspace is not None:
+            self.workspace.begin_layer(k)
+
+    def end_layers(self) -> None:
+        if self.workspace is not None:
+            self.workspace.end_layers()
 
     # ---- rows ----
     def embed(self, ids: torch.Tensor, table: torch.Tensor, scale: float) -> torch.Tensor:
@@ -90,7 +125,7 @@ class Ops:
         n, hidden = ids.numel(), table.shape[1]
         out = self.empty(n, hidden, dtype=torch.float32)
         check(self.lib.cpm_embed_rows(_ptr(ids), _ptr(table), _ptr(out), n, hidden, float(scale), self.code,
-                                      _stream()), "embed")
+                                      self._stream()), "embed")
         return out
 
     def add_rmsnorm(self, x: torch.Tensor, delta: Optional[torch.Tensor], alpha: float, weight: torch.Tensor,
@@ -102,7 +137,7 @@ class Ops:
             self._act(delta, "residual addend")
             if delta.shape != x.shape:
                 raise ValueError(f"residual addend {tuple(delta.shape)} does not match the stream {tuple(x.shape)}")
-        if weight.dtype not in (torch.float32, self.dtype) or weight.numel() != hidden or not weight.is_cuda:
+        if weight.dtype not in (torch.float32, self.dtype) or weight.numel() != hidden or weight.device.type != self.device.type:
             raise ValueError("norm weight: needs [hidden] in float32 or the compute dtype")
         n_rows = x.shape[0] if rows is None else rows.numel()
         if rows is not None:
@@ -110,7 +145,7 @@ class Ops:
         y = self.empty(n_rows, hidden)
         check(self.lib.cpm_add_rmsnorm(_ptr(x), _ptr(delta), float(alpha), _ptr(weight),
                                        1 if weight.dtype == torch.float32 else 0, _ptr(y), _ptr(rows), n_rows,
-                                       hidden, float(eps), 1 if rows is None else 0, self.code, _stream()),
+                                       hidden, float(eps), 1 if rows is None else 0, self.code, self._stream()),
               f"rmsnorm (hidden {hidden})")
         return y
 
@@ -119,7 +154,7 @@ class Ops:
         self._act(delta, "residual addend")
         if delta.shape != x.shape:
             raise ValueError("residual addend does not match the stream")
-        check(self.lib.cpm_residual_add(_ptr(x), _ptr(delta), float(alpha), x.numel(), self.code, _stream()),
+        check(self.lib.cpm_residual_add(_ptr(x), _ptr(delta), float(alpha), x.numel(), self.code, self._stream()),
               "residual add")
 
     def silu_mul(self, gu: torch.Tensor, interleave: int = 0) -> torch.Tensor:
@@ -128,7 +163,7 @@ class Ops:
         self._act(gu, "gate_up")
         n, two_i = gu.shape
         h = self.empty(n, two_i // 2)
-        check(self.lib.cpm_silu_mul(_ptr(gu), _ptr(h), n, two_i // 2, interleave, self.code, _stream()), "silu_mul")
+        check(self.lib.cpm_silu_mul(_ptr(gu), _ptr(h), n, two_i // 2, interleave, self.code, self._stream()), "silu_mul")
         return h
 
     # ---- matrix products ----
@@ -139,31 +174,38 @@ class Ops:
         return self.code == BF16 and M <= self.SKINNY_MAX_ROWS and K % 32 == 0
 
     def linear(self, a: torch.Tensor, w: torch.Tensor, alpha: float = 1.0,
-               out_f32: bool = False) -> torch.Tensor:
-        """alpha * a[M,K] @ w[N,K]^T -> [M,N] in the compute dtype, or fp32 when out_f32."""
+               out_f32: bool = False, result: bool = False) -> torch.Tensor:
+        """alpha * a[M,K] @ w[N,K]^T -> [M,N] in the compute dtype, or fp32 when out_f32.  ``result``: the
+        product is handed to the step's caller (see ``result``)."""
         self._act(a, "linear input")
         self._act(w, "linear weight")
         M, K = a.shape
         N = w.shape[0]
         if w.shape[1] != K:
             raise ValueError(f"linear: input [*, {K}] against weight {tuple(w.shape)}")
+        make = self.result if result else self.empty
         if self.code == F32:
-            c = self.empty(M, N, dtype=torch.float32)
-            check(self.lib.cpm_gemm_f32(_ptr(a), _ptr(w), _ptr(c), M, N, K, K, K, N, float(alpha), _stream()),
+            c = make(M, N, dtype=torch.float32)
+            check(self.lib.cpm_gemm_f32(_ptr(a), _ptr(w), _ptr(c), M, N, K, K, K, N, float(alpha), self._stream()),
                   "fp32 matrix product")
             return c
         if self._skinny_ok(M, K):
-            c = self.empty(M, N, dtype=torch.float32 if out_f32 else self.dtype)
+            c = make(M, N, dtype=torch.float32 if out_f32 else self.dtype)
             check(self.lib.cpm_gemm_skinny_bf16(_ptr(w), _ptr(a), _ptr(c), M, N, K, float(alpha), 1 if out_f32 else 0,
-                                                _stream()), "skinny matrix product")
+                                                self._stream()), "skinny matrix product")
             return c
-        if out_f32:
-            c = torch.mm(a, w.t(), out_dtype=torch.float32)
-        else:
-            c = torch.mm(a, w.t())
+        c = make(M, N, dtype=torch.float32 if out_f32 else self.dtype)
+        self._library_mm(a, w, c)
         if alpha != 1.0:
             c.mul_(alpha)
         return c
+
+    def _library_mm(self, a: torch.Tensor, w: torch.Tensor, c: torch.Tensor) -> None:
+        """c = a @ w^T by the library (cuBLAS through torch), into a tensor of this library's own."""
+        if c.dtype == a.dtype:
+            torch.mm(a, w.t(), out=c)
+        else:
+            torch.mm(a, w.t(), out_dtype=c.dtype, out=c)
 
     def linear_tcgen05(self, a: torch.Tensor, w: torch.Tensor, gated: bool = False, pair: bool = False) -> torch.Tensor:
         """a[M,K] @ w[N,K]^T on the tcgen05 tensor cores (TMA operands, TMEM accumulator); with ``gated`` the
@@ -175,7 +217,7 @@ class Ops:
         N = w.shape[0]
         out = self.empty(M, N // 2 if gated else N)
         entry = self.lib.cpm_gemm_bf16_tcgen05_pair if pair else self.lib.cpm_gemm_bf16_tcgen05
-        check(entry(_ptr(a), _ptr(w), _ptr(out), M, N, K, 2 if gated else 0, self.sm_count, _stream()),
+        check(entry(_ptr(a), _ptr(w), _ptr(out), M, N, K, 2 if gated else 0, self.sm_count, self._stream()),
               f"tcgen05 matrix product [{M}x{K}] x [{N}x{K}]^T")
         return out
 
@@ -191,7 +233,7 @@ class Ops:
             self._act(w_gate_up, "gate_up weight")
             h = self.empty(M, w_gate_up.shape[0] // 2)
             check(self.lib.cpm_gemm_skinny_bf16(_ptr(w_gate_up), _ptr(a), _ptr(h), M, w_gate_up.shape[0], K, 1.0, 2,
-                                                _stream()), "gated skinny matrix product")
+                                                self._stream()), "gated skinny matrix product")
             return h
         if (self.code == BF16 and interleave == 8 and self.use_tcgen05 and M >= self.TCGEN05_MIN_ROWS and K % 64 == 0
                 and w_gate_up.shape[0] % 32 == 0 and a.data_ptr() % 16 == 0):
@@ -221,7 +263,7 @@ class Ops:
         check(self.lib.cpm_rope_store(_ptr(qkv), _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(positions),
                                       _ptr(token_seq), _ptr(slots), _ptr(page_table), page_table.shape[1],
                                       _ptr(inv_freq), float(magnitude), n, n_heads, n_kv, d, rot_dim, self.code,
-                                      _stream()), "rope_store")
+                                      self._stream()), "rope_store")
         return q
 
     def attention_generic(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
@@ -239,7 +281,7 @@ class Ops:
         check(self.lib.cpm_attention_generic(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(positions),
                                              _ptr(token_seq), _ptr(slots), _ptr(page_table), page_table.shape[1],
                                              _ptr(block_list), list_cap, block_size, window, n, n_heads, n_kv, d,
-                                             float(scale), self.code, _stream()),
+                                             float(scale), self.code, self._stream()),
               f"attention (head_dim {d}, {n_heads} heads, {n_kv} kv heads)")
         return out
 
@@ -251,10 +293,10 @@ class Ops:
         self._f32(logits, "logits")
         rows, vocab = logits.shape
         if out is None:
-            out = self.empty(rows, dtype=torch.int32)
+            out = self.result(rows, dtype=torch.int32)
         check(self.lib.cpm_sample_rows(_ptr(logits), logits.stride(0), rows, vocab, _ptr(out), _ptr(temperature),
                                        _ptr(top_p), ctypes.c_uint64(seed & 0xFFFFFFFFFFFFFFFF), _ptr(seq_key),
-                                       _ptr(step_key), _stream()), "sample")
+                                       _ptr(step_key), self._stream()), "sample")
         return out
 
     def attention(self, ctx, q: torch.Tensor, lane, n_kv: int, scale: float, window: int = 0,
@@ -286,7 +328,7 @@ class Ops:
         """Stores the mean-pooled keys whose windows this step's tokens complete."""
         check(self.lib.cpm_pool_keys(_ptr(lane.k), _ptr(lane.pooled), _ptr(ctx.positions), _ptr(ctx.token_seq),
                                      _ptr(ctx.slot_dev), _ptr(lane.page_table), lane.page_table.shape[1],
-                                     ctx.n_tokens, n_kv, d, kernel, stride, self.code, _stream()), "pool_keys")
+                                     ctx.n_tokens, n_kv, d, kernel, stride, self.code, self._stream()), "pool_keys")
 
     def select_blocks(self, ctx, q: torch.Tensor, lane, n_kv: int, scale: float, sparse) -> Tuple[torch.Tensor, int]:
         """(block list int32 [tokens, kv_heads, cap], block size) for the step's queries."""
@@ -303,13 +345,13 @@ class Ops:
                                          _ptr(ctx.slot_dev), _ptr(lane.page_table), lane.page_table.shape[1],
                                          _ptr(lists), cap, n, n_heads, n_kv, d, float(scale), sparse["kernel_size"],
                                          stride, bs, sparse.get("init_blocks", 1), sparse["topk"], local_blocks,
-                                         sparse.get("dense_len", 0), max_entries, self.code, _stream()),
+                                         sparse.get("dense_len", 0), max_entries, self.code, self._stream()),
               f"select_blocks ({max_entries} pooled keys)")
         return lists, bs
 
     def advance_decode(self, ids, positions, kv_len, step_key, sampled, live) -> None:
         check(self.lib.cpm_advance_decode(_ptr(ids), _ptr(positions), _ptr(kv_len), _ptr(step_key), _ptr(sampled),
-                                          _ptr(live), ids.numel(), _stream()), "advance_decode")
+                                          _ptr(live), ids.numel(), self._stream()), "advance_decode")
 
     # ---- bf16 tensor-core attention ----
     def decode_splits(self, n_seqs: int, n_heads: int, n_kv: int) -> int:
@@ -332,7 +374,7 @@ class Ops:
         out = self.empty(n, n_heads * d)
         check(self.lib.cpm_decode_attention_bf16(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(kv_len),
                                                  _ptr(slots), _ptr(page_table), page_table.shape[1], _ptr(scratch),
-                                                 n, n_heads, n_kv, d, n_splits, float(scale), _stream()),
+                                                 n, n_heads, n_kv, d, n_splits, float(scale), self._stream()),
               f"decode attention (head_dim {d})")
         if n_splits > 1:
             LAUNCHES_EXTRA[0] += 1       # the launcher starts two kernels: the shares, then their combination
@@ -350,7 +392,7 @@ class Ops:
         check(self.lib.cpm_prefill_attention_bf16(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(tile_seq),
                                                   _ptr(tile_row), n_tiles, _ptr(cu_q), _ptr(kv_len), _ptr(slots),
                                                   _ptr(page_table), page_table.shape[1], n_heads, n_kv, d,
-                                                  float(scale), _stream()), f"prefill attention (head_dim {d})")
+                                                  float(scale), self._stream()), f"prefill attention (head_dim {d})")
         return out
 
 
@@ -368,7 +410,7 @@ class Ops:
         check(self.lib.cpm_prefill_attention_tcgen05(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(tile_seq),
                                                      _ptr(tile_row), n_tiles, _ptr(cu_q), _ptr(kv_len), _ptr(slots),
                                                      _ptr(page_table), page_table.shape[1], n, k_cache.shape[0],
-                                                     n_heads, n_kv, d, float(scale), _ptr(scratch), n_splits, _stream()),
+                                                     n_heads, n_kv, d, float(scale), _ptr(scratch), n_splits, self._stream()),
               f"tcgen05 prefill attention (head_dim {d})")
         return out
 
@@ -412,7 +454,7 @@ class Ops:
         check(self.lib.cpm_listed_attention_bf16(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(positions),
                                                  _ptr(token_seq), _ptr(slots), _ptr(page_table), page_table.shape[1],
                                                  _ptr(block_list), block_list.shape[-1], n, n_heads, n_kv, d,
-                                                 float(scale), _ptr(scratch), n_splits, _stream()),
+                                                 float(scale), _ptr(scratch), n_splits, self._stream()),
               f"block-list attention (head_dim {d})")
         return out
 

@@ -61,9 +61,9 @@ class GroupedQueryAttention(Mixer):
         own = self.position.weight_specs()
         if own:
             self.position.load_weights({n: tensors[self.position_name + n] for n in own})
-        self.w_qkv = torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]],
-                               dim=0).contiguous()
-        self.w_o = tensors["o_proj.weight"].contiguous()
+        self.w_qkv = self.ops.keep(torch.cat([tensors["q_proj.weight"], tensors["k_proj.weight"], tensors["v_proj.weight"]],
+                                             dim=0).contiguous())
+        self.w_o = self.ops.keep(tensors["o_proj.weight"].contiguous())
 
     def weight_bytes(self) -> int:
         return (self.w_qkv.numel() + self.w_o.numel()) * self.w_qkv.element_size()

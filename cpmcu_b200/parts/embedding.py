@@ -28,7 +28,7 @@ class ScaledEmbedding(Part):
         return {"weight": WeightSpec((self.vocab_size, self.hidden_size))}
 
     def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.weight = tensors["weight"].contiguous()
+        self.weight = self.ops.keep(tensors["weight"].contiguous()) if self.ops is not None else tensors["weight"]
 
     def forward(self, token_ids: torch.Tensor) -> torch.Tensor:
         return self.ops.embed(token_ids, self.weight, self.scale)
@@ -46,7 +46,7 @@ class ScaledHead(Part):
 
     def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
         if not self.tied:
-            self.weight = tensors["weight"].contiguous()
+            self.weight = self.ops.keep(tensors["weight"].contiguous())
 
     def tie(self, embedding_weight: torch.Tensor) -> None:
         self.weight = embedding_weight
@@ -56,4 +56,4 @@ class ScaledHead(Part):
 
     def forward(self, y: torch.Tensor) -> torch.Tensor:
         """normed rows [n, hidden] -> fp32 logits [n, vocab]."""
-        return self.ops.linear(y, self.weight, alpha=self.scale, out_f32=True)
+        return self.ops.linear(y, self.weight, alpha=self.scale, out_f32=True, result=True)

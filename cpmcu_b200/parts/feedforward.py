@@ -44,7 +44,8 @@ class GatedFeedForward(FeedForward):
         else:
             self.interleave = 0
             self.w_gate_up = torch.cat([gate, up], dim=0).contiguous()
-        self.w_down = tensors["down_proj.weight"].contiguous()
+        self.w_gate_up = self.ops.keep(self.w_gate_up)
+        self.w_down = self.ops.keep(tensors["down_proj.weight"].contiguous())
 
     def weight_bytes(self) -> int:
         return (self.w_gate_up.numel() + self.w_down.numel()) * self.w_gate_up.element_size()

@@ -21,7 +21,7 @@ class RMSNorm(Norm):
         return {"weight": WeightSpec((self.hidden_size,), "vector")}
 
     def load_weights(self, tensors: Dict[str, torch.Tensor]) -> None:
-        self.weight = tensors["weight"]
+        self.weight = self.ops.keep(tensors["weight"].contiguous())
 
     def weight_bytes(self) -> int:
         return self.weight.numel() * self.weight.element_size()

@@ -228,3 +228,49 @@ def test_many_random_batches_leave_the_cache_clean(model_folders, name, make, dt
                 assert tok == plain.sample_token(plain.forward(cfg, w, ids)[-1], 0.0, 0.0), (b, i, len(ids))
                 ids.append(tok)
     llm.ops.raise_on_kernel_error()
+
+
+def test_storage_is_one_arena_with_regions(model_folders):
+    """The Python entry point lays weights, step workspace, per-sequence state and key-value pages out in one
+    allocation; a memory limit that leaves no room, and a step larger than the workspace was sized for, are refused
+    with an error that names the region, before anything runs."""
+    from cpmcu_b200 import LLM
+    from cpmcu_b200.engine import SequenceStep
+    from cpmcu_b200.memory import PoolExhausted
+
+    folder = model_folders("tiny_b", configs.tiny_b(), 1, "bfloat16")
+    llm = LLM(folder, dtype="bfloat16", cuda_graph=True, max_tokens=64 * 16, chunk_length=64, max_batch=4)
+    llm.init_storage()
+    llm.load_from_hf()
+    arena = llm.storage.arena
+    assert list(arena.regions) == ["weights", "workspace", "frame0", "frame1", "state", "cache"]
+    lo, hi = arena.buffer.data_ptr(), arena.buffer.data_ptr() + arena.total
+    att = llm.model.blocks[0].mixer
+    lane = llm.cache.lane(0)
+    for t in (att.w_qkv, att.w_o, llm.model.embedding.weight, lane.k, lane.v, lane.pooled, lane.page_table):
+        assert lo <= t.data_ptr() < hi
+    prompts = [helpers.random_ids(1000, n, n) for n in (70, 9, 130)]
+    res = llm.generate_batch(prompts, generation_length=8)
+    assert all(len(r.tokens) == 8 for r in res)
+    ws = llm.storage.workspace
+    assert 0 < ws.peaks()[1] <= ws.frames[0].size and ws.peaks()[0] <= ws.persistent.size
+    # the same tokens as with torch's allocator
+    plain_llm = LLM(folder, dtype="bfloat16", cuda_graph=True, max_tokens=64 * 16, chunk_length=64, max_batch=4, use_arena=False)
+    assert [r.tokens for r in plain_llm.generate_batch(prompts, generation_length=8)] == [r.tokens for r in res]
+    # a step of more sequences than the workspace was sized for
+    slots = llm.stepper.open(5)
+    with pytest.raises(PoolExhausted, match="region 'workspace'.*sequences"):
+        llm.step([SequenceStep(s, [1, 2, 3], [2]) for s in slots])
+    for s in slots:
+        llm.stepper.close(s)
+    # a chunk larger than the workspace was sized for
+    llm.stepper.chunk_tokens = 512
+    slot = llm.stepper.open(1)[0]
+    with pytest.raises(PoolExhausted, match="region 'workspace'.*tokens"):
+        llm.step([SequenceStep(slot, helpers.random_ids(1000, 300, 1), [299])])
+    llm.stepper.close(slot)
+    # a memory limit that leaves nothing
+    tight = LLM(folder, dtype="bfloat16", memory_limit=1e-6)
+    with pytest.raises(PoolExhausted, match="memory_limit"):
+        tight.init_storage()
+    assert isinstance(PoolExhausted("cache", 1, 0), MemoryError)
