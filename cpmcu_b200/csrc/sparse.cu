@@ -465,6 +465,165 @@ select_blocks_mma_kernel(const bf16* __restrict__ q, const float* __restrict__ p
     finish_selection(sel, keys, chosen, list, list_cap, init_blocks, topk);
 }
 
+// ---------------------------------------------------------------------------
+// Few queries (decode): the pooled keys of one query are shared out over many blocks.
+// With one block per (token, kv head) a decode step of two sequences keeps four SMs busy
+// for the whole walk over some thousand pooled keys (measured 69 us a layer at 30,000
+// cached tokens).  Here a first kernel, gridDim.x slices per (token, kv head), writes the
+// raw scaled scores of its slice (log2 domain, [pooled key][16 heads]) and the slice's
+// maximum and sum of exponentials per head; a second kernel, one block per (token, kv
+// head), merges the statistics, turns scores into probabilities summed over the heads,
+// and chooses the blocks as the one-kernel path does.
+// ---------------------------------------------------------------------------
+constexpr int kSliceWarps = 4;
+
+template <int D>
+__global__ void __launch_bounds__(kSliceWarps * 32)
+select_scores_kernel(const bf16* __restrict__ q, const float* __restrict__ pooled, const int* __restrict__ positions,
+                     const int* __restrict__ token_seq, const int* __restrict__ slots,
+                     const int* __restrict__ page_table, int max_pages, int n_heads, int n_kv, float scale_log2,
+                     int kernel, int stride, int dense_len, int max_entries, float* __restrict__ raw,
+                     float* __restrict__ stats) {
+    __shared__ float stat_m[kSliceWarps][16], stat_l[kSliceWarps][16];
+    const int slice = blockIdx.x, n_slices = gridDim.x, kvh = blockIdx.y, t = blockIdx.z, tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, j = lane & 3;
+    const int p = positions[t];
+    if (p + 1 <= dense_len) return;
+    const int group = n_heads / n_kv;
+    const int* pages = page_table + (int64_t)slots[token_seq[t]] * max_pages;
+    const int per_page = kPageTokens / stride;
+    const int n_vis = min(p + 1 >= kernel ? (p + 1 - kernel) / stride + 1 : 0, max_entries);
+    const int n_tiles = (n_vis + 7) / 8;
+    const int per_slice = (n_tiles + n_slices - 1) / n_slices;
+    const int tile0 = slice * per_slice, tile1 = min(n_tiles, tile0 + per_slice);
+    const int64_t unit = (int64_t)t * n_kv + kvh;
+    float* my_raw = raw + unit * max_entries * 16;
+
+    uint4 qf[2][D / 32];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const bool ok = g + 8 * r < group;
+        const bf16* qrow = q + ((int64_t)t * n_heads + kvh * group + (ok ? g + 8 * r : 0)) * D + 8 * j;
+#pragma unroll
+        for (int w = 0; w < D / 32; ++w) {
+            const uint4 v = __ldg(reinterpret_cast<const uint4*>(qrow + 32 * w));
+            qf[r][w] = ok ? v : make_uint4(0, 0, 0, 0);
+        }
+    }
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    auto row_of = [&](int tile) {
+        return pooled_row(pooled, pages, min(tile * 8 + g, n_vis - 1), stride, per_page, n_kv, kvh, D);
+    };
+    RawKey<D> cur, nxt;
+    if (tile0 + warp < tile1) cur.load(row_of(tile0 + warp), j);
+    for (int tile = tile0 + warp; tile < tile1; tile += kSliceWarps) {
+        if (tile + kSliceWarps < tile1) nxt.load(row_of(tile + kSliceWarps), j);
+        float sc[4];
+        score_tile<D>(sc, qf, cur, scale_log2);
+        cur = nxt;
+        const int c0 = tile * 8 + 2 * j;
+        if (c0 < n_vis) {
+            my_raw[(int64_t)c0 * 16 + g] = sc[0];
+            my_raw[(int64_t)c0 * 16 + g + 8] = sc[2];
+        } else {
+            sc[0] = sc[2] = -INFINITY;
+        }
+        if (c0 + 1 < n_vis) {
+            my_raw[(int64_t)(c0 + 1) * 16 + g] = sc[1];
+            my_raw[(int64_t)(c0 + 1) * 16 + g + 8] = sc[3];
+        } else {
+            sc[1] = sc[3] = -INFINITY;
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            float mx = fmaxf(sc[2 * r], sc[2 * r + 1]);
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float mn = fmaxf(m[r], mx);                       // finite: column 0 of a tile is always visible
+            l[r] = l[r] * exp2f(m[r] - mn) + exp2f(sc[2 * r] - mn) + exp2f(sc[2 * r + 1] - mn);
+            m[r] = mn;
+        }
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 1);
+        l[r] += __shfl_xor_sync(0xffffffffu, l[r], 2);
+        if (j == 0) {
+            stat_m[warp][g + 8 * r] = m[r];
+            stat_l[warp][g + 8 * r] = l[r];
+        }
+    }
+    __syncthreads();
+    if (tid < 16) {
+        float mx = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < kSliceWarps; ++w) mx = fmaxf(mx, stat_m[w][tid]);
+        float sum = 0.f;
+#pragma unroll
+        for (int w = 0; w < kSliceWarps; ++w)
+            if (stat_m[w][tid] != -INFINITY) sum += stat_l[w][tid] * exp2f(stat_m[w][tid] - mx);
+        float* out = stats + ((unit * n_slices + slice) * 16 + tid) * 2;
+        out[0] = mx;
+        out[1] = sum;
+    }
+}
+
+constexpr int kFinishThreads = 512;
+
+__global__ void __launch_bounds__(kFinishThreads)
+select_finish_kernel(const float* __restrict__ raw, const float* __restrict__ stats, int n_slices,
+                     const int* __restrict__ positions, int* __restrict__ lists, int list_cap, int n_heads, int n_kv,
+                     int kernel, int stride, int block_size, int init_blocks, int topk, int local_blocks, int dense_len,
+                     int max_entries, int sort_cap) {
+    extern __shared__ __align__(16) unsigned char sm_raw[];
+    unsigned long long* keys = (unsigned long long*)sm_raw;                   // [sort_cap]
+    unsigned* chosen = (unsigned*)(keys + sort_cap);                         // [sort_cap / 32 + 1]
+    __shared__ float head_m[16], head_inv[16];
+    const int t = blockIdx.x, kvh = blockIdx.y, tid = threadIdx.x;
+    int* list = lists + ((int64_t)t * n_kv + kvh) * list_cap;
+    const int p = positions[t];
+    if (p + 1 <= dense_len) {
+        if (tid == 0) list[0] = -2;
+        return;
+    }
+    const int group = n_heads / n_kv;
+    const int64_t unit = (int64_t)t * n_kv + kvh;
+    const int n_vis = min(p + 1 >= kernel ? (p + 1 - kernel) / stride + 1 : 0, max_entries);
+    const Selection sel = selection_of(p, kernel, stride, block_size, init_blocks, local_blocks, sort_cap);
+    if (tid == 0 && p / block_size - local_blocks + 1 - init_blocks > sort_cap) g_select_overflow = 1;
+    clear_selection(sel, keys, chosen);
+    if (tid < 16) {
+        const float* st = stats + unit * n_slices * 32 + tid * 2;
+        float mx = -INFINITY;
+        for (int s = 0; s < n_slices; ++s) mx = fmaxf(mx, st[s * 32]);
+        float sum = 0.f;
+        for (int s = 0; s < n_slices; ++s)
+            if (st[s * 32] != -INFINITY) sum += st[s * 32 + 1] * exp2f(st[s * 32] - mx);
+        head_m[tid] = mx;
+        head_inv[tid] = (tid < group && sum > 0.f) ? 1.f / sum : 0.f;       // rows beyond the group count for nothing
+    }
+    __syncthreads();
+    const float* my_raw = raw + unit * max_entries * 16;
+    for (int i = tid; i < n_vis; i += kFinishThreads) {
+        const float4* row = reinterpret_cast<const float4*>(my_raw + (int64_t)i * 16);
+        float total = 0.f;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+            const float4 v = row[c];
+            total += exp2f(v.x - head_m[4 * c]) * head_inv[4 * c] + exp2f(v.y - head_m[4 * c + 1]) * head_inv[4 * c + 1]
+                   + exp2f(v.z - head_m[4 * c + 2]) * head_inv[4 * c + 2] + exp2f(v.w - head_m[4 * c + 3]) * head_inv[4 * c + 3];
+        }
+        note_score(sel, keys, init_blocks, i, total);
+    }
+    __syncthreads();
+    finish_selection(sel, keys, chosen, list, list_cap, init_blocks, topk);
+}
+
+// Floats of scratch the two-kernel path needs (raw scores and slice statistics).
+CPM_API int64_t cpm_select_blocks_scratch_floats(int n_tokens, int n_kv, int max_entries, int n_slices) {
+    return (int64_t)n_tokens * n_kv * ((int64_t)max_entries * 16 + (int64_t)n_slices * 32);
+}
+
 static int next_pow2(int n) {
     int v = 1;
     while (v < n) v <<= 1;
@@ -493,17 +652,53 @@ static int launch_select_mma(const void* q, const float* pooled, const int* posi
 
 // max_entries: an upper bound on the pooled keys any query of the step sees (longest sequence / stride + 1); it
 // sizes the sort of the candidate blocks, 8 bytes of shared memory per block.
+template <int D>
+static int launch_select_sliced(const void* q, const float* pooled, const int* positions, const int* token_seq,
+                                const int* slots, const int* page_table, int max_pages, int* lists, int list_cap,
+                                int n_tokens, int n_heads, int n_kv, float scale, int kernel, int stride, int block_size,
+                                int init_blocks, int topk, int local_blocks, int dense_len, int max_entries, int sort_cap,
+                                float* scratch, int n_slices, cudaStream_t stream) {
+    const size_t smem = (size_t)sort_cap * 8 + (size_t)((sort_cap / 32 + 4) & ~3) * 4;
+    if (smem > 200 * 1024 || n_tokens > 65535) return CPM_BAD_ARGUMENT;
+    float* raw = scratch;
+    float* stats = scratch + (int64_t)n_tokens * n_kv * max_entries * 16;
+    select_scores_kernel<D><<<dim3(n_slices, n_kv, n_tokens), kSliceWarps * 32, 0, stream>>>(
+        (const bf16*)q, pooled, positions, token_seq, slots, page_table, max_pages, n_heads, n_kv,
+        scale * 1.4426950408889634f, kernel, stride, dense_len, max_entries, raw, stats);
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(select_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    select_finish_kernel<<<dim3(n_tokens, n_kv), kFinishThreads, smem, stream>>>(
+        raw, stats, n_slices, positions, lists, list_cap, n_heads, n_kv, kernel, stride, block_size, init_blocks, topk,
+        local_blocks, dense_len, max_entries, sort_cap);
+    return launch_status();
+}
+
+// scratch/n_slices: with scratch of cpm_select_blocks_scratch_floats(n_tokens, n_kv, max_entries, n_slices) floats and
+// n_slices >= 1, bf16 queries of groups up to 16 heads take the two-kernel path that shares a query's pooled keys out
+// over n_slices blocks (for steps of few tokens); it launches two kernels.
 CPM_API int cpm_select_blocks(const void* q, const float* pooled, const int* positions, const int* token_seq,
                               const int* slots, const int* page_table, int max_pages, int* lists, int list_cap,
                               int n_tokens, int n_heads, int n_kv, int d, float scale, int kernel, int stride,
                               int block_size, int init_blocks, int topk, int local_blocks, int dense_len,
-                              int max_entries, int dtype, cudaStream_t stream) {
+                              int max_entries, int dtype, float* scratch, int n_slices, cudaStream_t stream) {
     if (n_tokens <= 0) return CPM_OK;
     if (stride <= 0 || kernel % stride || block_size % stride || kPageTokens % stride || n_kv > 65535 ||
         n_heads % n_kv || n_heads / n_kv > kMaxGroup || d % 4 || list_cap < topk + local_blocks + 1 || max_entries < 1)
         return CPM_BAD_ARGUMENT;
     const int sort_cap = next_pow2(max_entries / (block_size / stride) + 2);
     const int group = n_heads / n_kv;
+    if (dtype == CPM_BF16 && group <= 16 && scratch != nullptr && n_slices >= 1 && n_slices <= 65535) {
+#define CPM_SELECT_SLICED(DD) return launch_select_sliced<DD>(q, pooled, positions, token_seq, slots, page_table, max_pages, \
+        lists, list_cap, n_tokens, n_heads, n_kv, scale, kernel, stride, block_size, init_blocks, topk, local_blocks, \
+        dense_len, max_entries, sort_cap, scratch, n_slices, stream)
+        if (d == 32) CPM_SELECT_SLICED(32);
+        if (d == 64) CPM_SELECT_SLICED(64);
+        if (d == 96) CPM_SELECT_SLICED(96);
+        if (d == 128) CPM_SELECT_SLICED(128);
+#undef CPM_SELECT_SLICED
+    }
     if (dtype == CPM_BF16 && group <= 16) {
 #define CPM_SELECT_MMA(DD) return launch_select_mma<DD>(q, pooled, positions, token_seq, slots, page_table, max_pages, lists, \
         list_cap, n_tokens, n_heads, n_kv, scale, kernel, stride, block_size, init_blocks, topk, local_blocks, dense_len, \

@@ -26,6 +26,10 @@ class _NoLibrary:
     def cpm_decode_attention_scratch_floats(n_seqs, n_heads, n_kv, d, n_splits):
         return n_seqs * n_kv * ((n_heads // n_kv + 15) // 16) * n_splits * (16 * d + 32)
 
+    @staticmethod
+    def cpm_select_blocks_scratch_floats(n_tokens, n_kv, max_entries, n_slices):
+        return n_tokens * n_kv * (max_entries * 16 + n_slices * 32)
+
     def __getattr__(self, name):
         return lambda *args: 0
 

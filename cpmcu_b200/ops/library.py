@@ -35,7 +35,7 @@ _SIGNATURES = {
     "cpm_gemm_f32": [_P, _P, _P, c_int, c_int, c_int, c_int64, c_int64, c_int64, c_float, _P],
     "cpm_pool_keys": [_P, _P, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
     "cpm_select_blocks": [_P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, c_float, c_int,
-                          c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P],
+                          c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int, _P],
     "cpm_advance_decode": [_P, _P, _P, _P, _P, _P, c_int, _P],
     "cpm_decode_attention_bf16": [_P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, c_float, _P],
     "cpm_prefill_attention_bf16": [_P, _P, _P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float,
@@ -86,6 +86,8 @@ def load() -> ctypes.CDLL:
         lib.cpm_gemm_tcgen05_error.restype = c_int
         lib.cpm_attention_tcgen05_error.argtypes = []
         lib.cpm_attention_tcgen05_error.restype = c_int
+        lib.cpm_select_blocks_scratch_floats.argtypes = [c_int, c_int, c_int, c_int]
+        lib.cpm_select_blocks_scratch_floats.restype = c_int64
         lib.cpm_select_blocks_error.argtypes = []
         lib.cpm_select_blocks_error.restype = c_int
         lib.cpm_decode_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int, c_int]

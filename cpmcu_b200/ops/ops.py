@@ -169,6 +169,7 @@ class Ops:
     # ---- matrix products ----
     SKINNY_MAX_ROWS = int(os.environ.get("CPMCU_SKINNY_MAX_ROWS", "8"))   # most rows the weight-streaming product takes
     TCGEN05_MIN_ROWS = 256       # below this the 128-row tiles of the tcgen05 product are mostly empty
+    SELECT_SCRATCH_BYTES = 64 << 20     # most scratch the sliced block selection may take (raw scores of all pooled keys)
 
     def _skinny_ok(self, M: int, K: int) -> bool:
         return self.code == BF16 and M <= self.SKINNY_MAX_ROWS and K % 32 == 0
@@ -341,12 +342,22 @@ class Ops:
         longest = lane.page_table.shape[1] * PAGE_TOKENS if ctx.captured else ctx.max_kv_len
         max_entries = max(1, longest // stride + 1)
         lists = self.empty(n, n_kv, cap, dtype=torch.int32)
+        # few queries (a decode step): share every query's pooled keys out over many blocks, in two kernels
+        scratch, n_slices = None, 0
+        units = n * n_kv
+        if (self.code == BF16 and units * 2 <= self.sm_count and n_heads // n_kv <= 16 and d in FAST_HEAD_DIMS
+                and units * max_entries * 64 <= self.SELECT_SCRATCH_BYTES):
+            n_slices = max(1, min(2 * self.sm_count // units, (max_entries + 63) // 64))
+            scratch = self.empty(self.lib.cpm_select_blocks_scratch_floats(n, n_kv, max_entries, n_slices), dtype=torch.float32)
         check(self.lib.cpm_select_blocks(_ptr(q), _ptr(lane.pooled), _ptr(ctx.positions), _ptr(ctx.token_seq),
                                          _ptr(ctx.slot_dev), _ptr(lane.page_table), lane.page_table.shape[1],
                                          _ptr(lists), cap, n, n_heads, n_kv, d, float(scale), sparse["kernel_size"],
                                          stride, bs, sparse.get("init_blocks", 1), sparse["topk"], local_blocks,
-                                         sparse.get("dense_len", 0), max_entries, self.code, self._stream()),
+                                         sparse.get("dense_len", 0), max_entries, self.code, _ptr(scratch), n_slices,
+                                         self._stream()),
               f"select_blocks ({max_entries} pooled keys)")
+        if scratch is not None:
+            LAUNCHES_EXTRA[0] += 1
         return lists, bs
 
     def advance_decode(self, ids, positions, kv_len, step_key, sampled, live) -> None:

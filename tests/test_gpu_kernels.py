@@ -608,12 +608,22 @@ def test_select_blocks_at_long_context_sizes(dtype):
     qkv = torch.zeros(m, n_heads + 2 * n_kv, d, dtype=DT[dtype])
     qkv[:, :n_heads] = q_rows
     scale = 1 / math.sqrt(d)
-    for captured in (False, True):
+    all_sample, all_rows, all_qkv = sample, q_rows, qkv
+    few = list(range(0, 6)) + list(range(len(sample) - 6, len(sample)))           # a dozen queries: the path for decode steps
+    for captured, pick in ((False, None), (True, None), (False, few), (True, few)):
+        sample = all_sample if pick is None else [all_sample[i] for i in pick]
+        q_rows = all_rows if pick is None else all_rows[pick]
+        qkv = all_qkv if pick is None else all_qkv[pick].contiguous()
+        m = len(sample)
         ctx = StepContext(m, 1, False, captured, [m], [n], [slot], m, n, i32([0] * m), i32(sample), i32([0] * m),
                           i32([0, m]), i32([n]), sl, cache)
         q = ops.rope_store(qkv.view(m, -1).cuda(), n_heads, n_kv, d, ctx.positions, ctx.token_seq, sl, lane.page_table,
                            None, None, None, 1.0, 0)
+        from cpmcu_b200.ops import library
+        before = library.LAUNCHES[0]
         lists, bs = ops.select_blocks(ctx, q, lane, n_kv, scale, sparse)
+        # few queries in bf16 share each query's pooled keys out over many blocks (two kernels instead of one)
+        assert library.LAUNCHES[0] - before == (2 if pick is not None and dtype == "bfloat16" else 1)
         ops.raise_on_kernel_error()
         lists = lists.cpu()
         checked = 0
