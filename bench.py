@@ -172,7 +172,7 @@ def build_engine(n_layers: int, max_tokens: int, max_batch: int, model: dict = N
                            n_slots=max_batch + 2)
     model.load_weights(random_tensors(model.weight_specs(), seed, torch.bfloat16, std=0.02, norm_mean=1.0, device="cuda:0"))
     torch.cuda.empty_cache()                                         # the loader's tensors: their copies live in the arena
-    return cfg, model, storage.cache, Stepper(model, storage.cache, chunk_tokens=chunk)
+    return cfg, model, storage.cache, Stepper(model, storage.cache, chunk_tokens=chunk, graph_prompts=True)
 
 
 def random_prompt(vocab: int, n: int, seed: int) -> list:
@@ -308,7 +308,8 @@ def workload_half_b(steps: int, warmup: int) -> int:
     batch, context, chunk = 64, 8192, 512
     pk = peaks()
     cfg, model, cache, stepper = build_engine(MODEL_HALF_B["num_hidden_layers"], batch * (context + 64) + 128, batch,
-                                              model=MODEL_HALF_B, seed=3, max_seq_tokens=context + 64, chunk_tokens=chunk)
+                                              model=MODEL_HALF_B, seed=3, max_seq_tokens=context + 64, chunk_tokens=2048)
+    stepper.chunk_tokens = chunk                                                # the workload's prompts: chunks of 512
     g = torch.Generator().manual_seed(3)
     lens = torch.randint(64, 2049, (batch,), generator=g).tolist()
     prompts = [random_prompt(cfg.vocab_size, n, 300 + i) for i, n in enumerate(lens)]

@@ -284,13 +284,79 @@ __device__ __forceinline__ void attend_page_smem(TileState<D>& st, const uint4 (
     }
 }
 
+// The decode step's rotation of q and k and the store of the new key and value, done by the attention
+// kernel itself instead of a kernel before it (head sizes 64 and 128, where the two members of a
+// rotary pair lie in one thread's fragments).  qkv: the step's product [seqs, (heads + 2 kv) * D],
+// null = q is given rotated and the cache holds the step's token already.  inv_freq null = no
+// rotation.  write_cache 0: the cache holds the step's token already (a run that shares another
+// run's lane), only q is taken from qkv.
+struct DecodeRope {
+    const bf16* qkv;
+    const float* inv_freq;
+    float magnitude;
+    int write_cache;
+    bf16* k_out;
+    bf16* v_out;
+};
+
+// x' = x cos - y sin, y' = x sin + y cos on the 8 bf16 pairs (x from ``lo``, y from ``hi``), cos and sin
+// of the 8 dimensions in cs[], sn[]; rounded to bf16 as the stand-alone rotary kernel does.
+__device__ __forceinline__ void rotate8(uint4& lo, uint4& hi, const float (&cs)[8], const float (&sn)[8]) {
+    uint32_t a[4] = {lo.x, lo.y, lo.z, lo.w}, b[4] = {hi.x, hi.y, hi.z, hi.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&a[i]));
+        const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&b[i]));
+        a[i] = pack_bf16(x.x * cs[2 * i] - y.x * sn[2 * i], x.y * cs[2 * i + 1] - y.y * sn[2 * i + 1]);
+        b[i] = pack_bf16(x.x * sn[2 * i] + y.x * cs[2 * i], x.y * sn[2 * i + 1] + y.y * cs[2 * i + 1]);
+    }
+    lo = make_uint4(a[0], a[1], a[2], a[3]);
+    hi = make_uint4(b[0], b[1], b[2], b[3]);
+}
+
+// The new token's key (rotated) and value into the stage that holds its page (so that this block attends to
+// it) and, if ``to_cache``, into the cache pages for later steps.  One warp; row = the token's place in its page.
+template <int D>
+__device__ __forceinline__ void put_new_token(unsigned char* stage, const bf16* __restrict__ k_raw,
+                                              const bf16* __restrict__ v_raw, const float* __restrict__ inv_freq,
+                                              float magnitude, int pos, int row, bf16* __restrict__ k_page,
+                                              bf16* __restrict__ v_page, bool to_cache, int lane) {
+    using S = DecodeSmem<D>;
+    constexpr int kHalf = D / 2;
+    const int swz = S::kSwizzleKeys ? ((row & 1) << 2) : 0;
+    bf16* k_row = reinterpret_cast<bf16*>(stage);
+    for (int c = lane; c < kHalf; c += 32) {
+        float cs = 1.f, sn = 0.f;
+        if (inv_freq) {
+            sincosf((float)pos * inv_freq[c], &sn, &cs);
+            cs *= magnitude;
+            sn *= magnitude;
+        }
+        const float x = __bfloat162float(k_raw[c]), y = __bfloat162float(k_raw[c + kHalf]);
+        const bf16 xr = __float2bfloat16_rn(x * cs - y * sn), yr = __float2bfloat16_rn(x * sn + y * cs);
+        const int c2 = c + kHalf;
+        k_row[(row * S::kChunksPerKeyRow + ((c >> 3) ^ swz)) * 8 + (c & 7)] = xr;
+        k_row[(row * S::kChunksPerKeyRow + ((c2 >> 3) ^ swz)) * 8 + (c2 & 7)] = yr;
+        if (to_cache) {
+            k_page[row * D + c] = xr;
+            k_page[row * D + c2] = yr;
+        }
+    }
+    bf16* v_rows = reinterpret_cast<bf16*>(stage + S::kKeyBytes);
+    for (int dd = lane; dd < D; dd += 32) {
+        const bf16 v = v_raw[dd];
+        v_rows[(dd * 8 + ((row >> 3) ^ ((dd & 1) << 2))) * 8 + (row & 7)] = v;
+        if (to_cache) v_page[dd * kPageTokens + row] = v;
+    }
+}
+
 template <int D>
 __global__ void __launch_bounds__(kDecodeWarps * 32, 1)
 decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                         const int* __restrict__ kv_len, const int* __restrict__ slots,
                         const int* __restrict__ page_table, int max_pages, float* __restrict__ part_o,
                         float* __restrict__ part_ml, bf16* __restrict__ out, int n_heads, int n_kv, int m_tiles,
-                        int n_splits, float scale_log2) {
+                        int n_splits, float scale_log2, DecodeRope rope) {
     // A block takes one share of a sequence's pages; its warps take every third page of the
     // share and merge their results in shared memory before anything is written.  With one share
     // per sequence the block writes the final result to ``out`` itself and no combine kernel follows.
@@ -326,17 +392,47 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
     TileState<D> st;
     st.init();
     uint4 qf[2][D / 32];
+    const int64_t q_row_stride = rope.qkv ? (int64_t)(n_heads + 2 * n_kv) * D : (int64_t)n_heads * D;
+    const bf16* q_rows = rope.qkv ? rope.qkv : q;
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         const int local = min(mt * 16 + g + 8 * r, group - 1);      // rows beyond the group repeat a valid head; never stored
-        const bf16* qrow = q + ((int64_t)b * n_heads + kvh * group + local) * D + 8 * j;
+        const bf16* qrow = q_rows + (int64_t)b * q_row_stride + (int64_t)(kvh * group + local) * D + 8 * j;
 #pragma unroll
         for (int w = 0; w < D / 32; ++w) qf[r][w] = __ldg(reinterpret_cast<const uint4*>(qrow + 32 * w));
+    }
+    if constexpr (D == 64 || D == 128) {
+        if (rope.qkv && rope.inv_freq) {
+            // this thread's dims 32w + 8j .. + 7 of the first half pair with the same dims of fragment w + D/64
+#pragma unroll
+            for (int w = 0; w < D / 64; ++w) {
+                float cs[8], sn[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    sincosf((float)(len - 1) * rope.inv_freq[32 * w + 8 * j + e], &sn[e], &cs[e]);
+                    cs[e] *= rope.magnitude;
+                    sn[e] *= rope.magnitude;
+                }
+                rotate8(qf[0][w], qf[0][w + D / 64], cs, sn);
+                rotate8(qf[1][w], qf[1][w + D / 64], cs, sn);
+            }
+        }
     }
     for (int k = 0; p0 + warp + k * kDecodeWarps < p1; ++k) {
         cp_async_wait<kDecodeStages - 1>();
         __syncwarp();
         const int p = p0 + warp + k * kDecodeWarps;
+        if constexpr (D == 64 || D == 128) {
+            if (rope.qkv && rope.write_cache && p == n_pages - 1) {
+                // the step's own token is not in the cache yet: this warp holds its page and puts it there
+                const bf16* raw = rope.qkv + (int64_t)b * q_row_stride + (int64_t)(n_heads + kvh) * D;
+                const int64_t base = (int64_t)pages[p] * page_elems + (int64_t)kvh * kPageTokens * D;
+                put_new_token<D>(smem_raw + (warp * kDecodeStages + (k % kDecodeStages)) * S::kStageBytes, raw,
+                                 raw + (int64_t)n_kv * D, rope.inv_freq, rope.magnitude, len - 1, (len - 1) % kPageTokens,
+                                 rope.k_out + base, rope.v_out + base, mt == 0, lane);
+                __syncwarp();
+            }
+        }
         attend_page_smem<D>(st, qf, my_stages + (k % kDecodeStages) * S::kStageBytes, p * kPageTokens, len - 1, len - 1,
                             scale_log2, lane);
         __syncwarp();
@@ -430,7 +526,8 @@ CPM_API int64_t cpm_decode_attention_scratch_floats(int n_seqs, int n_heads, int
 template <int D>
 static int launch_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int* kv_len,
                          const int* slots, const int* page_table, int max_pages, float* scratch, int n_seqs,
-                         int n_heads, int n_kv, int n_splits, float scale, cudaStream_t stream) {
+                         int n_heads, int n_kv, int n_splits, float scale, cudaStream_t stream,
+                         DecodeRope rope = DecodeRope{nullptr, nullptr, 1.f, 0, nullptr, nullptr}) {
     const int m_tiles = (n_heads / n_kv + 15) / 16;
     float* part_o = scratch;
     float* part_ml = scratch + (int64_t)n_seqs * n_kv * m_tiles * n_splits * 16 * D;
@@ -441,7 +538,7 @@ static int launch_decode(const void* q, const void* k_cache, const void* v_cache
     if (int st = ensure_dynamic_smem(kern, smem, configured)) return st;
     cpm_launch(kLaunchAttention, kern, grid, kDecodeWarps * 32, smem, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
                kv_len, slots, page_table, max_pages, part_o, part_ml, (bf16*)out, n_heads, n_kv, m_tiles, n_splits,
-               scale * 1.4426950408889634f);
+               scale * 1.4426950408889634f, rope);
     if (n_splits > 1)
         cpm_launch(kLaunchCombine, combine_splits_kernel, dim3(n_heads, n_seqs), D >= 128 ? 128 : 64, 0, stream, (const float*)part_o,
                    (const float*)part_ml, (bf16*)out, n_heads, n_kv, m_tiles, n_splits, (int)D);
@@ -460,6 +557,24 @@ CPM_API int cpm_decode_attention_bf16(const void* q, const void* k_cache, const 
         case 64: return launch_decode<64>(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream);
         case 96: return launch_decode<96>(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream);
         case 128: return launch_decode<128>(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream);
+        default: return CPM_BAD_ARGUMENT;
+    }
+}
+
+// The same with the step's rotation and cache store done inside (see DecodeRope): qkv [n_seqs, (heads + 2 kv) * d]
+// is the step's fused product, positions are kv_len - 1, the cache pages of the step's tokens are written here.
+// Head sizes 64 and 128 only.
+CPM_API int cpm_decode_attention_rope_bf16(const void* qkv, void* k_cache, void* v_cache, void* out,
+                                           const int* kv_len, const int* slots, const int* page_table, int max_pages,
+                                           float* scratch, int n_seqs, int n_heads, int n_kv, int d, int n_splits,
+                                           float scale, const float* inv_freq, float magnitude, int write_cache,
+                                           cudaStream_t stream) {
+    if (n_seqs <= 0) return CPM_OK;
+    if (n_kv <= 0 || n_heads % n_kv || n_splits < 1 || n_seqs > 65535 || !scratch || !qkv) return CPM_BAD_ARGUMENT;
+    const DecodeRope rope{(const bf16*)qkv, inv_freq, magnitude, write_cache, (bf16*)k_cache, (bf16*)v_cache};
+    switch (d) {
+        case 64: return launch_decode<64>(nullptr, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream, rope);
+        case 128: return launch_decode<128>(nullptr, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream, rope);
         default: return CPM_BAD_ARGUMENT;
     }
 }

@@ -12,6 +12,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
+import numpy as np
 import torch
 
 from ..cache import Cache
@@ -65,16 +66,32 @@ def plan_chunks(lengths: Sequence[int], chunk_tokens: int) -> List[Chunk]:
     return chunks
 
 
+class _PromptGraph:
+    """A recorded prompt chunk: its input buffer [ids | positions | keys after the chunk, slot | wanted rows], the
+    buffers that never change (token -> sequence, offsets, query tiles), the graph and its logits."""
+
+    def __init__(self, inputs: torch.Tensor, fixed: torch.Tensor):
+        self.inputs, self.fixed = inputs, fixed
+        self.graph: Optional[torch.cuda.CUDAGraph] = None
+        self.logits: Optional[torch.Tensor] = None
+
+
 class Stepper:
     """Drives a model over a cache, step by step."""
 
-    def __init__(self, model: Model, cache: Cache, chunk_tokens: int = 2048):
+    def __init__(self, model: Model, cache: Cache, chunk_tokens: int = 2048, graph_prompts: bool = False):
+        """``graph_prompts``: a full chunk of one sequence's prompt (``chunk_tokens`` tokens: all chunks of a long prompt
+        but the last) is recorded into a CUDA graph the first time it runs and replayed from then on, whatever the
+        history, because every kernel reads lengths, positions and pages from device memory.  It takes the host out of
+        the prompt (about ten launches a layer otherwise) and needs a model whose parts are all ``recordable_prompt``."""
         self.model = model
         self.cache = cache
         self.ops = model.ops
         self.chunk_tokens = int(chunk_tokens)
         self.vocab_size = model.spec.vocab_size
         self.taps: Optional[dict] = None      # when set, parts may leave intermediate results in it (ctx.extras["taps"])
+        self.graph_prompts = bool(graph_prompts) and model.recordable_prompt()
+        self.prompt_graphs: Dict[Tuple[int, int, int], "_PromptGraph"] = {}
 
     # ---- sequences ----
     def open(self, n: int) -> List[int]:
@@ -90,15 +107,20 @@ class Stepper:
         if not batch:
             return None
         seen = set()
+        arrays: List[np.ndarray] = []                       # every sequence's tokens, checked once, as int32
         for s in batch:
             if s.slot in seen:
                 raise ValueError(f"slot {s.slot} appears twice in one step")
             seen.add(s.slot)
             if len(s.tokens) == 0:
                 raise ValueError(f"slot {s.slot} brings no tokens")
-            for t in s.tokens:
-                if not 0 <= int(t) < self.vocab_size:
-                    raise ValueError(f"token id {t} is outside the vocabulary [0, {self.vocab_size})")
+            arr = np.asarray(s.tokens, dtype=np.int64)
+            if arr.ndim != 1:
+                raise ValueError(f"slot {s.slot}: tokens must be a flat sequence of ids")
+            if int(arr.min()) < 0 or int(arr.max()) >= self.vocab_size:
+                bad = int(arr[(arr < 0) | (arr >= self.vocab_size)][0])
+                raise ValueError(f"token id {bad} is outside the vocabulary [0, {self.vocab_size})")
+            arrays.append(arr.astype(np.int32))
             for w in s.want:
                 if not 0 <= int(w) < len(s.tokens):
                     raise ValueError(f"wanted place {w} is outside the {len(s.tokens)} tokens of slot {s.slot}")
@@ -129,7 +151,7 @@ class Stepper:
                 for i, first, count in chunk.pieces:
                     self.cache.reserve(batch[i].slot, history[i] + first + count)
                 self.cache.sync()
-            out = self._run_chunk(batch, history, chunk, [r for _, r in rows_here])
+            out = self._run_chunk(batch, arrays, history, chunk, [r for _, r in rows_here])
             if len(chunks) > 1:
                 for i, first, count in chunk.pieces:
                     self.cache.set_length(batch[i].slot, history[i] + first + count)
@@ -143,34 +165,101 @@ class Stepper:
             self.cache.set_length(s.slot, h + n)
         return logits
 
-    def _run_chunk(self, batch, history, chunk: Chunk, want_rows: List[int]) -> Optional[torch.Tensor]:
-        ids: List[int] = []
-        positions: List[int] = []
-        token_seq: List[int] = []
-        cu_q = [0]
+    def _graph_chunk(self, tokens: np.ndarray, slot: int, start: int, want_rows: List[int]) -> Optional[torch.Tensor]:
+        """A full chunk of one sequence through its recorded graph; None if there is none yet (the chunk then runs
+        the ordinary way, and is recorded afterwards for the chunks to come)."""
+        n = int(tokens.shape[0])
+        g = self.prompt_graphs[(n, len(want_rows), self._length_bound(start + n))]
+        host = np.concatenate([tokens, np.arange(start, start + n, dtype=np.int32),
+                               np.asarray([start + n, slot] + list(want_rows), dtype=np.int32)])
+        g.inputs.copy_(torch.from_numpy(host))
+        g.graph.replay()
+        return None if g.logits is None else g.logits.clone()
+
+    def _length_bound(self, kv_len: int) -> int:
+        """The bound on the sequence's length that a recorded chunk is made for: the next power of two (at least
+        1,024), at most the cache's capacity per sequence.  Parts decide on the host from this bound (which kernel,
+        how many shares, dense or sparse attention), so a recording serves every chunk below its bound."""
+        bound = 1024
+        while bound < kv_len:
+            bound *= 2
+        return min(bound, self.cache.max_pages_per_seq * 64)
+
+    def _record_chunk(self, n: int, n_want: int, bound: int) -> None:
+        """Records the graph of a full chunk of ``n`` tokens with ``n_want`` wanted rows for sequences of up to
+        ``bound`` tokens.  Nothing runs: the recording's own launches are never executed."""
+        ops, dev = self.ops, self.ops.device
+        inputs = torch.zeros(2 * n + 2 + n_want, dtype=torch.int32, device=dev)
+        n_tiles = (n + PREFILL_TILE_ROWS - 1) // PREFILL_TILE_ROWS
+        fixed = torch.cat([torch.zeros(n, dtype=torch.int32), torch.tensor([0, n], dtype=torch.int32),
+                           torch.zeros(n_tiles, dtype=torch.int32),
+                           torch.arange(0, n, PREFILL_TILE_ROWS, dtype=torch.int32)]).to(dev)
+        g = _PromptGraph(inputs, fixed)
+        def body():
+            ws = ops.workspace
+            if ws is not None:
+                ws.require(n, 1)
+            ops.begin_step()
+            ctx = StepContext(
+                n_tokens=n, n_seqs=1, is_decode=(n == 1), captured=True, q_lens=[n], kv_lens=[], slots=[], max_q_len=n,
+                max_kv_len=bound, token_ids=inputs[:n], positions=inputs[n:2 * n], token_seq=fixed[:n],
+                cu_q=fixed[n:n + 2], kv_len_dev=inputs[2 * n:2 * n + 1], slot_dev=inputs[2 * n + 1:2 * n + 2], cache=self.cache)
+            ctx.extras["q_tiles"] = (fixed[n + 2:n + 2 + n_tiles], fixed[n + 2 + n_tiles:], n_tiles)
+            ctx.extras["step_begun"] = True
+            return self.model.forward(ctx, inputs[2 * n + 2:] if n_want else None)
+
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            g.logits = body()
+        g.graph = graph
+        self.prompt_graphs[(n, n_want, bound)] = g
+
+    def _run_chunk(self, batch, arrays, history, chunk: Chunk, want_rows: List[int]) -> Optional[torch.Tensor]:
+        record = False
+        if self.graph_prompts and self.taps is None and len(chunk.pieces) == 1 and chunk.pieces[0][2] == self.chunk_tokens \
+                and self.chunk_tokens > 1:
+            i, first, count = chunk.pieces[0]
+            bound = self._length_bound(history[i] + first + count)
+            if (count, len(want_rows), bound) in self.prompt_graphs:
+                return self._graph_chunk(arrays[i][first:first + count], batch[i].slot, history[i] + first, want_rows)
+            record = True                     # this one runs the ordinary way (it also warms the kernels up), then the graph is made
+        out = self._run_chunk_eager(batch, arrays, history, chunk, want_rows)
+        if record:
+            self._record_chunk(chunk.pieces[0][2], len(want_rows), bound)
+        return out
+
+    def _run_chunk_eager(self, batch, arrays, history, chunk: Chunk, want_rows: List[int]) -> Optional[torch.Tensor]:
         kv_lens: List[int] = []
         q_lens: List[int] = []
         slots: List[int] = []
-        for j, (i, first, count) in enumerate(chunk.pieces):
-            s = batch[i]
-            ids.extend(int(t) for t in s.tokens[first:first + count])
+        id_parts, pos_parts = [], []
+        for i, first, count in chunk.pieces:
             start = history[i] + first
-            positions.extend(range(start, start + count))
-            token_seq.extend([j] * count)
-            cu_q.append(cu_q[-1] + count)
+            id_parts.append(arrays[i][first:first + count])
+            pos_parts.append(np.arange(start, start + count, dtype=np.int32))
             kv_lens.append(start + count)
             q_lens.append(count)
-            slots.append(s.slot)
-        n_tok, n_seq = len(ids), len(slots)
+            slots.append(batch[i].slot)
+        ids = np.concatenate(id_parts)
+        q_arr = np.asarray(q_lens, dtype=np.int32)
+        cu_q = np.zeros(len(q_lens) + 1, dtype=np.int32)
+        np.cumsum(q_arr, out=cu_q[1:])
+        n_tok, n_seq = int(ids.shape[0]), len(slots)
         ws = self.ops.workspace
         if ws is not None:
             ws.require(n_tok, n_seq)          # a step the workspace was not sized for is refused before anything runs
         self.ops.begin_step()
         # query tiles of the prefill attention kernel: (sequence, first token of the tile)
-        tile_seq = [j for j, n in enumerate(q_lens) for _ in range(0, n, PREFILL_TILE_ROWS)]
-        tile_row = [r for n in q_lens for r in range(0, n, PREFILL_TILE_ROWS)]
-        packed = torch.tensor(ids + positions + token_seq + cu_q + kv_lens + slots + want_rows + tile_seq + tile_row,
-                              dtype=torch.int32)
+        tiles_per = (q_arr + PREFILL_TILE_ROWS - 1) // PREFILL_TILE_ROWS
+        tile_seq = np.repeat(np.arange(len(q_lens), dtype=np.int32), tiles_per)
+        tile_first = np.zeros(len(q_lens), dtype=np.int32)
+        np.cumsum(tiles_per[:-1], out=tile_first[1:])
+        tile_row = (np.arange(int(tiles_per.sum()), dtype=np.int32) - np.repeat(tile_first, tiles_per)) * PREFILL_TILE_ROWS
+        packed = torch.from_numpy(np.concatenate([
+            ids, np.concatenate(pos_parts), np.repeat(np.arange(len(q_lens), dtype=np.int32), q_arr), cu_q,
+            np.asarray(kv_lens, dtype=np.int32), np.asarray(slots, dtype=np.int32), np.asarray(want_rows, dtype=np.int32),
+            tile_seq, tile_row.astype(np.int32)]).astype(np.int32, copy=False))
         dev = self.ops.empty(packed.numel(), dtype=torch.int32)
         dev.copy_(packed)                     # pageable staging: the copy is over when this returns
         o = 0

@@ -100,7 +100,7 @@ class LLM:
             self.cache = Cache(needs, max_tokens=tokens, dtype=self.dtype, device=self.device,
                                n_slots=min(max(2, tokens // PAGE_TOKENS), self.max_batch * 2 + 2), max_seq_tokens=per_seq,
                                max_step_tokens=self.chunk_length)
-        self.stepper = Stepper(self.model, self.cache, chunk_tokens=self.chunk_length)
+        self.stepper = Stepper(self.model, self.cache, chunk_tokens=self.chunk_length, graph_prompts=self.cuda_graph)
         self.max_total_length = self.cache.max_pages_per_seq * PAGE_TOKENS
         return self.max_total_length
 

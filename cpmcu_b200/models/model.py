@@ -66,6 +66,13 @@ class Model:
         total = sum(self.blocks[e.layer].weight_bytes() for e in self.schedule)
         return total + self.final_norm.weight_bytes() + self.head.weight_bytes()
 
+    def recordable_prompt(self) -> bool:
+        """Whether every part can run a prompt chunk without reading the batch on the host (see Part)."""
+        parts = [self.embedding, self.final_norm, self.head]
+        for b in self.blocks:
+            parts += [b, b.mixer, b.feed_forward, b.mixer_norm, b.feed_forward_norm]
+        return all(bool(getattr(p, "recordable_prompt", False)) for p in parts)
+
     # ---- cache ----
     def cache_needs(self) -> List[CacheNeeds]:
         needs: List[Optional[CacheNeeds]] = [None] * self.spec.n_lanes()

@@ -38,6 +38,8 @@ _SIGNATURES = {
                           c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, _P, c_int, _P],
     "cpm_advance_decode": [_P, _P, _P, _P, _P, _P, c_int, _P],
     "cpm_decode_attention_bf16": [_P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, c_float, _P],
+    "cpm_decode_attention_rope_bf16": [_P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, c_float,
+                                       _P, c_float, c_int, _P],
     "cpm_prefill_attention_bf16": [_P, _P, _P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float,
                                    _P],
     "cpm_listed_attention_bf16": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, c_float, _P,

@@ -168,7 +168,11 @@ class Ops:
 
     # ---- matrix products ----
     SKINNY_MAX_ROWS = int(os.environ.get("CPMCU_SKINNY_MAX_ROWS", "8"))   # most rows the weight-streaming product takes
-    TCGEN05_MIN_ROWS = 256       # below this the 128-row tiles of the tcgen05 product are mostly empty
+    # From this many rows on the gated product runs on the tcgen05 kernel.  Its 128-row tiles are mostly empty for a
+    # decode batch, but the product is bound by streaming the weights, not by the tensor cores: at 16 to 128 rows
+    # it takes 51 us on the 8B gate_up shape (5.2 TB/s) with the activation applied in the epilogue, where the library
+    # product takes 51 us and the activation kernel 4 us more.
+    TCGEN05_MIN_ROWS = int(os.environ.get("CPMCU_TCGEN05_MIN_ROWS", "9"))
     SELECT_SCRATCH_BYTES = 64 << 20     # most scratch the sliced block selection may take (raw scores of all pooled keys)
 
     def _skinny_ok(self, M: int, K: int) -> bool:
@@ -236,8 +240,9 @@ class Ops:
             check(self.lib.cpm_gemm_skinny_bf16(_ptr(w_gate_up), _ptr(a), _ptr(h), M, w_gate_up.shape[0], K, 1.0, 2,
                                                 self._stream()), "gated skinny matrix product")
             return h
+        few_tiles = M < 256 and w_gate_up.shape[0] // 256 < self.sm_count // 2     # a decode batch on a narrow model: too few blocks
         if (self.code == BF16 and interleave == 8 and self.use_tcgen05 and M >= self.TCGEN05_MIN_ROWS and K % 64 == 0
-                and w_gate_up.shape[0] % 32 == 0 and a.data_ptr() % 16 == 0):
+                and w_gate_up.shape[0] % 32 == 0 and a.data_ptr() % 16 == 0 and not few_tiles):
             # many rows (prefill): the tcgen05 product applies the activation in its epilogue
             return self.linear_tcgen05(a, w_gate_up, gated=True, pair=self.tcgen05_pair)
         return self.silu_mul(self.linear(a, w_gate_up), interleave)
@@ -339,7 +344,7 @@ class Ops:
         cap = sparse["topk"] + local_blocks + 2
         # an upper bound on the pooled keys a query sees; it sizes the sort of the candidate blocks (8 bytes of shared
         # memory per block), not the walk over the pooled keys, which follows each query's own position
-        longest = lane.page_table.shape[1] * PAGE_TOKENS if ctx.captured else ctx.max_kv_len
+        longest = ctx.max_kv_len          # in a recorded step an upper bound (the cache's capacity per sequence, or less)
         max_entries = max(1, longest // stride + 1)
         lists = self.empty(n, n_kv, cap, dtype=torch.int32)
         # few queries (a decode step): share every query's pooled keys out over many blocks, in two kernels
@@ -389,6 +394,41 @@ class Ops:
               f"decode attention (head_dim {d})")
         if n_splits > 1:
             LAUNCHES_EXTRA[0] += 1       # the launcher starts two kernels: the shares, then their combination
+        return out
+
+    FUSED_ROPE_HEAD_DIMS = (64, 128)      # head sizes whose rotary pairs lie in one thread's fragments of the decode kernel
+
+    def fused_decode_ok(self, ctx, d: int, rot_dim: int, window: int, sparse) -> bool:
+        """Whether a decode step's rotation and cache store can be done by the attention kernel itself."""
+        return (self.code == BF16 and ctx.is_decode and not window and sparse is None and d in self.FUSED_ROPE_HEAD_DIMS
+                and rot_dim in (0, d) and os.environ.get("CPMCU_FUSED_ROPE", "1") != "0")
+
+    def decode_attention_rope(self, qkv: torch.Tensor, lane, kv_len: torch.Tensor, slots: torch.Tensor, n_heads: int,
+                              n_kv: int, d: int, scale: float, inv_freq: Optional[torch.Tensor], magnitude: float,
+                              write_cache: bool, n_splits: Optional[int] = None) -> torch.Tensor:
+        """A decode step's attention straight from the fused product qkv [seqs, (heads + 2 kv) * d]: the kernel
+        rotates q and the new key (position = keys - 1), stores the new key and value into the sequence's page (when
+        ``write_cache``) and attends.  One launch less than rope_store followed by decode_attention."""
+        self._act(qkv, "qkv")
+        n = qkv.shape[0]
+        if qkv.shape[1] != (n_heads + 2 * n_kv) * d:
+            raise ValueError("qkv row size does not match the head counts")
+        if inv_freq is not None:
+            self._f32(inv_freq, "inv_freq")
+            if inv_freq.numel() != d // 2:
+                raise ValueError("inv_freq needs head_dim/2 entries")
+        if n_splits is None:
+            n_splits = self.decode_splits(n, n_heads, n_kv)
+        floats = self.lib.cpm_decode_attention_scratch_floats(n, n_heads, n_kv, d, n_splits)
+        scratch = self.empty(floats, dtype=torch.float32)
+        out = self.empty(n, n_heads * d)
+        check(self.lib.cpm_decode_attention_rope_bf16(_ptr(qkv), _ptr(lane.k), _ptr(lane.v), _ptr(out), _ptr(kv_len),
+                                                      _ptr(slots), _ptr(lane.page_table), lane.page_table.shape[1],
+                                                      _ptr(scratch), n, n_heads, n_kv, d, n_splits, float(scale),
+                                                      _ptr(inv_freq), float(magnitude), 1 if write_cache else 0,
+                                                      self._stream()), f"decode attention with rotation (head_dim {d})")
+        if n_splits > 1:
+            LAUNCHES_EXTRA[0] += 1
         return out
 
     def prefill_attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, tiles,

@@ -21,6 +21,10 @@ from .base import MIXERS, POSITIONS, CacheNeeds, Mixer, PartSpec, WeightSpec, bu
 
 @MIXERS.register("gqa_attention")
 class GroupedQueryAttention(Mixer):
+    @property
+    def recordable_prompt(self) -> bool:
+        return bool(self.position.recordable_prompt)
+
     def __init__(self, ops, hidden_size: int, n_heads: int, n_kv_heads: int, head_dim: int,
                  position: PartSpec, window: Optional[int] = None, sparse: Optional[Mapping[str, int]] = None,
                  softmax_scale: Optional[float] = None, position_name: str = ""):
@@ -97,6 +101,11 @@ class GroupedQueryAttention(Mixer):
             row = qkv.view(ctx.n_tokens, self.n_heads + 2 * self.n_kv, self.d)
             self.position.apply(ctx, row[:, :self.n_heads], row[:, self.n_heads:self.n_heads + self.n_kv])
             inv_freq, magnitude, rot_dim = None, 1.0, 0
+        if rot_dim >= 0 and ops.fused_decode_ok(ctx, self.d, rot_dim, self.window, self.sparse):
+            # one token per sequence: the attention kernel rotates, stores the new key and value, and attends
+            out = ops.decode_attention_rope(qkv, lane, ctx.kv_len_dev, ctx.slot_dev, self.n_heads, self.n_kv, self.d,
+                                            self.scale, inv_freq if rot_dim else None, magnitude, writes_cache)
+            return ops.linear(out, self.w_o)
         q = ops.rope_store(qkv, self.n_heads, self.n_kv, self.d, ctx.positions, ctx.token_seq, ctx.slot_dev,
                            lane.page_table, k_cache if writes_cache else None, v_cache if writes_cache else None,
                            inv_freq, magnitude, rot_dim)
@@ -104,7 +113,7 @@ class GroupedQueryAttention(Mixer):
         if self.sparse is not None:
             if writes_cache:
                 ops.pool_keys(ctx, lane, self.n_kv, self.d, self.sparse["kernel_size"], self.sparse["kernel_stride"])
-            if ctx.captured or ctx.max_kv_len > self.sparse.get("dense_len", 0):
+            if ctx.max_kv_len > self.sparse.get("dense_len", 0):      # in a recorded step an upper bound: still the right test
                 block_list, block_size = ops.select_blocks(ctx, q, lane, self.n_kv, self.scale, self.sparse)
                 taps = ctx.extras.get("taps")
                 if taps is not None and not ctx.captured:

@@ -176,6 +176,11 @@ class Part:
         """Bytes of weights one step reads (each tensor once)."""
         return 0
 
+    # True if ``forward`` reads nothing of the batch on the host but ``n_tokens``, ``n_seqs``, ``q_lens`` and the
+    # upper bound ``max_kv_len``, for prompts too: such a part can be recorded into a graph for a prompt chunk
+    # (a part that walks ``ctx.slots`` or ``ctx.kv_lens`` on the host cannot; the default is the safe answer).
+    recordable_prompt = False
+
 
 class Norm(Part):
     def forward(self, x: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
@@ -336,11 +341,12 @@ class StepContext:
     by the step function, and by the decode runner without a graph (its padding
     entries appear as sequences of one key in a scratch slot).
 
-    In a captured decode step (``captured`` True) the device tensors are fixed
+    In a captured step (``captured`` True: a decode step, or a prompt chunk of one
+    sequence when every part of the model is ``recordable_prompt``) the device tensors are fixed
     buffers whose contents change between replays; the recording is made once, on
     padding entries only, and replayed for any batch.  A part may then read only:
-    ``n_tokens``, ``n_seqs`` (the bucket size), ``is_decode`` (True), ``q_lens`` (all 1),
-    ``max_q_len`` (1), ``max_kv_len`` (the cache's capacity per sequence, an upper
+    ``n_tokens``, ``n_seqs`` (the bucket size), ``is_decode``, ``q_lens`` (all 1, or the chunk's size),
+    ``max_q_len``, ``max_kv_len`` (the cache's capacity per sequence, an upper
     bound), the device tensors, ``cache`` and its lanes.  ``kv_lens`` and ``slots`` are
     empty; everything that depends on a sequence (its slot, its length, its state
     in ``lane.state[name][slot]``) has to be reached on the device through

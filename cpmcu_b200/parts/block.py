@@ -13,6 +13,8 @@ class PreNormResidualBlock(Block):
     The scale is a parameter of the block; the block does not know where it comes from.
     """
 
+    recordable_prompt = True
+
     def __init__(self, ops, mixer, feed_forward, mixer_norm, feed_forward_norm, names,
                  residual_scale: float = 1.0):
         super().__init__(ops, mixer, feed_forward, mixer_norm, feed_forward_norm, names)

@@ -19,6 +19,8 @@ HEADS: Registry[Type[Part]] = Registry("output head")
 
 @EMBEDDINGS.register("scaled_embedding")
 class ScaledEmbedding(Part):
+    recordable_prompt = True
+
     def __init__(self, ops, vocab_size: int, hidden_size: int, scale: float = 1.0):
         super().__init__(ops)
         self.vocab_size, self.hidden_size, self.scale = int(vocab_size), int(hidden_size), float(scale)
@@ -36,6 +38,8 @@ class ScaledEmbedding(Part):
 
 @HEADS.register("scaled_lm_head")
 class ScaledHead(Part):
+    recordable_prompt = True
+
     def __init__(self, ops, vocab_size: int, hidden_size: int, scale: float = 1.0, tied: bool = False):
         super().__init__(ops)
         self.vocab_size, self.hidden_size, self.scale, self.tied = int(vocab_size), int(hidden_size), float(scale), bool(tied)

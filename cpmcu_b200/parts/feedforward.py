@@ -15,6 +15,8 @@ from .base import FEED_FORWARDS, FeedForward, WeightSpec
 
 @FEED_FORWARDS.register("gated_ffn")
 class GatedFeedForward(FeedForward):
+    recordable_prompt = True
+
     def __init__(self, ops, hidden_size: int, intermediate_size: int, activation: str = "silu"):
         super().__init__(ops)
         if activation != "silu":

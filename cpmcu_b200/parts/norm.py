@@ -11,6 +11,8 @@ from .base import NORMS, Norm, WeightSpec
 
 @NORMS.register("rms_norm")
 class RMSNorm(Norm):
+    recordable_prompt = True
+
     def __init__(self, ops, hidden_size: int, eps: float):
         super().__init__(ops)
         self.hidden_size = int(hidden_size)

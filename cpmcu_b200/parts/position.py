@@ -28,6 +28,8 @@ from .base import POSITIONS, PositionEncoding
 class NoPosition(PositionEncoding):
     """No position information: queries and keys pass unchanged."""
 
+    recordable_prompt = True
+
     def __init__(self, ops):
         super().__init__(ops)
 
@@ -37,6 +39,8 @@ class NoPosition(PositionEncoding):
 
 @POSITIONS.register("rope")
 class Rotary(PositionEncoding):
+    recordable_prompt = True
+
     def __init__(self, ops, head_dim: int, theta: float, rot_dim: Optional[int] = None):
         super().__init__(ops)
         self.rot_dim = int(rot_dim if rot_dim is not None else head_dim)

@@ -88,7 +88,10 @@ def test_workspace_is_measured_by_the_models_own_forward_pass():
             assert notes == [] and p > 0 and f > 0
             sizes[(name, chunk)] = (p, f)
         # four times the tokens: up to four times the frame (per-token tensors, plus padding and scratch that do not grow)
-        assert 2.0 < sizes[(name, 256)][1] / sizes[(name, 64)][1] < 4.5
+        if name == "a":
+            assert 2.0 < sizes[(name, 256)][1] / sizes[(name, 64)][1] < 4.5
+        else:       # the sparse model's largest tensor is the block selection's scratch for steps of few tokens
+            assert sizes[(name, 256)][1] >= sizes[(name, 64)][1]
     p32, f32, _ = measure_workspace(arch.model_spec(arch.config_class.from_dict(configs.tiny_a())), torch.float32, 64, 4, 1024)
     assert f32 > sizes[("a", 64)][1]
     # a frame holds at least the widest tensor of a layer: the gate_up product of 64 tokens

@@ -615,7 +615,8 @@ def test_select_blocks_at_long_context_sizes(dtype):
         q_rows = all_rows if pick is None else all_rows[pick]
         qkv = all_qkv if pick is None else all_qkv[pick].contiguous()
         m = len(sample)
-        ctx = StepContext(m, 1, False, captured, [m], [n], [slot], m, n, i32([0] * m), i32(sample), i32([0] * m),
+        longest = cache.max_pages_per_seq * 64 if captured else n       # a recorded step knows only the cache's capacity
+        ctx = StepContext(m, 1, False, captured, [m], [n], [slot], m, longest, i32([0] * m), i32(sample), i32([0] * m),
                           i32([0, m]), i32([n]), sl, cache)
         q = ops.rope_store(qkv.view(m, -1).cuda(), n_heads, n_kv, d, ctx.positions, ctx.token_seq, sl, lane.page_table,
                            None, None, None, 1.0, 0)
@@ -643,3 +644,91 @@ def test_select_blocks_at_long_context_sizes(dtype):
                 assert len(got) == 64 + 32              # the leading block and 63 chosen ones, then the local window
                 checked += 1
         assert checked >= 0.8 * m * n_kv, (checked, m * n_kv)
+
+
+@pytest.mark.parametrize("M", [9, 17, 40, 64, 200])
+def test_gated_product_of_a_decode_batch_takes_the_own_kernel(M):
+    """9 to 255 rows (a decode batch) against a wide gate_up matrix: the gated product runs on the tcgen05 kernel
+    with the activation in its epilogue (one launch of this library, no library product), against fp32 torch."""
+    from cpmcu_b200.ops import library
+
+    ops = _ops("bfloat16")
+    inter, K = 9600, 128                                            # 75 tiles of 256 interleaved rows
+    g = torch.Generator().manual_seed(19)
+    a = torch.randn(M, K, generator=g).bfloat16().cuda()
+    gate_w = (torch.randn(inter, K, generator=g) * 0.05).bfloat16().cuda()
+    up_w = (torch.randn(inter, K, generator=g) * 0.05).bfloat16().cuda()
+    wi = torch.stack([gate_w.view(inter // 8, 8, K), up_w.view(inter // 8, 8, K)], dim=1).reshape(2 * inter, K).contiguous()
+    before = library.LAUNCHES[0]
+    h = ops.gated_linear(a, wi, 8)
+    assert library.LAUNCHES[0] - before == 1
+    assert ops.tcgen05_error() == 0
+    gate, up = a.float() @ gate_w.float().T, a.float() @ up_w.float().T
+    assert _err(h, gate * torch.sigmoid(gate) * up) < KTOL["bfloat16"]
+
+
+@pytest.mark.parametrize("n_heads,n_kv,d", [(32, 2, 128), (16, 2, 64), (6, 3, 128), (20, 1, 64)])
+def test_decode_attention_with_rotation_inside(n_heads, n_kv, d):
+    """The decode kernel that rotates q and the new key and stores the new key and value itself, against the
+    rotary kernel followed by the plain decode kernel and against fp32 torch: the new token at the start, in the
+    middle and at the end of a page, a sequence of one token, groups of more than 16 heads; afterwards both caches
+    hold the same keys and values.  Also without rotation and without the store (a lane another run has written)."""
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.parts.base import CacheNeeds
+
+    ops = _ops("bfloat16")
+    lens = [1, 64, 65, 300, 129, 640, 2, 191]                  # keys per sequence after this step
+    g = torch.Generator().manual_seed(29)
+    caches = [Cache([CacheNeeds(kv_heads=n_kv, head_dim=d)], max_tokens=64 * 40, dtype=torch.bfloat16, device="cuda:0")
+              for _ in range(2)]
+    inv_freq = (1.0 / (10000.0 ** (torch.arange(0, d, 2, dtype=torch.float32) / d))).cuda()
+    mag = 1.1
+    hist = [n - 1 for n in lens]
+    T = sum(hist)
+    old = torch.randn(T, (n_heads + 2 * n_kv) * d, generator=g).bfloat16().cuda()
+    new = torch.randn(len(lens), (n_heads + 2 * n_kv) * d, generator=g).bfloat16().cuda()
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32).cuda()
+    slots_of = []
+    for c in caches:                                          # the history, stored by the rotary kernel in both caches
+        slots = c.open_sequences(len(lens))
+        for s, n in zip(slots, lens):
+            c.reserve(s, n)
+        c.sync()
+        lane = c.lane(0)
+        pos = torch.cat([torch.arange(n) for n in hist]).int().cuda()
+        seq = torch.cat([torch.full((n,), i) for i, n in enumerate(hist)]).int().cuda()
+        ops.rope_store(old, n_heads, n_kv, d, pos, seq, i32(slots), lane.page_table, lane.k, lane.v, inv_freq, mag, d)
+        slots_of.append(i32(slots))
+    kv_len, scale = i32(lens), 1 / math.sqrt(d)
+    seq = torch.arange(len(lens)).int().cuda()
+    for splits in (None, 1, 3):
+        a, b = caches[0].lane(0), caches[1].lane(0)
+        q = ops.rope_store(new, n_heads, n_kv, d, i32(hist), seq, slots_of[0], a.page_table, a.k, a.v, inv_freq, mag, d)
+        want = ops.decode_attention(q, a.k, a.v, kv_len, slots_of[0], a.page_table, n_kv, scale, n_splits=splits)
+        got = ops.decode_attention_rope(new, b, kv_len, slots_of[1], n_heads, n_kv, d, scale, inv_freq, mag, True, n_splits=splits)
+        assert _err(got, want) < 2e-3, splits             # same arithmetic; the rotation may round the last bit otherwise
+        assert _err(b.k, a.k) < 1e-2 and torch.equal(b.v, a.v)
+        # the lane is written already: only q comes from the product
+        again = ops.decode_attention_rope(new, b, kv_len, slots_of[1], n_heads, n_kv, d, scale, inv_freq, mag, False, n_splits=splits)
+        assert _err(again, want) < 2e-3
+    # fp32 torch on the last sequence but one
+    i = 5
+    rows_old = old.float().cpu().view(T, n_heads + 2 * n_kv, d)[sum(hist[:i]):sum(hist[:i + 1])]
+    rows = torch.cat([rows_old, new.float().cpu().view(len(lens), -1, d)[i:i + 1]])
+    pos = torch.arange(lens[i])
+    qr = plain.rotate(rows[:, :n_heads], pos, inv_freq.cpu(), mag)
+    kr = plain.rotate(rows[:, n_heads:n_heads + n_kv], pos, inv_freq.cpu(), mag)
+    ref = plain.dense_attention(qr, kr, rows[:, n_heads + n_kv:], scale)[-1].reshape(-1)
+    assert _err(got[i], ref) < KTOL["bfloat16"]
+    # no rotation at all (an encoding applied before, or none)
+    c = Cache([CacheNeeds(kv_heads=n_kv, head_dim=d)], max_tokens=64 * 4, dtype=torch.bfloat16, device="cuda:0")
+    s = c.open_sequence()
+    c.reserve(s, 3)
+    c.sync()
+    lane = c.lane(0)
+    three = torch.randn(3, (n_heads + 2 * n_kv) * d, generator=g).bfloat16().cuda()
+    ops.rope_store(three[:2].contiguous(), n_heads, n_kv, d, i32([0, 1]), i32([0, 0]), i32([s]), lane.page_table, lane.k, lane.v, None, 1.0, 0)
+    got = ops.decode_attention_rope(three[2:].contiguous(), lane, i32([3]), i32([s]), n_heads, n_kv, d, scale, None, 1.0, True)
+    r3 = three.float().cpu().view(3, -1, d)
+    ref = plain.dense_attention(r3[:, :n_heads], r3[:, n_heads:n_heads + n_kv], r3[:, n_heads + n_kv:], scale)[-1].reshape(-1)
+    assert _err(got[0], ref) < KTOL["bfloat16"]

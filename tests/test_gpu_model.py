@@ -245,3 +245,42 @@ def test_short_chunks_after_a_long_history(model_folders, name, make, seed):
     helpers.check_rows(tail, folder, ids, range(n, n + 10), dtype, (name, "decoded"))
     st.close(slot)
     st.ops.raise_on_kernel_error()
+
+
+@pytest.mark.parametrize("name,make,seed,dtype", [("tiny_a", configs.tiny_a, 0, "float32"), ("tiny_a", configs.tiny_a, 0, "bfloat16"),
+                                                  ("tiny_b", configs.tiny_b, 1, "float32"), ("tiny_e", configs.tiny_e, 6, "bfloat16"),
+                                                  ("tiny_f", configs.tiny_f, 7, "bfloat16")])
+def test_full_prompt_chunks_through_a_recorded_graph(model_folders, name, make, seed, dtype):
+    """Prompts of several chunks with the chunk graph on: the first full chunk runs the ordinary way and is recorded,
+    the later ones (other histories, another sequence in another slot, a reused slot) are replays; the last, partial
+    chunk and the decode steps run the ordinary way again.  Logits at places in every chunk against the plain
+    implementation."""
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.engine import SequenceStep, Stepper
+    from cpmcu_b200.loading import load_model
+
+    folder = model_folders(name, make(), seed, dtype)
+    _, cfg, model = load_model(folder, dtype)
+    chunk = 64
+    cache = Cache(model.cache_needs(), max_tokens=64 * 24, dtype=model.ops.dtype, device="cuda:0", max_step_tokens=chunk)
+    st = Stepper(model, cache, chunk_tokens=chunk, graph_prompts=True)
+    assert st.graph_prompts
+    limit = min(cfg.max_position_embeddings, 330) if name != "tiny_a" else 120
+    for round_, n in enumerate((limit, limit - 70, limit - 3)):
+        ids = helpers.random_ids(cfg.vocab_size, n + 3, 300 + round_)
+        places = sorted(p for p in {0, 5, 63, 64, 65, 127, 128, n // 2, n - 2, n - 1} if p < n)
+        slot = st.open(1)[0]
+        got = st.step([SequenceStep(slot, ids[:n], places)])
+        helpers.check_rows(got, folder, ids, places, dtype, (name, round_, "prompt"))
+        tail = torch.cat([st.step([SequenceStep(slot, ids[i:i + 1], [0])]) for i in range(n, n + 3)])
+        helpers.check_rows(tail, folder, ids, range(n, n + 3), dtype, (name, round_, "decoded"))
+        if round_ != 1:
+            st.close(slot)                                    # round 2 runs beside round 1's sequence, in another slot
+    assert len(st.prompt_graphs) >= 1 and all(k[0] == chunk and k[2] == 1024 for k in st.prompt_graphs)
+    st.ops.raise_on_kernel_error()
+    # a model with a part that reads the batch on the host keeps to the ordinary way
+    from tests import toy_arch  # noqa: F401  (registers the architecture)
+    from cpmcu_b200.models.model import Model
+    from cpmcu_b200.registry import architecture
+    toy = architecture(toy_arch.NAME)
+    assert not Model(toy.model_spec(toy.config_class.from_dict(toy_arch.config_dict())), None).recordable_prompt()
