@@ -168,6 +168,12 @@ def build_engine(n_layers: int, max_tokens: int, max_batch: int, model: dict = N
     model = build_model(arch, cfg, torch.bfloat16, "cuda:0")
     chunk = chunk_tokens or PREFILL_TOKENS
     # one arena: weights, step workspace, per-sequence state and the key-value pages (as the Python entry point does)
+    if os.environ.get("CPMCU_BENCH_ARENA", "1") == "0":              # for comparisons: every tensor from torch's allocator
+        from cpmcu_b200.cache import Cache
+        model.load_weights(random_tensors(model.weight_specs(), seed, torch.bfloat16, std=0.02, norm_mean=1.0, device="cuda:0"))
+        cache = Cache(model.cache_needs(), max_tokens=max_tokens, dtype=torch.bfloat16, device="cuda:0",
+                      n_slots=max_batch + 2, max_seq_tokens=max_seq_tokens or CONTEXT + 64, max_step_tokens=chunk)
+        return cfg, model, cache, Stepper(model, cache, chunk_tokens=chunk, graph_prompts=True)
     storage = make_storage(model, chunk, max_batch, max_tokens=max_tokens, max_seq_tokens=max_seq_tokens or CONTEXT + 64,
                            n_slots=max_batch + 2)
     model.load_weights(random_tensors(model.weight_specs(), seed, torch.bfloat16, std=0.02, norm_mean=1.0, device="cuda:0"))

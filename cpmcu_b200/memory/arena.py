@@ -19,7 +19,9 @@ from typing import Dict, List, Optional, Sequence, Tuple
 
 import torch
 
-ALIGN = 256
+import os
+
+ALIGN = int(os.environ.get("CPMCU_ARENA_ALIGN", "256"))      # every tensor of the arena starts at a multiple of this
 
 
 def round_up(n: int, to: int = ALIGN) -> int:
