@@ -29,9 +29,9 @@ def plain_greedy(folder, prompt, n_new, stop=()):
 
 
 def check_greedy(folder, prompt, got, dtype, n_new, stop=()):
-    """fp32: the very tokens of the plain implementation.  bf16: every chosen token is
-    within the rounding margin of the plain implementation's best logit, given the
-    engine's own history."""
+    """fp32: the very tokens of the plain implementation.  bf16: every chosen token is within the rounding margin of
+    the plain implementation's best logit, given the engine's own history; that is a check of the loop, not of the
+    values: the logits of the decode runner are compared row by row in test_gpu_runner.py."""
     if dtype == "float32":
         want, _ = plain_greedy(folder, prompt, n_new, stop)
         assert got == want
