@@ -605,6 +605,8 @@ listed_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
     const int kvh = blockIdx.y / m_tiles, mt = blockIdx.y % m_tiles;
     const int group = n_heads / n_kv;
     const int j = lane & 3, g = lane >> 2;
+    pdl_launch_dependents();
+    pdl_wait();
     const int p = positions[t];
     const int* pages = page_table + (int64_t)slots[token_seq[t]] * max_pages;
     const int* list = block_list + ((int64_t)t * n_kv + kvh) * list_cap;
@@ -708,9 +710,9 @@ static int launch_listed(const void* q, const void* k_cache, const void* v_cache
     constexpr int smem = DecodeSmem<D>::kTotal;
     static bool configured[kMaxDevices] = {};            // per kernel and per device
     if (int st = ensure_dynamic_smem(kern, smem, configured)) return st;
-    kern<<<dim3(n_tokens, n_kv * m_tiles, n_splits), kDecodeWarps * 32, smem, stream>>>((const bf16*)q, (const bf16*)k_cache,
-        (const bf16*)v_cache, (bf16*)out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_heads,
-        n_kv, m_tiles, scale * 1.4426950408889634f, part_o, part_ml, n_splits);
+    cpm_launch(kLaunchAttention, kern, dim3(n_tokens, n_kv * m_tiles, n_splits), kDecodeWarps * 32, smem, stream, (const bf16*)q,
+               (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, positions, token_seq, slots, page_table, max_pages,
+               block_list, list_cap, n_heads, n_kv, m_tiles, scale * 1.4426950408889634f, part_o, part_ml, n_splits);
     if (n_splits > 1)
         combine_splits_kernel<<<dim3(n_heads, n_tokens), D >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, (bf16*)out, n_heads,
                                                                                     n_kv, m_tiles, n_splits, D);

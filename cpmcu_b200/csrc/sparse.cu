@@ -26,6 +26,8 @@ __global__ void pool_keys_kernel(const T* __restrict__ k_cache, float* __restric
                                  const int* __restrict__ slots, const int* __restrict__ page_table, int max_pages,
                                  int n_kv, int d, int kernel, int stride) {
     const int t = blockIdx.x, kvh = blockIdx.y;
+    pdl_launch_dependents();
+    pdl_wait();
     const int first = positions[t] + 1 - kernel;
     if (first < 0 || first % stride != 0) return;
     const int* pages = page_table + (int64_t)slots[token_seq[t]] * max_pages;
@@ -51,8 +53,8 @@ CPM_API int cpm_pool_keys(const void* k_cache, float* pooled, const int* positio
     dim3 grid(n_tokens, n_kv);
     const int threads = d >= 128 ? 128 : 64;
     if (dtype == CPM_BF16)
-        pool_keys_kernel<bf16><<<grid, threads, 0, stream>>>((const bf16*)k_cache, pooled, positions, token_seq, slots,
-                                                             page_table, max_pages, n_kv, d, kernel, stride);
+        cpm_launch(kLaunchAttention, pool_keys_kernel<bf16>, grid, threads, 0, stream, (const bf16*)k_cache, pooled, positions,
+                   token_seq, slots, page_table, max_pages, n_kv, d, kernel, stride);
     else
         pool_keys_kernel<float><<<grid, threads, 0, stream>>>((const float*)k_cache, pooled, positions, token_seq,
                                                               slots, page_table, max_pages, n_kv, d, kernel, stride);
@@ -487,6 +489,8 @@ select_scores_kernel(const bf16* __restrict__ q, const float* __restrict__ poole
     __shared__ float stat_m[kSliceWarps][16], stat_l[kSliceWarps][16];
     const int slice = blockIdx.x, n_slices = gridDim.x, kvh = blockIdx.y, t = blockIdx.z, tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, j = lane & 3;
+    pdl_launch_dependents();
+    pdl_wait();
     const int p = positions[t];
     if (p + 1 <= dense_len) return;
     const int group = n_heads / n_kv;
@@ -581,6 +585,8 @@ select_finish_kernel(const float* __restrict__ raw, const float* __restrict__ st
     __shared__ float head_m[16], head_inv[16];
     const int t = blockIdx.x, kvh = blockIdx.y, tid = threadIdx.x;
     int* list = lists + ((int64_t)t * n_kv + kvh) * list_cap;
+    pdl_launch_dependents();
+    pdl_wait();
     const int p = positions[t];
     if (p + 1 <= dense_len) {
         if (tid == 0) list[0] = -2;
@@ -592,15 +598,36 @@ select_finish_kernel(const float* __restrict__ raw, const float* __restrict__ st
     const Selection sel = selection_of(p, kernel, stride, block_size, init_blocks, local_blocks, sort_cap);
     if (tid == 0 && p / block_size - local_blocks + 1 - init_blocks > sort_cap) g_select_overflow = 1;
     clear_selection(sel, keys, chosen);
-    if (tid < 16) {
-        const float* st = stats + unit * n_slices * 32 + tid * 2;
-        float mx = -INFINITY;
-        for (int s = 0; s < n_slices; ++s) mx = fmaxf(mx, st[s * 32]);
-        float sum = 0.f;
-        for (int s = 0; s < n_slices; ++s)
-            if (st[s * 32] != -INFINITY) sum += st[s * 32 + 1] * exp2f(st[s * 32] - mx);
-        head_m[tid] = mx;
-        head_inv[tid] = (tid < group && sum > 0.f) ? 1.f / sum : 0.f;       // rows beyond the group count for nothing
+    {
+        // The slices' statistics, merged by all threads: thread (head = tid % 16, lot = tid / 16) takes the slices
+        // lot, lot + 32, ... (sixteen threads walking them one after the other waited for one load at a time:
+        // 23 us at 74 slices), then sixteen threads merge the 32 lots.
+        __shared__ float lot_m[kFinishThreads / 16][16], lot_l[kFinishThreads / 16][16];
+        const int head = tid & 15, lot = tid >> 4;
+        const float* st = stats + unit * n_slices * 32 + head * 2;
+        float mx = -INFINITY, sum = 0.f;
+        for (int s = lot; s < n_slices; s += kFinishThreads / 16) {
+            const float m = st[s * 32], l = st[s * 32 + 1];
+            if (m != -INFINITY) {
+                const float mn = fmaxf(mx, m);
+                sum = sum * exp2f(mx - mn) + l * exp2f(m - mn);
+                mx = mn;
+            }
+        }
+        lot_m[lot][head] = mx;
+        lot_l[lot][head] = sum;
+        __syncthreads();
+        if (tid < 16) {
+            float all_m = -INFINITY;
+#pragma unroll
+            for (int i = 0; i < kFinishThreads / 16; ++i) all_m = fmaxf(all_m, lot_m[i][tid]);
+            float all_l = 0.f;
+#pragma unroll
+            for (int i = 0; i < kFinishThreads / 16; ++i)
+                if (lot_m[i][tid] != -INFINITY) all_l += lot_l[i][tid] * exp2f(lot_m[i][tid] - all_m);
+            head_m[tid] = all_m;
+            head_inv[tid] = (tid < group && all_l > 0.f) ? 1.f / all_l : 0.f;   // rows beyond the group count for nothing
+        }
     }
     __syncthreads();
     const float* my_raw = raw + unit * max_entries * 16;
@@ -662,16 +689,16 @@ static int launch_select_sliced(const void* q, const float* pooled, const int* p
     if (smem > 200 * 1024 || n_tokens > 65535) return CPM_BAD_ARGUMENT;
     float* raw = scratch;
     float* stats = scratch + (int64_t)n_tokens * n_kv * max_entries * 16;
-    select_scores_kernel<D><<<dim3(n_slices, n_kv, n_tokens), kSliceWarps * 32, 0, stream>>>(
-        (const bf16*)q, pooled, positions, token_seq, slots, page_table, max_pages, n_heads, n_kv,
-        scale * 1.4426950408889634f, kernel, stride, dense_len, max_entries, raw, stats);
+    cpm_launch(kLaunchAttention, select_scores_kernel<D>, dim3(n_slices, n_kv, n_tokens), kSliceWarps * 32, 0, stream,
+               (const bf16*)q, pooled, positions, token_seq, slots, page_table, max_pages, n_heads, n_kv,
+               scale * 1.4426950408889634f, kernel, stride, dense_len, max_entries, raw, stats);
     if (smem > 48 * 1024) {
         cudaError_t e = cudaFuncSetAttribute(select_finish_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return (int)e;
     }
-    select_finish_kernel<<<dim3(n_tokens, n_kv), kFinishThreads, smem, stream>>>(
-        raw, stats, n_slices, positions, lists, list_cap, n_heads, n_kv, kernel, stride, block_size, init_blocks, topk,
-        local_blocks, dense_len, max_entries, sort_cap);
+    cpm_launch(kLaunchAttention, select_finish_kernel, dim3(n_tokens, n_kv), kFinishThreads, smem, stream,
+               (const float*)raw, (const float*)stats, n_slices, positions, lists, list_cap, n_heads, n_kv, kernel, stride,
+               block_size, init_blocks, topk, local_blocks, dense_len, max_entries, sort_cap);
     return launch_status();
 }
 

@@ -173,6 +173,7 @@ class Ops:
     # it takes 51 us on the 8B gate_up shape (5.2 TB/s) with the activation applied in the epilogue, where the library
     # product takes 51 us and the activation kernel 4 us more.
     TCGEN05_MIN_ROWS = int(os.environ.get("CPMCU_TCGEN05_MIN_ROWS", "9"))
+    MAX_DECODE_SPLITS = int(os.environ.get("CPMCU_MAX_SPLITS", "16"))     # most shares a sequence's pages are cut into
     SELECT_SCRATCH_BYTES = 64 << 20     # most scratch the sliced block selection may take (raw scores of all pooled keys)
 
     def _skinny_ok(self, M: int, K: int) -> bool:
@@ -375,7 +376,7 @@ class Ops:
         block per SM (its page buffers fill the shared memory), so aim at one wave of blocks."""
         m_tiles = (n_heads // n_kv + 15) // 16
         units = max(1, n_seqs * n_kv * m_tiles)
-        return max(1, min(16, self.sm_count // units))
+        return max(1, min(self.MAX_DECODE_SPLITS, self.sm_count // units))
 
     def decode_attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, kv_len: torch.Tensor,
                          slots: torch.Tensor, page_table: torch.Tensor, n_kv: int, scale: float,
