@@ -381,7 +381,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
     auto issue = [&](int k) {           // the warp's k-th page into stage k % kDecodeStages
         const int p = p0 + warp + k * kDecodeWarps;
         if (p < p1) {
-            const int64_t base = (int64_t)pages[p] * page_elems + (int64_t)kvh * kPageTokens * D;
+            const int64_t base = (int64_t)CPM_PAGE(pages, p, max_pages) * page_elems + (int64_t)kvh * kPageTokens * D;
             copy_page_async<D>(my_stages + (k % kDecodeStages) * S::kStageBytes, k_cache + base, v_cache + base, lane);
         }
         cp_async_commit();
@@ -426,7 +426,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
             if (rope.qkv && rope.write_cache && p == n_pages - 1) {
                 // the step's own token is not in the cache yet: this warp holds its page and puts it there
                 const bf16* raw = rope.qkv + (int64_t)b * q_row_stride + (int64_t)(n_heads + kvh) * D;
-                const int64_t base = (int64_t)pages[p] * page_elems + (int64_t)kvh * kPageTokens * D;
+                const int64_t base = (int64_t)CPM_PAGE(pages, p, max_pages) * page_elems + (int64_t)kvh * kPageTokens * D;
                 put_new_token<D>(smem_raw + (warp * kDecodeStages + (k % kDecodeStages)) * S::kStageBytes, raw,
                                  raw + (int64_t)n_kv * D, rope.inv_freq, rope.magnitude, len - 1, (len - 1) % kPageTokens,
                                  rope.k_out + base, rope.v_out + base, mt == 0, lane);
@@ -623,7 +623,7 @@ listed_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
     auto block_of = [&](int k) { const int i = item0 + warp + k * kDecodeWarps; return dense ? i : list[i]; };
     auto issue = [&](int k) {
         if (item0 + warp + k * kDecodeWarps < n_items) {
-            const int64_t base = (int64_t)pages[block_of(k)] * page_elems + (int64_t)kvh * kPageTokens * D;
+            const int64_t base = (int64_t)CPM_PAGE(pages, block_of(k), max_pages) * page_elems + (int64_t)kvh * kPageTokens * D;
             copy_page_async<D>(my_stages + (k % kDecodeStages) * S::kStageBytes, k_cache + base, v_cache + base, lane);
         }
         cp_async_commit();
@@ -776,7 +776,7 @@ prefill_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_
 
     auto issue = [&](int p) {
         if (p <= last_page) {
-            const int64_t base = (int64_t)pages[p] * page_elems + (int64_t)kvh * kPageTokens * D;
+            const int64_t base = (int64_t)CPM_PAGE(pages, p, max_pages) * page_elems + (int64_t)kvh * kPageTokens * D;
             copy_page_async<D, kPrefillWarps * 32>(stages + (p & 1) * S::kStageBytes, k_cache + base, v_cache + base,
                                                    threadIdx.x);
         }
@@ -922,3 +922,5 @@ int cpm_decode_attention_bf16_static(const void* q, const void* k_cache, const v
     return cpm_decode_attention_bf16(q, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs,
                                      n_heads, n_kv, d, n_splits, scale, stream);
 }
+
+CPM_BOUNDS_TU(attention_bf16)

@@ -66,7 +66,7 @@ __global__ void attention_generic_kernel(
             const bool valid = j < seg_hi;
             float s = -INFINITY;
             if (valid) {
-                const int page = pages[j / kPageTokens];
+                const int page = CPM_PAGE(pages, j / kPageTokens, max_pages);
                 const T* krow = k_cache + page_row_offset(page, kvh, j % kPageTokens, n_kv, d);
                 float dot = 0.f;
                 for (int c = 0; c < d; ++c) dot = fmaf(qs[c], to_f32(krow[c]), dot);
@@ -83,7 +83,7 @@ __global__ void attention_generic_kernel(
             for (int jj = 0; jj < n_here; ++jj) {
                 const float pj = __shfl_sync(0xffffffffu, pr, jj);
                 const int key = j0 + jj;
-                const int page = pages[key / kPageTokens];
+                const int page = CPM_PAGE(pages, key / kPageTokens, max_pages);
                 const T* vcol = v_cache + value_offset(page, kvh, 0, key % kPageTokens, n_kv, d);
 #pragma unroll
                 for (int i = 0; i < kMaxDimsPerLane; ++i) {
@@ -123,3 +123,5 @@ CPM_API int cpm_attention_generic(const void* q, const void* k_cache, const void
             list_cap, block_size, window, n_heads, n_kv, d, scale);
     return launch_status();
 }
+
+CPM_BOUNDS_TU(attention_generic)

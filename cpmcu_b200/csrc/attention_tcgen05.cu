@@ -176,8 +176,8 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
             for (int j = 0; j < n_blocks && !aborted(); ++j, ++issued) {
                 const int s = j & 1, ph = (j >> 1) & 1;
                 // the second page of the last step may lie beyond the keys: its scores are masked, any page will do
-                const int pa = min(max(pages[2 * (j_first + j)], 0), n_pages - 1);
-                const int pb = min(max(pages[min(2 * (j_first + j) + 1, last_page)], 0), n_pages - 1);
+                const int pa = min(max(CPM_PAGE(pages, 2 * (j_first + j), max_pages), 0), n_pages - 1);
+                const int pb = min(max(CPM_PAGE(pages, min(2 * (j_first + j) + 1, last_page), max_pages), 0), n_pages - 1);
                 if (!mbar_wait_bounded(smem_u32(&k_empty[s]), ph ^ 1)) { fail(ERR_K_EMPTY); break; }
                 mbar_expect_tx(smem_u32(&k_full[s]), kTileBytes);
                 for (int half = 0; half < Z::kHalves; ++half) {
@@ -467,3 +467,5 @@ CPM_API int cpm_attention_tcgen05_error() {
     cudaMemcpyToSymbol(fa5::g_error, &zero, sizeof(int));
     return code;
 }
+
+CPM_BOUNDS_TU(attention_tcgen05)

@@ -100,6 +100,42 @@ __device__ __forceinline__ ArgMax block_argmax(ArgMax a, ArgMax* scratch /* 33 *
     return scratch[32];
 }
 
+// A build with -DCPM_CHECK_BOUNDS checks every page number a kernel takes from a page table (the logical index
+// against the table's width, the page against the number of pages the cache holds) before it is used as an
+// address: a bad one is recorded (the first per source file and run: what, index, value, limit), page 0 is used
+// in its place, and the host reads the record after the step (cpm_bounds_error_<file>).  It stands in for a
+// memory checker where none can be run; the ordinary build has none of it.
+#ifdef CPM_CHECK_BOUNDS
+static __device__ int g_bounds_record[4];               // code (0 = none), index, value, limit
+static __device__ int g_bounds_pages = 0x7fffffff;      // pages the cache in use holds (cpm_bounds_limit_<file>)
+__device__ __forceinline__ int cpm_checked_page(const int* pages, int idx, int max_pages) {
+    const bool idx_ok = idx >= 0 && idx < max_pages;
+    const int v = idx_ok ? pages[idx] : -1;
+    if (idx_ok && v >= 0 && v < g_bounds_pages) return v;
+    if (atomicCAS(&g_bounds_record[0], 0, idx_ok ? 2 : 1) == 0) {
+        g_bounds_record[1] = idx;
+        g_bounds_record[2] = v;
+        g_bounds_record[3] = idx_ok ? g_bounds_pages : max_pages;
+    }
+    return 0;
+}
+#define CPM_PAGE(pages, idx, max_pages) cpm_checked_page(pages, idx, max_pages)
+// The host side of one source file's record: read-and-clear, and the page limit.
+#define CPM_BOUNDS_TU(name)                                                                          \
+    CPM_API int cpm_bounds_error_##name(int* out4) {                                                 \
+        int zero[4] = {0, 0, 0, 0};                                                                  \
+        if (cudaMemcpyFromSymbol(out4, g_bounds_record, sizeof(zero)) != cudaSuccess) return -1;     \
+        if (out4[0]) cudaMemcpyToSymbol(g_bounds_record, zero, sizeof(zero));                        \
+        return out4[0];                                                                              \
+    }                                                                                                \
+    CPM_API int cpm_bounds_limit_##name(int n_pages) {                                               \
+        return cudaMemcpyToSymbol(g_bounds_pages, &n_pages, sizeof(int)) == cudaSuccess ? 0 : -1;    \
+    }
+#else
+#define CPM_PAGE(pages, idx, max_pages) ((pages)[idx])
+#define CPM_BOUNDS_TU(name)
+#endif
+
 // Address of the first element of (page, kv_head, token_in_page) in a cache lane.
 __device__ __forceinline__ int64_t page_row_offset(int page, int kv_head, int in_page, int n_kv, int d) {
     return (((int64_t)page * n_kv + kv_head) * kPageTokens + in_page) * (int64_t)d;

@@ -268,7 +268,7 @@ __global__ void rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_o
     int64_t k_base = 0, v_base = 0;
     if (k_cache) {
         const int slot = slots[token_seq[t]];
-        const int page = page_table[(int64_t)slot * max_pages + pos / kPageTokens];
+        const int page = CPM_PAGE(page_table + (int64_t)slot * max_pages, pos / kPageTokens, max_pages);
         k_base = page_row_offset(page, 0, pos % kPageTokens, n_kv, d);
         v_base = value_offset(page, 0, 0, pos % kPageTokens, n_kv, d);
     }
@@ -333,7 +333,7 @@ __global__ void rope_store_vec_kernel(const bf16* __restrict__ qkv, bf16* __rest
     int64_t k_base = 0, v_base = 0;
     if (k_cache && h_end > n_heads) {                            // only blocks with key or value heads look the page up
         const int slot = slots[token_seq[t]];
-        const int page = page_table[(int64_t)slot * max_pages + pos / kPageTokens];
+        const int page = CPM_PAGE(page_table + (int64_t)slot * max_pages, pos / kPageTokens, max_pages);
         k_base = page_row_offset(page, 0, pos % kPageTokens, n_kv, d);
         v_base = value_offset(page, 0, 0, pos % kPageTokens, n_kv, d);
     }
@@ -438,3 +438,5 @@ CPM_API int cpm_advance_decode(int* ids, int* positions, int* kv_len, int* step_
     cpm_launch(kLaunchOther, advance_decode_kernel, (n + 127) / 128, 128, 0, stream, ids, positions, kv_len, step_key, sampled, live, n);
     return launch_status();
 }
+
+CPM_BOUNDS_TU(elementwise)

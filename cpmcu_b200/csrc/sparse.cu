@@ -32,14 +32,14 @@ __global__ void pool_keys_kernel(const T* __restrict__ k_cache, float* __restric
     if (first < 0 || first % stride != 0) return;
     const int* pages = page_table + (int64_t)slots[token_seq[t]] * max_pages;
     const int per_page = kPageTokens / stride;
-    const int64_t dst = (((int64_t)pages[first / kPageTokens] * n_kv + kvh) * per_page
+    const int64_t dst = (((int64_t)CPM_PAGE(pages, first / kPageTokens, max_pages) * n_kv + kvh) * per_page
                          + (first % kPageTokens) / stride) * d;
     const float inv = 1.0f / (float)kernel;
     for (int c = threadIdx.x; c < d; c += blockDim.x) {
         float s = 0.f;
         for (int r = 0; r < kernel; ++r) {
             const int j = first + r;
-            s += to_f32(k_cache[page_row_offset(pages[j / kPageTokens], kvh, j % kPageTokens, n_kv, d) + c]);
+            s += to_f32(k_cache[page_row_offset(CPM_PAGE(pages, j / kPageTokens, max_pages), kvh, j % kPageTokens, n_kv, d) + c]);
         }
         pooled[dst + c] = s * inv;
     }
@@ -188,7 +188,7 @@ constexpr int kMaxGroup = 32;              // query heads per kv head this kerne
 __device__ __forceinline__ const float* pooled_row(const float* __restrict__ pooled, const int* __restrict__ pages,
                                                    int entry, int stride, int per_page, int n_kv, int kvh, int d) {
     const int tok = entry * stride;
-    return pooled + (((int64_t)pages[tok / kPageTokens] * n_kv + kvh) * per_page + (tok % kPageTokens) / stride) * d;
+    return pooled + (((int64_t)CPM_PAGE(pages, tok / kPageTokens, 0x7fffffff) * n_kv + kvh) * per_page + (tok % kPageTokens) / stride) * d;
 }
 
 // Dot products of one pooled key with every head of the group; every lane returns all of them
@@ -758,3 +758,5 @@ CPM_API int cpm_select_blocks(const void* q, const float* pooled, const int* pos
     }
     return launch_status();
 }
+
+CPM_BOUNDS_TU(sparse)

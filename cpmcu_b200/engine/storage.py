@@ -8,6 +8,7 @@ workspace is measured by running the model once on tensors without storage
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import List, Optional
 
@@ -85,8 +86,9 @@ def make_storage(model: Model, chunk_tokens: int, max_batch: int, max_tokens: Op
                                 f"memory_limit {memory_limit} of {total >> 20} MiB ({free >> 20} MiB free) leaves nothing")
     tokens, total_bytes = plan_storage(budget, w_bytes, persistent + 2 * frame, lambda t: sum(counted_cache(t)), max_tokens)
     st_bytes, pg_bytes = counted_cache(tokens)
-    total_bytes = w_bytes + persistent + 2 * frame + st_bytes + pg_bytes + 8 * ALIGN       # what the regions add up to
-    arena = Arena(total_bytes, device)
+    checked = os.environ.get("CPMCU_CHECK_BOUNDS", "0") not in ("", "0")       # guard words behind every region
+    total_bytes = w_bytes + persistent + 2 * frame + st_bytes + pg_bytes + 16 * ALIGN      # what the regions add up to
+    arena = Arena(total_bytes, device, guards=checked)
     if w_bytes:
         ops.weights = arena.carve("weights", w_bytes)
     workspace = Workspace(arena.carve("workspace", persistent), [arena.carve("frame0", frame), arena.carve("frame1", frame)],

@@ -76,8 +76,14 @@ class Region:
 
 
 class Arena:
-    def __init__(self, total_bytes: Optional[int], device: "torch.device | str | None"):
-        """``device`` None: a counting arena without memory (``total_bytes`` may be None = unbounded)."""
+    GUARD_BYTE = 0xA5
+
+    def __init__(self, total_bytes: Optional[int], device: "torch.device | str | None", guards: bool = False):
+        """``device`` None: a counting arena without memory (``total_bytes`` may be None = unbounded).
+        ``guards``: every region is followed by ALIGN bytes of a fixed pattern that nothing may write;
+        ``check_guards`` says which region was overrun (for checked runs; ``total_bytes`` must leave room for them)."""
+        self.guards = bool(guards)
+        self.guard_at: Dict[str, int] = {}
         self.total = None if total_bytes is None else int(total_bytes)
         self.device = None if device is None else torch.device(device)
         self.buffer: Optional[torch.Tensor] = None
@@ -108,8 +114,23 @@ class Arena:
                 raise PoolExhausted("arena", size, self.total, self.carved, f"carving region '{name}'")
             region = Region(self, name, self.carved, size)
             self.carved += size
+            if self.guards and self.buffer is not None:
+                if self.carved + ALIGN > self.total:
+                    raise PoolExhausted("arena", ALIGN, self.total, self.carved, f"the guard behind region '{name}'")
+                self.guard_at[name] = self.carved
+                self.buffer[self.carved:self.carved + ALIGN].fill_(self.GUARD_BYTE)
+                self.carved += ALIGN
         self.regions[name] = region
         return region
+
+    def check_guards(self) -> None:
+        """Raises if the bytes behind a region have been written (something ran over the region's end)."""
+        for name, at in self.guard_at.items():
+            g = self.buffer[at:at + ALIGN]
+            if not bool((g == self.GUARD_BYTE).all()):
+                first = int((g != self.GUARD_BYTE).nonzero()[0])
+                raise RuntimeError(f"memory arena: the guard behind region '{name}' was overwritten "
+                                   f"(first at byte {first} past the region's end)")
 
     def view(self, at: int, nbytes: int, shape: Tuple[int, ...], dtype: torch.dtype, zero: bool) -> torch.Tensor:
         if self.buffer is None:

@@ -50,9 +50,13 @@ def sources() -> List[str]:
     return sorted(f for f in os.listdir(CSRC_DIR) if f.endswith(".cu"))
 
 
-def _fingerprint() -> str:
+# The checked build: every page number taken from a page table is checked before use (csrc/common.cuh).
+BOUNDS_FLAG = "-DCPM_CHECK_BOUNDS"
+
+
+def _fingerprint(check_bounds: bool = False) -> str:
     h = hashlib.sha256()
-    h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(" ".join(NVCC_FLAGS + ([BOUNDS_FLAG] if check_bounds else [])).encode())
     for name in sorted(os.listdir(CSRC_DIR)):
         if name.endswith((".cu", ".cuh", ".h")):
             h.update(name.encode())
@@ -73,12 +77,13 @@ def _writable_dir(path: str) -> bool:
         return False
 
 
-def build_dirs() -> List[str]:
+def build_dirs(check_bounds: bool = False) -> List[str]:
+    sub = "_lib_checked" if check_bounds else "_lib"
     dirs = []
     if os.environ.get("CPMCU_BUILD_DIR"):
-        dirs.append(os.environ["CPMCU_BUILD_DIR"])
-    dirs.append(os.path.join(PACKAGE_DIR, "_lib"))
-    dirs.append(os.path.join(tempfile.gettempdir(), f"cpmcu_b200-{os.getuid()}", "_lib"))
+        dirs.append(os.path.join(os.environ["CPMCU_BUILD_DIR"], "checked") if check_bounds else os.environ["CPMCU_BUILD_DIR"])
+    dirs.append(os.path.join(PACKAGE_DIR, "_lib", "checked") if check_bounds else os.path.join(PACKAGE_DIR, "_lib"))
+    dirs.append(os.path.join(tempfile.gettempdir(), f"cpmcu_b200-{os.getuid()}", sub))
     return dirs
 
 
@@ -86,10 +91,10 @@ def _say(msg: str) -> None:
     print(f"[cpmcu_b200 build] {msg}", file=sys.stderr, flush=True)
 
 
-def existing_library() -> Optional[str]:
+def existing_library(check_bounds: bool = False) -> Optional[str]:
     """Path of an up-to-date library, or None."""
-    fp = _fingerprint()
-    for d in build_dirs():
+    fp = _fingerprint(check_bounds)
+    for d in build_dirs(check_bounds):
         lib, stamp = os.path.join(d, LIB_NAME), os.path.join(d, "fingerprint")
         try:
             if os.path.isfile(lib) and open(stamp).read().strip() == fp:
@@ -99,21 +104,23 @@ def existing_library() -> Optional[str]:
     return None
 
 
-def build(force: bool = False, verbose: bool = True) -> str:
-    """Returns the path of the shared library, compiling it if it is stale or absent."""
+def build(force: bool = False, verbose: bool = True, check_bounds: bool = False) -> str:
+    """Returns the path of the shared library, compiling it if it is stale or absent.  ``check_bounds``: the
+    checked build (a library of its own beside the ordinary one)."""
     if not force:
-        lib = existing_library()
+        lib = existing_library(check_bounds)
         if lib:
             return lib
     nvcc = find_nvcc()
-    out_dir = next((d for d in build_dirs() if _writable_dir(d)), None)
+    out_dir = next((d for d in build_dirs(check_bounds) if _writable_dir(d)), None)
     if out_dir is None:
-        raise BuildError(f"no writable folder to build in (tried {build_dirs()})")
+        raise BuildError(f"no writable folder to build in (tried {build_dirs(check_bounds)})")
+    flags = NVCC_FLAGS + ([BOUNDS_FLAG] if check_bounds else [])
     obj_dir = os.path.join(out_dir, "_build")
     os.makedirs(obj_dir, exist_ok=True)
     srcs = sources()
     if verbose:
-        _say(f"compiling {len(srcs)} CUDA sources for sm_100a into {out_dir}")
+        _say(f"compiling {len(srcs)} CUDA sources for sm_100a into {out_dir}" + (" (checked build)" if check_bounds else ""))
     t0 = time.time()
     done = threading.Event()
 
@@ -126,7 +133,7 @@ def build(force: bool = False, verbose: bool = True) -> str:
 
     def compile_one(name: str) -> str:
         obj = os.path.join(obj_dir, name[:-3] + ".o")
-        cmd = [nvcc, *NVCC_FLAGS, "-I", CSRC_DIR, "-c", os.path.join(CSRC_DIR, name), "-o", obj]
+        cmd = [nvcc, *flags, "-I", CSRC_DIR, "-c", os.path.join(CSRC_DIR, name), "-o", obj]
         p = subprocess.run(cmd, capture_output=True, text=True)
         if p.returncode != 0:
             raise BuildError(f"nvcc failed on {name}:\n{' '.join(cmd)}\n{p.stdout}\n{p.stderr}")
@@ -144,7 +151,7 @@ def build(force: bool = False, verbose: bool = True) -> str:
             raise BuildError(f"link failed:\n{' '.join(cmd)}\n{p.stdout}\n{p.stderr}")
         os.replace(tmp_lib, os.path.join(out_dir, LIB_NAME))
         with open(os.path.join(out_dir, "fingerprint"), "w") as f:
-            f.write(_fingerprint())
+            f.write(_fingerprint(check_bounds))
     finally:
         done.set()
     if verbose:
@@ -153,4 +160,4 @@ def build(force: bool = False, verbose: bool = True) -> str:
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv))
+    print(build(force="--force" in sys.argv, check_bounds="--check-bounds" in sys.argv))

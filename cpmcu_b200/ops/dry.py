@@ -66,6 +66,9 @@ class DryOps(Ops):
     def _f32(t, what):
         return t
 
+    def set_page_limit(self, n_pages):
+        pass
+
     def result(self, *shape, dtype=None):
         return torch.empty(*shape, dtype=dtype or self.dtype, device="meta")
 

@@ -51,6 +51,9 @@ _SIGNATURES = {
     "cpm_sample_rows": [_P, c_int64, c_int, c_int, _P, _P, _P, c_uint64, _P, _P, _P],
 }
 
+# source files whose kernels follow page tables; the checked build (CPMCU_CHECK_BOUNDS=1) keeps a record per file
+BOUNDS_FILES = ("attention_bf16", "attention_generic", "attention_tcgen05", "elementwise", "sparse")
+
 _lock = threading.Lock()
 _lib: Optional[ctypes.CDLL] = None
 _lib_path: Optional[str] = None
@@ -68,8 +71,9 @@ def load() -> ctypes.CDLL:
     with _lock:
         if _lib is not None:
             return _lib
+        checked = os.environ.get("CPMCU_CHECK_BOUNDS", "0") not in ("", "0")
         try:
-            path = _build.build()
+            path = _build.build(check_bounds=checked)
         except _build.BuildError as e:
             raise KernelLibraryError(f"the CUDA kernel library could not be built: {e}") from None
         try:
@@ -101,6 +105,13 @@ def load() -> ctypes.CDLL:
                 raise KernelLibraryError(f"{path} lacks the entry point {name}; rebuild it") from None
             fn.argtypes = argtypes
             fn.restype = c_int
+        lib.checked_files = []
+        if checked:
+            for tu in BOUNDS_FILES:
+                err, lim = getattr(lib, f"cpm_bounds_error_{tu}"), getattr(lib, f"cpm_bounds_limit_{tu}")
+                err.argtypes, err.restype = [ctypes.POINTER(c_int * 4)], c_int
+                lim.argtypes, lim.restype = [c_int], c_int
+                lib.checked_files.append((tu, err, lim))
         _lib, _lib_path = lib, path
         return lib
 

@@ -492,9 +492,32 @@ class Ops:
         if gemm or attn:
             raise RuntimeError(f"a tcgen05 kernel gave up waiting on a barrier (product: code {gemm}, attention: code "
                                f"{attn}); the results of this step are not valid")
+        self.raise_on_bounds_error()
+        arena = self.workspace.persistent.arena if self.workspace is not None else None
+        if arena is not None and arena.guards:
+            arena.check_guards()
         if int(self.lib.cpm_select_blocks_error()):
             raise RuntimeError("block selection met a query with more candidate key blocks than the launch made room "
                                "for (a sequence longer than the bound the step gave); the results of this step are not valid")
+
+    # ---- the checked build (CPMCU_CHECK_BOUNDS=1) ----
+    def set_page_limit(self, n_pages: int) -> None:
+        """Tells the checked kernels how many pages the cache in use holds (no-op in the ordinary build)."""
+        if (getattr(self.lib, "checked_files", None) and n_pages != getattr(self, "_page_limit", None)
+                and not torch.cuda.is_current_stream_capturing()):
+            for _, _, limit in self.lib.checked_files:
+                limit(int(n_pages))
+            self._page_limit = n_pages
+
+    def raise_on_bounds_error(self) -> None:
+        """The checked build's records: a page index or page number out of range that a kernel met (and did not
+        follow).  Synchronises."""
+        for name, error, _ in getattr(self.lib, "checked_files", None) or ():
+            rec = (ctypes.c_int * 4)()
+            if error(ctypes.byref(rec)):
+                what = "a page-table index beyond the table" if rec[0] == 1 else "a page number beyond the cache"
+                raise RuntimeError(f"checked build: a kernel of {name}.cu met {what}: index {rec[1]}, value {rec[2]}, "
+                                   f"limit {rec[3]}; it used page 0 instead, the step's results are not valid")
 
     def listed_attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, positions: torch.Tensor,
                          token_seq: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,

@@ -93,6 +93,8 @@ class GroupedQueryAttention(Mixer):
     # ---- forward ----
     def forward(self, ctx, y: torch.Tensor, lane, writes_cache: bool) -> torch.Tensor:
         ops = self.ops
+        if lane.k is not None:
+            ops.set_page_limit(lane.k.shape[0])          # the checked build's kernels compare page numbers with it
         qkv = ops.linear(y, self.w_qkv)
         inv_freq, magnitude, rot_dim = self.position.rotary() or (None, 1.0, -1)
         k_cache, v_cache = lane.k, lane.v

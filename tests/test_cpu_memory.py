@@ -121,3 +121,16 @@ def test_cache_inside_regions():
     with pytest.raises(PoolExhausted, match="region 'cache'.*key-value pages"):
         Cache(needs, max_tokens=64 * 64, dtype=torch.float32, device="cpu", n_slots=4,
               state_region=small.carve("state", 1 << 16), page_region=small.carve("cache", 1 << 18))
+
+
+def test_guard_words_show_which_region_was_overrun():
+    arena = Arena(64 * 1024, "cpu", guards=True)
+    a = arena.carve("frame0", 1024)
+    b = arena.carve("frame1", 1024)
+    assert b.offset == a.offset + a.size + ALIGN            # a guard lies between them
+    t = a.tensor((256,), torch.float32)
+    t.fill_(1.0)
+    arena.check_guards()
+    arena.buffer[a.offset + a.size + 3] = 0                 # one byte past frame0's end
+    with pytest.raises(RuntimeError, match="behind region 'frame0'.*byte 3"):
+        arena.check_guards()
