@@ -297,7 +297,11 @@ struct DecodeRope {
     int write_cache;
     bf16* k_out;
     bf16* v_out;
+    int early;            // ask for the first pages before waiting for the kernel ahead (cpm_set_decode_early)
 };
+
+static int g_decode_early = 1;
+CPM_API void cpm_set_decode_early(int on) { g_decode_early = on ? 1 : 0; }
 
 // x' = x cos - y sin, y' = x sin + y cos on the 8 bf16 pairs (x from ``lo``, y from ``hi``), cos and sin
 // of the 8 dimensions in cs[], sn[]; rounded to bf16 as the stand-alone rotary kernel does.
@@ -369,7 +373,9 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
     const int group = n_heads / n_kv;
     const int j = lane & 3, g = lane >> 2;
     pdl_launch_dependents();
-    pdl_wait();
+    // Lengths, slots, page numbers and every page but the sequence's last were written by earlier steps (or by the
+    // host before this one): they are read, and the first pages asked for, before this kernel waits for the
+    // one ahead of it, which writes only the step's own token (into the last page) and q.
     const int len = kv_len[b];
     const int n_pages = (len + kPageTokens - 1) / kPageTokens;
     const int per = (n_pages + n_splits - 1) / n_splits;
@@ -386,8 +392,17 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
         }
         cp_async_commit();
     };
-    issue(0);
-    issue(1);
+    // the warp whose first two pages include the last page waits first (its copies must stay in order)
+    const bool early = rope.early && p0 + warp != n_pages - 1 && p0 + warp + kDecodeWarps != n_pages - 1;
+    if (early) {
+        issue(0);
+        issue(1);
+    }
+    pdl_wait();
+    if (!early) {
+        issue(0);
+        issue(1);
+    }
 
     TileState<D> st;
     st.init();
@@ -527,12 +542,13 @@ template <int D>
 static int launch_decode(const void* q, const void* k_cache, const void* v_cache, void* out, const int* kv_len,
                          const int* slots, const int* page_table, int max_pages, float* scratch, int n_seqs,
                          int n_heads, int n_kv, int n_splits, float scale, cudaStream_t stream,
-                         DecodeRope rope = DecodeRope{nullptr, nullptr, 1.f, 0, nullptr, nullptr}) {
+                         DecodeRope rope = DecodeRope{nullptr, nullptr, 1.f, 0, nullptr, nullptr, 0}) {
     const int m_tiles = (n_heads / n_kv + 15) / 16;
     float* part_o = scratch;
     float* part_ml = scratch + (int64_t)n_seqs * n_kv * m_tiles * n_splits * 16 * D;
     dim3 grid(n_splits, n_kv * m_tiles, n_seqs);
     auto kern = decode_attention_kernel<D>;
+    rope.early = g_decode_early;
     constexpr int smem = DecodeSmem<D>::kTotal;
     static bool configured[kMaxDevices] = {};            // per kernel and per device
     if (int st = ensure_dynamic_smem(kern, smem, configured)) return st;
@@ -571,7 +587,7 @@ CPM_API int cpm_decode_attention_rope_bf16(const void* qkv, void* k_cache, void*
                                            cudaStream_t stream) {
     if (n_seqs <= 0) return CPM_OK;
     if (n_kv <= 0 || n_heads % n_kv || n_splits < 1 || n_seqs > 65535 || !scratch || !qkv) return CPM_BAD_ARGUMENT;
-    const DecodeRope rope{(const bf16*)qkv, inv_freq, magnitude, write_cache, (bf16*)k_cache, (bf16*)v_cache};
+    const DecodeRope rope{(const bf16*)qkv, inv_freq, magnitude, write_cache, (bf16*)k_cache, (bf16*)v_cache, 0};
     switch (d) {
         case 64: return launch_decode<64>(nullptr, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream, rope);
         case 128: return launch_decode<128>(nullptr, k_cache, v_cache, out, kv_len, slots, page_table, max_pages, scratch, n_seqs, n_heads, n_kv, n_splits, scale, stream, rope);

@@ -306,7 +306,8 @@ __global__ void rope_store_vec_kernel(const bf16* __restrict__ qkv, bf16* __rest
                                       int n_heads, int n_kv, int d, int heads_per_block) {
     extern __shared__ float cs_table[];       // cos[half], sin[half] of this token
     pdl_launch_dependents();
-    pdl_wait();
+    // Positions, slots and page tables were written before this step's kernels began; the angles and the page are
+    // worked out from them while the product ahead of this kernel is still finishing.  Only qkv needs the wait.
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int half = d >> 1;
@@ -328,7 +329,6 @@ __global__ void rope_store_vec_kernel(const bf16* __restrict__ qkv, bf16* __rest
         cs_table[c] = cs;
         cs_table[half + c] = sn;
     }
-    __syncthreads();
 
     int64_t k_base = 0, v_base = 0;
     if (k_cache && h_end > n_heads) {                            // only blocks with key or value heads look the page up
@@ -337,6 +337,8 @@ __global__ void rope_store_vec_kernel(const bf16* __restrict__ qkv, bf16* __rest
         k_base = page_row_offset(page, 0, pos % kPageTokens, n_kv, d);
         v_base = value_offset(page, 0, 0, pos % kPageTokens, n_kv, d);
     }
+    __syncthreads();
+    pdl_wait();
     const int per_head = d >> 4;                                 // items of 16 elements in a head
     const int items = (h_end - h_begin) * per_head;
     for (int item = threadIdx.x; item < items; item += blockDim.x) {

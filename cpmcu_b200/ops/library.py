@@ -88,6 +88,10 @@ def load() -> ctypes.CDLL:
         lib.cpm_set_skinny_prefetch_lines.restype = None
         if os.environ.get("CPMCU_SKINNY_PREFETCH"):
             lib.cpm_set_skinny_prefetch_lines(int(os.environ["CPMCU_SKINNY_PREFETCH"]))
+        lib.cpm_set_decode_early.argtypes = [c_int]
+        lib.cpm_set_decode_early.restype = None
+        if os.environ.get("CPMCU_DECODE_EARLY") is not None:      # 0: the decode attention waits before it reads anything
+            lib.cpm_set_decode_early(int(os.environ["CPMCU_DECODE_EARLY"]))
         lib.cpm_gemm_tcgen05_error.argtypes = []
         lib.cpm_gemm_tcgen05_error.restype = c_int
         lib.cpm_attention_tcgen05_error.argtypes = []
