@@ -23,10 +23,9 @@ from typing import Dict, List, Optional, Sequence
 
 import torch
 
-from ..parts.base import CacheNeeds
+from ..parts.base import PAGE_TOKENS, CacheNeeds
 from .allocator import CacheFull, FreeList, HandleError
 
-PAGE_TOKENS = 64
 RELEASED = -1          # entry of a sequence's page list whose page went back to the pool
 
 

@@ -441,4 +441,7 @@ CPM_API int cpm_advance_decode(int* ids, int* positions, int* kv_len, int* step_
     return launch_status();
 }
 
+// Tokens per cache page these kernels were built for (the Python side compares it with its own constant).
+CPM_API int cpm_page_tokens() { return kPageTokens; }
+
 CPM_BOUNDS_TU(elementwise)

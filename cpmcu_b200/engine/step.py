@@ -204,7 +204,7 @@ class Stepper:
                 n_tokens=n, n_seqs=1, is_decode=(n == 1), captured=True, q_lens=[n], kv_lens=[], slots=[], max_q_len=n,
                 max_kv_len=bound, token_ids=inputs[:n], positions=inputs[n:2 * n], token_seq=fixed[:n],
                 cu_q=fixed[n:n + 2], kv_len_dev=inputs[2 * n:2 * n + 1], slot_dev=inputs[2 * n + 1:2 * n + 2], cache=self.cache)
-            ctx.extras["q_tiles"] = (fixed[n + 2:n + 2 + n_tiles], fixed[n + 2 + n_tiles:], n_tiles)
+            ctx.q_tiles = (fixed[n + 2:n + 2 + n_tiles], fixed[n + 2 + n_tiles:], n_tiles)
             ctx.extras["step_begun"] = True
             return self.model.forward(ctx, inputs[2 * n + 2:] if n_want else None)
 
@@ -277,7 +277,7 @@ class Stepper:
             kv_len_dev=cut(n_seq), slot_dev=cut(n_seq), cache=self.cache,
         )
         rows = cut(len(want_rows)) if want_rows else None
-        ctx.extras["q_tiles"] = (cut(len(tile_seq)), cut(len(tile_row)), len(tile_seq))
+        ctx.q_tiles = (cut(len(tile_seq)), cut(len(tile_row)), len(tile_seq))
         ctx.extras["step_begun"] = True
         if self.taps is not None:
             ctx.extras["taps"] = self.taps

@@ -70,7 +70,7 @@ class Model:
         """Whether every part can run a prompt chunk without reading the batch on the host (see Part)."""
         parts = [self.embedding, self.final_norm, self.head]
         for b in self.blocks:
-            parts += [b, b.mixer, b.feed_forward, b.mixer_norm, b.feed_forward_norm]
+            parts += [p for p in (b, b.mixer, b.feed_forward, b.mixer_norm, b.feed_forward_norm) if p is not None]
         return all(bool(getattr(p, "recordable_prompt", False)) for p in parts)
 
     # ---- cache ----

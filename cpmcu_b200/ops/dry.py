@@ -87,7 +87,7 @@ def dry_context(n_tokens: int, n_seqs: int, max_kv_len: int, cache, decode: bool
         max_q_len=max(q_lens), max_kv_len=max_kv_len, token_ids=_meta(n_tokens), positions=_meta(n_tokens),
         token_seq=_meta(n_tokens), cu_q=_meta(n_seqs + 1), kv_len_dev=_meta(n_seqs), slot_dev=_meta(n_seqs), cache=cache)
     n_tiles = sum((n + PREFILL_TILE_ROWS - 1) // PREFILL_TILE_ROWS for n in q_lens)
-    ctx.extras["q_tiles"] = (_meta(n_tiles), _meta(n_tiles), n_tiles)
+    ctx.q_tiles = (_meta(n_tiles), _meta(n_tiles), n_tiles)
     ctx.extras["step_begun"] = True
     return ctx
 

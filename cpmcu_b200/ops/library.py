@@ -88,6 +88,9 @@ def load() -> ctypes.CDLL:
         lib.cpm_set_skinny_prefetch_lines.restype = None
         if os.environ.get("CPMCU_SKINNY_PREFETCH"):
             lib.cpm_set_skinny_prefetch_lines(int(os.environ["CPMCU_SKINNY_PREFETCH"]))
+        for name in ("cpm_page_tokens", "cpm_prefill_attention_tile_rows"):
+            getattr(lib, name).argtypes = []
+            getattr(lib, name).restype = c_int
         lib.cpm_set_decode_early.argtypes = [c_int]
         lib.cpm_set_decode_early.restype = None
         if os.environ.get("CPMCU_DECODE_EARLY") is not None:      # 0: the decode attention waits before it reads anything

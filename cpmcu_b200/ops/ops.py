@@ -21,10 +21,11 @@ import torch
 from . import library
 from .library import check
 
+from ..parts.base import PAGE_TOKENS, QUERY_TILE_TOKENS
+
 F32, BF16 = 0, 1
-PAGE_TOKENS = 64
 FAST_HEAD_DIMS = (32, 64, 96, 128)       # head sizes the tensor-core attention kernels are built for
-PREFILL_TILE_ROWS = 64                   # query tokens per block of the prefill attention kernel
+PREFILL_TILE_ROWS = QUERY_TILE_TOKENS    # query tokens per block of the prefill attention kernel
 
 
 def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
@@ -54,6 +55,8 @@ class Ops:
         if not torch.cuda.is_available():
             raise library.KernelLibraryError("no CUDA device is available; there is no CPU path")
         self.lib = library.load()
+        if int(self.lib.cpm_page_tokens()) != PAGE_TOKENS or int(self.lib.cpm_prefill_attention_tile_rows()) != PREFILL_TILE_ROWS:
+            raise library.KernelLibraryError("the kernel library was built for another page or query-tile size than the package")
         self.element_size = 4 if dtype == torch.float32 else 2
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.use_tcgen05 = os.environ.get("CPMCU_TCGEN05", "1") != "0"
@@ -314,7 +317,7 @@ class Ops:
             if ctx.is_decode:
                 return self.decode_attention(q, lane.k, lane.v, ctx.kv_len_dev, ctx.slot_dev, lane.page_table,
                                              n_kv, scale)
-            tiles = ctx.extras.get("q_tiles")
+            tiles = ctx.q_tiles
             if (tiles is not None and self.use_tcgen05_attention and (n_heads // n_kv) % 2 == 0
                     and (d == 128 or (d == 64 and ctx.max_kv_len >= 1024))):      # short prompts of head size 64: the smaller tiles win
                 return self.prefill_attention_tcgen05(q, lane.k, lane.v, tiles, ctx.cu_q, ctx.kv_len_dev, ctx.slot_dev,

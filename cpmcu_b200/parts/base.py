@@ -20,6 +20,12 @@ import torch
 
 T = TypeVar("T")
 
+# Tokens per page of the key-value cache.  The one Python-side definition (cache and kernel wrappers import it); the
+# kernels' own constant (csrc/common.cuh) is compared with it when the library is loaded.
+PAGE_TOKENS = 64
+# Query tokens per tile of the tiled prompt attention kernels (StepContext.q_tiles is made for this size).
+QUERY_TILE_TOKENS = 64
+
 
 class Registry(Generic[T]):
     """A table from a name to a class, with an error that lists what is known."""
@@ -70,13 +76,14 @@ class LayerSpec:
 
     ``prefix`` is the layer's part of the tensor names ("model.layers.3."); the
     names below it are given by ``names``: sub-part -> infix ("self_attn." ...).
+    ``feed_forward`` and ``feed_forward_norm`` may be None: a layer of a mixer alone.
     """
 
     block: PartSpec
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]
     mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward_norm: Optional[PartSpec]
     prefix: str
     names: Mapping[str, str]
 
@@ -264,8 +271,8 @@ class ResidualStream:
 class Block(Part):
     """An arrangement of a mixer, a feed-forward and norms around the residual stream."""
 
-    def __init__(self, ops, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm,
-                 feed_forward_norm: Norm, names: Mapping[str, str]):
+    def __init__(self, ops, mixer: Mixer, feed_forward: Optional[FeedForward], mixer_norm: Norm,
+                 feed_forward_norm: Optional[Norm], names: Mapping[str, str]):
         super().__init__(ops)
         self.mixer = mixer
         self.feed_forward = feed_forward
@@ -274,12 +281,13 @@ class Block(Part):
         self.names = dict(names)
 
     def sub_parts(self) -> List[Tuple[str, Part]]:
-        return [
+        parts = [
             (self.names.get("mixer_norm", "mixer_norm."), self.mixer_norm),
             (self.names.get("mixer", "mixer."), self.mixer),
             (self.names.get("feed_forward_norm", "feed_forward_norm."), self.feed_forward_norm),
             (self.names.get("feed_forward", "feed_forward."), self.feed_forward),
         ]
+        return [(infix, part) for infix, part in parts if part is not None]      # a layer may have no feed-forward
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         out: Dict[str, WeightSpec] = {}
@@ -320,9 +328,9 @@ def build_block(spec: LayerSpec, ops) -> Block:
     return cls(
         ops,
         mixer=build_part(MIXERS, spec.mixer, ops),
-        feed_forward=build_part(FEED_FORWARDS, spec.feed_forward, ops),
+        feed_forward=build_part(FEED_FORWARDS, spec.feed_forward, ops) if spec.feed_forward is not None else None,
         mixer_norm=build_part(NORMS, spec.mixer_norm, ops),
-        feed_forward_norm=build_part(NORMS, spec.feed_forward_norm, ops),
+        feed_forward_norm=build_part(NORMS, spec.feed_forward_norm, ops) if spec.feed_forward_norm is not None else None,
         names=spec.names,
         **dict(spec.block.params),
     )
@@ -373,4 +381,9 @@ class StepContext:
     slot_dev: torch.Tensor               # [seqs]
     cache: Any = None                    # cpmcu_b200.cache.Cache
     workspace: Any = None                # per-engine scratch tensors by name
+    # Query tiles for mixers that work on tiles of QUERY_TILE_TOKENS consecutive tokens of one sequence (the tiled
+    # prompt attention): (tile -> sequence index int32 [tiles], tile -> first token inside the sequence's tokens of
+    # this step int32 [tiles], number of tiles); None when the step's maker gives none (a mixer then falls back to
+    # a kernel that needs no tiles).
+    q_tiles: Optional[Tuple[torch.Tensor, torch.Tensor, int]] = None
     extras: Dict[str, Any] = field(default_factory=dict)

@@ -24,6 +24,8 @@ class PreNormResidualBlock(Block):
         y = stream.normed(self.mixer_norm)
         a = self.mixer.forward(ctx, y, lane, writes_cache)
         stream.add(a, self.residual_scale)
+        if self.feed_forward is None:
+            return                                   # a layer of a mixer alone
         y2 = stream.normed(self.feed_forward_norm)
         f = self.feed_forward.forward(ctx, y2)
         stream.add(f, self.residual_scale)

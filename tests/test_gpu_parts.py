@@ -532,3 +532,50 @@ def test_routed_feed_forward_and_another_position_encoding(dtype):
         assert upto == len(seqs[i]) or dtype == "bfloat16"
         if upto:
             assert _err(g_all[:upto], want[:upto]) < TOL[dtype], i
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_layer_of_a_mixer_alone(dtype):
+    """A layer needs no feed-forward: layer 0 is attention only (no feed-forward, no second norm, no tensors for
+    them), layer 1 a whole layer; prompt in chunks, then token by token, against a plain computation."""
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.engine import SequenceStep, Stepper
+    from cpmcu_b200.models.model import Model
+    from cpmcu_b200.parts import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from cpmcu_b200.weights import random_tensors
+
+    c = TOY
+    norm = PartSpec("rms_norm", {"hidden_size": c["hidden"], "eps": c["eps"]})
+    attn = PartSpec("gqa_attention", {"hidden_size": c["hidden"], "n_heads": c["heads"], "n_kv_heads": c["kv"],
+                                      "head_dim": c["d"], "position": PartSpec("rope", {"head_dim": c["d"], "theta": 10000.0})})
+    ffn = PartSpec("gated_ffn", {"hidden_size": c["hidden"], "intermediate_size": c["inter"]})
+    block = PartSpec("pre_norm_residual", {"residual_scale": c["rs"]})
+    names = {"mixer_norm": "n1.", "mixer": "mix.", "feed_forward_norm": "n2.", "feed_forward": "ff."}
+    layers = [LayerSpec(block, attn, None, norm, None, "L0.", names), LayerSpec(block, attn, ffn, norm, norm, "L1.", names)]
+    spec = ModelSpec("MixerOnly", c["hidden"], c["vocab"],
+                     PartSpec("scaled_embedding", {"vocab_size": c["vocab"], "hidden_size": c["hidden"], "scale": 3.0}),
+                     layers, [ScheduleEntry(0, 0), ScheduleEntry(1, 1)], norm,
+                     PartSpec("scaled_lm_head", {"vocab_size": c["vocab"], "hidden_size": c["hidden"], "scale": 0.5}),
+                     embedding_name="emb.", final_norm_name="fn.", head_name="head.")
+    model = Model(spec, _ops(dtype))
+    assert not any(n.startswith("L0.ff.") or n.startswith("L0.n2.") for n in model.weight_specs())
+    w = random_tensors(model.weight_specs(), 9, DT[dtype], std=0.1)
+    model.load_weights({k: v.cuda() for k, v in w.items()})
+    st = Stepper(model, Cache(model.cache_needs(), max_tokens=64 * 4, dtype=DT[dtype], device="cuda:0"), chunk_tokens=16)
+    ids = helpers.random_ids(c["vocab"], 45, 4)
+    wf = {k: v.float().cpu() for k, v in w.items()}
+    cfg = {"num_attention_heads": c["heads"], "num_key_value_heads": c["kv"], "head_dim": c["d"], "hidden_size": c["hidden"],
+           "rope_theta": 10000.0, "max_position_embeddings": 4096}
+    x = plain.embed(ids, wf["emb.weight"], 3.0)
+    for layer in (0, 1):
+        p = f"L{layer}."
+        a, _ = plain.attention_layer(plain.rms_norm(x, wf[p + "n1.weight"], c["eps"]), wf, p + "mix.", cfg, torch.arange(len(ids)))
+        x = x + c["rs"] * a
+        if layer == 1:
+            y = plain.rms_norm(x, wf[p + "n2.weight"], c["eps"])
+            x = x + c["rs"] * plain.gated_ffn(y, {"f." + n: wf[p + "ff." + n] for n in ("gate_proj.weight", "up_proj.weight", "down_proj.weight")}, "f.")
+    want = plain.lm_head(plain.rms_norm(x, wf["fn.weight"], c["eps"]), {"lm_head.weight": wf["head.weight"]}, {}, 0.5)
+    slot = st.open(1)[0]
+    got = [st.step([SequenceStep(slot, ids[:40], list(range(40)))])]
+    got += [st.step([SequenceStep(slot, ids[i:i + 1], [0])]) for i in range(40, 45)]
+    assert _err(torch.cat(got), want) < TOL[dtype]
