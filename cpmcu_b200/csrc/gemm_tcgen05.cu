@@ -29,6 +29,17 @@ constexpr int kABytes = kBlockM * kBlockK * 2;                  // 16 KiB
 constexpr int kBBytes = kBlockN * kBlockK * 2;                  // 32 KiB
 constexpr int kStageBytes = kABytes + kBBytes;
 constexpr int kSmemBytes = kStages * kStageBytes + 1024 + 4 * 4096;   // + room to align the stages to 1 KiB, + the epilogue warps' staging
+// The single-block kernel also comes with tiles of 224 weight rows: with few rows of A (a decode batch: one row
+// tile) the tiles are all there is to share out, and 32,768 weight rows are 128 tiles of 256 (20 of 148 SMs idle)
+// but 147 tiles of 224.  The second accumulator always starts at TMEM column 256.
+constexpr int kNarrowN = 224;
+template <int BN> struct TileN {
+    static constexpr int kB = BN * kBlockK * 2;
+    static constexpr int kStage = kABytes + kB;
+    static constexpr int kSmem = kStages * kStage + 1024 + 4 * 4096;
+    static constexpr uint32_t kDesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                                      ((uint32_t)(kBlockM >> 4) << 24);
+};
 constexpr int kThreads = 192;                                   // 6 warps
 constexpr int kTmemCols = 512;
 constexpr int kBandTiles = 16;                                  // 2048 rows of A are shared by the blocks that run together
@@ -62,19 +73,22 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int tiles_m, int tiles
 // 128 x 256 kernel 12 % of its time.)  The staging rows are 128 bytes, their 16-byte chunks XOR-swizzled
 // by the row, which keeps both the writes (one row per lane) and the reads (eight lanes per row) free of
 // bank conflicts.  taddr: TMEM address of the warp's lanes and the tile's first column.
-template <int EPI>
+template <int EPI, int BN = kBlockN>
 __device__ __forceinline__ void epilogue_tile(bf16* __restrict__ out, uint32_t taddr, unsigned char* staging, int row0, int n0,
                                               int M, int N, int lane) {
     constexpr int kLoadsPerPass = EPI == EPI_SILU ? 4 : 2;          // 32 accumulator columns each; a pass is 64 outputs
-    constexpr int kPasses = kBlockN / (32 * kLoadsPerPass);
+    constexpr int kLoads = BN / 32;                                 // the tile's accumulator columns, 32 at a time
+    constexpr int kPasses = (kLoads + kLoadsPerPass - 1) / kLoadsPerPass;     // the last pass may be a part of one
     const int ldo = EPI == EPI_SILU ? N >> 1 : N;
     const int oc_tile = EPI == EPI_SILU ? n0 >> 1 : n0;
     uint4* my_row = reinterpret_cast<uint4*>(staging + lane * 128);
 #pragma unroll 1
     for (int p = 0; p < kPasses; ++p) {
         if (oc_tile + p * 64 >= ldo) break;
+        const int loads_here = min(kLoadsPerPass, kLoads - p * kLoadsPerPass);
 #pragma unroll
         for (int h = 0; h < kLoadsPerPass; ++h) {
+            if (h >= loads_here) break;                              // warp-uniform
             uint32_t v[32];
             tmem_load_32cols(taddr + (p * kLoadsPerPass + h) * 32, v);
             tmem_load_wait();
@@ -109,20 +123,25 @@ __device__ __forceinline__ void epilogue_tile(bf16* __restrict__ out, uint32_t t
         }
         __syncwarp();
         const int j = lane & 7, col = oc_tile + p * 64 + j * 8;
+        const bool chunk_valid = j < loads_here * (8 / kLoadsPerPass);       // 16-byte chunks this pass has filled
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
             const int r = 4 * i + (lane >> 3);
             const uint4 val = *reinterpret_cast<const uint4*>(staging + r * 128 + ((j ^ (r & 7)) << 4));
-            if (row0 + r < M && col < ldo) *reinterpret_cast<uint4*>(out + (int64_t)(row0 + r) * ldo + col) = val;
+            if (chunk_valid && row0 + r < M && col < ldo) *reinterpret_cast<uint4*>(out + (int64_t)(row0 + r) * ldo + col) = val;
         }
         __syncwarp();
     }
 }
 
-template <int EPI>
+template <int EPI, int BN = kBlockN>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     bf16* __restrict__ out, int M, int N, int K) {
+    constexpr int kBlockN = BN;                                    // this instantiation's tile width
+    constexpr int kStageBytes = TileN<BN>::kStage;
+    constexpr uint32_t kInstrDesc = TileN<BN>::kDesc;
+    constexpr int kAccStride = 256;                                // TMEM columns between the two accumulators
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[kStages], empty_bar[kStages], acc_full_bar[2], acc_empty_bar[2];
     __shared__ uint32_t tmem_base_slot;
@@ -165,20 +184,45 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         // ---- TMA producer (one elected lane) ----
         if (lane == 0) {
             uint32_t it = 0;
+            // Under programmatic dependent launch this kernel may start while the one ahead of it still runs.
+            // Weights are written by no kernel: the first stages' weight tiles are asked for at once, the
+            // activations' tiles (which the kernel ahead writes) after the wait.  Nothing is written to global
+            // memory before the wait either: the epilogue runs on accumulators that need the activations.
+            int early = 0;
+            if (blockIdx.x < n_tiles) {
+                const TileCoord tc0 = tile_coord(blockIdx.x, tiles_m, tiles_n, kBandTiles);
+                early = min(kStages, k_blocks);
+                for (int kb = 0; kb < early; ++kb) {
+                    const uint32_t bar = smem_u32(&full_bar[kb]);
+                    mbar_expect_tx(bar, kStageBytes);
+                    tma_load_2d(stages + kb * kStageBytes + kABytes, &map_w, bar, kb * kBlockK, tc0.n * kBlockN);
+                }
+            }
+            pdl_wait();
             for (int tile = blockIdx.x; tile < n_tiles && !*(volatile int*)&abort_flag; tile += gridDim.x) {
                 const TileCoord tc = tile_coord(tile, tiles_m, tiles_n, kBandTiles);
                 const int m0 = tc.m * kBlockM, n0 = tc.n * kBlockN;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % kStages;
-                    if (!mbar_wait_bounded(smem_u32(&empty_bar[s]), ((it / kStages) & 1) ^ 1)) { fail(ERR_EMPTY_WAIT); break; }
                     const uint32_t bar = smem_u32(&full_bar[s]);
+                    if ((int)it < early) {                               // its weight tile is on its way already
+                        tma_load_2d(stages + s * kStageBytes, &map_a, bar, kb * kBlockK, m0);
+                        continue;
+                    }
+                    if (!mbar_wait_bounded(smem_u32(&empty_bar[s]), ((it / kStages) & 1) ^ 1)) { fail(ERR_EMPTY_WAIT); break; }
                     mbar_expect_tx(bar, kStageBytes);
                     tma_load_2d(stages + s * kStageBytes, &map_a, bar, kb * kBlockK, m0);
                     tma_load_2d(stages + s * kStageBytes + kABytes, &map_w, bar, kb * kBlockK, n0);
                 }
             }
             if (*(volatile int*)&abort_flag) {
-                // copies that were asked for must land before the block gives up its shared memory
+                // copies that were asked for must land before the block gives up its shared memory; stages whose
+                // weight tile was asked for early still lack their activations' tile: ask for it, so that they complete
+                if ((int)it < early) {
+                    const TileCoord tc0 = tile_coord(blockIdx.x, tiles_m, tiles_n, kBandTiles);
+                    for (; (int)it < early; ++it)
+                        tma_load_2d(stages + it * kStageBytes, &map_a, smem_u32(&full_bar[it]), it * kBlockK, tc0.m * kBlockM);
+                }
                 const uint32_t first = it > (uint32_t)kStages ? it - kStages : 0;
                 for (uint32_t j = first; j < it; ++j)
                     mbar_wait_bounded(smem_u32(&full_bar[j % kStages]), (j / kStages) & 1);
@@ -192,7 +236,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 const int acc = local_tile & 1;
                 if (!mbar_wait_bounded(smem_u32(&acc_empty_bar[acc]), ((local_tile >> 1) & 1) ^ 1)) { fail(ERR_ACC_EMPTY_WAIT); break; }
                 tcgen05_fence_after();
-                const uint32_t tmem_d = tmem_base + acc * kBlockN;
+                const uint32_t tmem_d = tmem_base + acc * kAccStride;
                 bool ok = true;
                 for (int kb = 0; kb < k_blocks; ++kb, ++it) {
                     const int s = it % kStages;
@@ -219,8 +263,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             const int acc = local_tile & 1;
             if (!mbar_wait_bounded(smem_u32(&acc_full_bar[acc]), (local_tile >> 1) & 1)) { fail(ERR_ACC_FULL_WAIT); break; }
             tcgen05_fence_after();
-            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kBlockN;
-            epilogue_tile<EPI>(out, taddr, staging + quarter * 4096, m0 + quarter * 32, n0, M, N, lane);
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + acc * kAccStride;
+            epilogue_tile<EPI, BN>(out, taddr, staging + quarter * 4096, m0 + quarter * 32, n0, M, N, lane);
             tcgen05_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(smem_u32(&acc_empty_bar[acc]));
@@ -404,16 +448,30 @@ static bool make_map(CUtensorMap* map, const void* base, int rows, int K, int bo
     return make_map_2d_bf16(map, base, (uint64_t)rows, (uint64_t)K, (uint64_t)K * 2, kBlockK, box_rows);
 }
 
+template <int EPI, int BN>
+static int launch_tiles(const void* A, const void* W, void* out, int M, int N, int K, int n_blocks, cudaStream_t stream) {
+    CUtensorMap map_a, map_w;
+    if (!make_map(&map_a, A, M, K, kBlockM) || !make_map(&map_w, W, N, K, BN)) return CPM_BAD_ARGUMENT;
+    auto kern = gemm_tcgen05_kernel<EPI, BN>;
+    static bool configured[kMaxDevices] = {};            // per kernel and per device
+    if (int st = ensure_dynamic_smem(kern, TileN<BN>::kSmem, configured)) return st;
+    const int tiles = ((M + kBlockM - 1) / kBlockM) * ((N + BN - 1) / BN);
+    cpm_launch(kLaunchProduct, kern, dim3(tiles < n_blocks ? tiles : n_blocks), dim3(kThreads), (size_t)TileN<BN>::kSmem, stream,
+               map_a, map_w, (bf16*)out, M, N, K);
+    return launch_status();
+}
+
+static int g_narrow_tiles = 1;       // cpm_set_tcgen05_narrow: 0 keeps every product on 256-row tiles
+
 template <int EPI>
 static int launch(const void* A, const void* W, void* out, int M, int N, int K, int n_blocks, cudaStream_t stream) {
-    CUtensorMap map_a, map_w;
-    if (!make_map(&map_a, A, M, K, kBlockM) || !make_map(&map_w, W, N, K, kBlockN)) return CPM_BAD_ARGUMENT;
-    auto kern = gemm_tcgen05_kernel<EPI>;
-    static bool configured[kMaxDevices] = {};            // per kernel and per device
-    if (int st = ensure_dynamic_smem(kern, kSmemBytes, configured)) return st;
-    const int tiles = ((M + kBlockM - 1) / kBlockM) * ((N + kBlockN - 1) / kBlockN);
-    kern<<<tiles < n_blocks ? tiles : n_blocks, kThreads, kSmemBytes, stream>>>(map_a, map_w, (bf16*)out, M, N, K);
-    return launch_status();
+    // One row tile of A (a decode batch): the weight tiles are all the work there is to share out; take the
+    // narrower tiles where they need fewer rounds of the blocks times their width.
+    if (g_narrow_tiles && M <= kBlockM) {
+        auto cost = [&](int bn) { const int t = (N + bn - 1) / bn; return (int64_t)((t + n_blocks - 1) / n_blocks) * bn; };
+        if (cost(kNarrowN) < cost(kBlockN)) return launch_tiles<EPI, kNarrowN>(A, W, out, M, N, K, n_blocks, stream);
+    }
+    return launch_tiles<EPI, kBlockN>(A, W, out, M, N, K, n_blocks, stream);
 }
 
 // The pair kernel: clusters of two blocks, n_blocks rounded down to an even number.
@@ -463,6 +521,8 @@ CPM_API int cpm_gemm_bf16_tcgen05_pair(const void* A, const void* W, void* out, 
 
 // A [M,K], W [N,K] bf16 row-major (16-byte aligned, K a multiple of 64); out [M,N] bf16, or [M,N/2] for the
 // gated epilogue (N a multiple of 32, W rows interleaved in blocks of 8).  n_blocks: blocks to launch (one per SM).
+CPM_API void cpm_set_tcgen05_narrow(int on) { tc5::g_narrow_tiles = on ? 1 : 0; }
+
 CPM_API int cpm_gemm_bf16_tcgen05(const void* A, const void* W, void* out, int M, int N, int K, int epilogue,
                                   int n_blocks, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return CPM_OK;

@@ -91,6 +91,10 @@ def load() -> ctypes.CDLL:
         for name in ("cpm_page_tokens", "cpm_prefill_attention_tile_rows"):
             getattr(lib, name).argtypes = []
             getattr(lib, name).restype = c_int
+        lib.cpm_set_tcgen05_narrow.argtypes = [c_int]
+        lib.cpm_set_tcgen05_narrow.restype = None
+        if os.environ.get("CPMCU_TCGEN05_NARROW") is not None:    # 0: every tcgen05 product on 256-row tiles
+            lib.cpm_set_tcgen05_narrow(int(os.environ["CPMCU_TCGEN05_NARROW"]))
         lib.cpm_set_decode_early.argtypes = [c_int]
         lib.cpm_set_decode_early.restype = None
         if os.environ.get("CPMCU_DECODE_EARLY") is not None:      # 0: the decode attention waits before it reads anything
