@@ -65,17 +65,16 @@ CPM_API int cpm_pool_keys(const void* k_cache, float* pooled, const int* positio
 // maximum over the pooled keys that overlap the block; the leading blocks and the blocks of the
 // local window are always taken; of the others the topk - init_blocks best are chosen (ties to
 // the lower index).  Nothing here is sized by the number of pooled keys: every pooled key's score
-// goes straight into the sort keys of the blocks it overlaps (note_score, an atomic maximum in
+// goes straight into the keys of the blocks it overlaps (note_score, an atomic maximum in
 // shared memory), so the shared arrays grow with the number of candidate blocks only.
 //
-// A sort key is the score's bits made monotonic, then the inverted candidate index, so that a
-// descending sort puts the higher score first and among equal scores the lower index; 0 is below
-// every real key and stands for "no pooled key overlaps this block".
+// A block's key is the score's bits made monotonic, then the inverted candidate index, so that
+// the larger key has the higher score and among equal scores the lower index; 0 is below every
+// real key and stands for "no pooled key overlaps this block".
 struct Selection {
     int qb;             // block of the query
     int last_choice;    // last block that can be chosen (those after it are the local window)
     int n_cand;         // candidates: blocks init_blocks .. last_choice
-    int n_sort;         // power of two >= n_cand
     int per_block;      // pooled keys that start inside one block
     int reach_back;     // pooled keys before a block's first that still overlap it
 };
@@ -88,15 +87,13 @@ __device__ __forceinline__ Selection selection_of(int p, int kernel, int stride,
     s.per_block = block_size / stride;
     s.reach_back = kernel / stride - 1;
     s.n_cand = min(max(0, s.last_choice + 1 - init_blocks), sort_cap);
-    s.n_sort = 1;
-    while (s.n_sort < s.n_cand) s.n_sort <<= 1;
     return s;
 }
 
-// Clears the sort keys and the chosen bits; all threads call it, a barrier must follow.
+// Clears the candidates' keys and the chosen bits; all threads call it, a barrier must follow.
 __device__ __forceinline__ void clear_selection(const Selection& s, unsigned long long* __restrict__ keys,
                                                 unsigned* __restrict__ chosen) {
-    for (int i = threadIdx.x; i < s.n_sort; i += blockDim.x) keys[i] = 0ull;
+    for (int i = threadIdx.x; i < s.n_cand; i += blockDim.x) keys[i] = 0ull;
     for (int i = threadIdx.x; i < (s.n_cand + 31) / 32; i += blockDim.x) chosen[i] = 0u;
 }
 
@@ -112,54 +109,99 @@ __device__ __forceinline__ void note_score(const Selection& s, unsigned long lon
     }
 }
 
-// keys: [n_sort] filled by note_score; chosen: [(n_cand + 31) / 32] cleared.  All threads call this
-// after a barrier that follows the last note_score.
-__device__ void finish_selection(const Selection& s, unsigned long long* __restrict__ keys, unsigned* __restrict__ chosen,
+// The ``rank``-th largest (1 <= rank <= n) of keys[0..n): eight passes over the keys' bytes from the top one down.
+// Each pass counts, in 256 bins, the next byte of the keys that agree with the bytes found so far, and one warp
+// walks the bins from the high end to the one that holds the rank.  All threads call it (at least one warp) and
+// all get the value; the keys stay as they are.  The selection needs the set of the best keys, not their order,
+// so this stands where a sort would: 8 short passes whatever the count, against 45 barriers for 512 keys.
+__device__ unsigned long long kth_largest(const unsigned long long* __restrict__ keys, int n, int rank) {
+    __shared__ unsigned bins[256];
+    __shared__ unsigned long long found;
+    __shared__ int rank_left;
+    const int tid = threadIdx.x, n_threads = blockDim.x, lane = tid & 31;
+    if (tid == 0) {
+        found = 0ull;
+        rank_left = rank;
+    }
+    unsigned long long prefix = 0ull, mask = 0ull;
+    for (int shift = 56; shift >= 0; shift -= 8) {
+        for (int i = tid; i < 256; i += n_threads) bins[i] = 0u;
+        __syncthreads();
+        for (int i = tid; i < n; i += n_threads) {
+            const unsigned long long k = keys[i];
+            if ((k & mask) == prefix) atomicAdd(&bins[(unsigned)(k >> shift) & 255u], 1u);
+        }
+        __syncthreads();
+        if (tid < 32) {                                   // lane L owns bins 255 - 8L down to 248 - 8L
+            const unsigned r = (unsigned)rank_left;
+            unsigned c[8], sum = 0u;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                c[j] = bins[255 - 8 * lane - j];
+                sum += c[j];
+            }
+            unsigned upto = sum;                          // keys in this lane's bins and in all higher ones
+#pragma unroll
+            for (int off = 1; off < 32; off <<= 1) {
+                const unsigned t = __shfl_up_sync(0xffffffffu, upto, off);
+                if (lane >= off) upto += t;
+            }
+            unsigned above = upto - sum;
+            if (above < r && r <= upto) {                 // true in exactly one lane
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (above < r && r <= above + c[j]) {
+                        found = prefix | ((unsigned long long)(255 - 8 * lane - j) << shift);
+                        rank_left = (int)(r - above);
+                    }
+                    above += c[j];
+                }
+            }
+        }
+        __syncthreads();
+        prefix = found;
+        mask |= 0xffull << shift;
+    }
+    return prefix;
+}
+
+// keys: [n_cand] filled by note_score; chosen: [(n_cand + 31) / 32] cleared.  All threads call this
+// after a barrier that follows the last note_score.  A key holds the score above the block's inverted
+// number, so no two are equal and the best ``room`` of them are those not below the room-th largest.
+__device__ void finish_selection(const Selection& s, const unsigned long long* __restrict__ keys, unsigned* __restrict__ chosen,
                                  int* __restrict__ list, int list_cap, int init_blocks, int topk) {
     const int tid = threadIdx.x, n_threads = blockDim.x;
-    const int n_sort = s.n_sort, n_cand = s.n_cand;
+    const int n_cand = s.n_cand;
     const int room = min(max(0, topk - init_blocks), n_cand);
-    if (n_cand > room) {                  // with room for every candidate there is nothing to sort
-        for (int k = 2; k <= n_sort; k <<= 1) {
-            for (int j = k >> 1; j > 0; j >>= 1) {
-                for (int i = tid; i < n_sort; i += n_threads) {
-                    const int partner = i ^ j;
-                    if (partner > i) {
-                        const unsigned long long a = keys[i], b = keys[partner];
-                        const bool descending = (i & k) == 0;
-                        if (descending ? a < b : a > b) {
-                            keys[i] = b;
-                            keys[partner] = a;
-                        }
-                    }
-                }
-                __syncthreads();
-            }
-        }
-    }
-    for (int r = tid; r < (n_cand > room ? room : n_cand); r += n_threads) {
-        const unsigned long long key = keys[r];
-        if (key != 0ull) {
-            const int i = 0x7fffffff - (int)(unsigned)(key & 0xffffffffull);
-            atomicOr(&chosen[i >> 5], 1u << (i & 31));
-        }
+    unsigned long long least = ~0ull;                     // no room: nothing is chosen
+    if (room >= n_cand) least = 0ull;                     // room for every candidate
+    else if (room > 0) least = kth_largest(keys, n_cand, room);
+    for (int i = tid; i < n_cand; i += n_threads) {
+        const unsigned long long key = keys[i];
+        if (key != 0ull && key >= least) atomicOr(&chosen[i >> 5], 1u << (i & 31));
     }
     __syncthreads();
-    if (tid == 0) {
-        int n = 0;
-        const int n_init = min(init_blocks, s.qb + 1);
-        for (int k = 0; k < n_init && n < list_cap - 1; ++k) list[n++] = k;
-        for (int w = 0; w < (n_cand + 31) / 32; ++w) {
-            unsigned bits = chosen[w];
-            while (bits && n < list_cap - 1) {
-                const int b = __ffs(bits) - 1;
-                bits &= bits - 1;
-                list[n++] = init_blocks + 32 * w + b;
-            }
+    // the list in rising order: first blocks, the chosen ones, the local window; every entry's place follows
+    // from the counts before it, so all threads write (a list that is too short keeps its first entries)
+    const int n_init = min(init_blocks, s.qb + 1);
+    const int last = list_cap - 1;
+    for (int k = tid; k < n_init; k += n_threads)
+        if (k < last) list[k] = k;
+    for (int i = tid; i < n_cand; i += n_threads) {
+        const unsigned w = chosen[i >> 5];
+        if ((w >> (i & 31)) & 1u) {
+            int at = n_init + __popc(w & ((1u << (i & 31)) - 1u));
+            for (int j = 0; j < (i >> 5); ++j) at += __popc(chosen[j]);
+            if (at < last) list[at] = init_blocks + i;
         }
-        for (int k = max(n_init, s.last_choice + 1); k <= s.qb && n < list_cap - 1; ++k) list[n++] = k;
-        list[n] = -1;
     }
+    int n_chosen = 0;
+    for (int j = 0; j < (n_cand + 31) / 32; ++j) n_chosen += __popc(chosen[j]);
+    const int first_local = max(n_init, s.last_choice + 1);
+    const int base = n_init + n_chosen;
+    for (int k = first_local + tid; k <= s.qb; k += n_threads)
+        if (base + k - first_local < last) list[base + k - first_local] = k;
+    if (tid == 0) list[min(base + max(0, s.qb - first_local + 1), last)] = -1;
 }
 
 // Set when a query had more candidate blocks than the launch made room for (the caller's bound on the
@@ -678,7 +720,7 @@ static int launch_select_mma(const void* q, const float* pooled, const int* posi
 }
 
 // max_entries: an upper bound on the pooled keys any query of the step sees (longest sequence / stride + 1); it
-// sizes the sort of the candidate blocks, 8 bytes of shared memory per block.
+// sizes the keys of the candidate blocks (``sort_cap`` of them), 8 bytes of shared memory per block.
 template <int D>
 static int launch_select_sliced(const void* q, const float* pooled, const int* positions, const int* token_seq,
                                 const int* slots, const int* page_table, int max_pages, int* lists, int list_cap,
