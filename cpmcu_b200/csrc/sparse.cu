@@ -68,9 +68,9 @@ CPM_API int cpm_pool_keys(const void* k_cache, float* pooled, const int* positio
 // goes straight into the keys of the blocks it overlaps (note_score, an atomic maximum in
 // shared memory), so the shared arrays grow with the number of candidate blocks only.
 //
-// A block's key is the score's bits made monotonic, then the inverted candidate index, so that
-// the larger key has the higher score and among equal scores the lower index; 0 is below every
-// real key and stands for "no pooled key overlaps this block".
+// A block's key is its score's bits made monotonic (an unsigned compare orders them like the
+// floats); 0 is below every real key and stands for "no pooled key overlaps this block".  Among
+// equal scores the lower block wins.
 struct Selection {
     int qb;             // block of the query
     int last_choice;    // last block that can be chosen (those after it are the local window)
@@ -90,95 +90,118 @@ __device__ __forceinline__ Selection selection_of(int p, int kernel, int stride,
     return s;
 }
 
-// Clears the candidates' keys and the chosen bits; all threads call it, a barrier must follow.
-__device__ __forceinline__ void clear_selection(const Selection& s, unsigned long long* __restrict__ keys,
-                                                unsigned* __restrict__ chosen) {
-    for (int i = threadIdx.x; i < s.n_cand; i += blockDim.x) keys[i] = 0ull;
-    for (int i = threadIdx.x; i < (s.n_cand + 31) / 32; i += blockDim.x) chosen[i] = 0u;
+// The selection's arrays in shared memory, sized by the launch for ``cap`` candidate blocks.
+struct SelectionArrays {
+    unsigned* keys;      // [cap] a candidate's best score, monotonic bits
+    unsigned* chosen;    // [words] a bit per chosen candidate
+    unsigned* equal;     // [words] a bit per candidate whose score equals the last one taken
+};
+__host__ __device__ constexpr int selection_words(int cap) { return (cap / 32 + 4) & ~3; }
+__host__ __device__ constexpr size_t selection_bytes(int cap) { return (size_t)cap * 4 + 2 * (size_t)selection_words(cap) * 4; }
+__device__ __forceinline__ SelectionArrays selection_arrays(unsigned char* base, int cap) {
+    SelectionArrays a;
+    a.keys = reinterpret_cast<unsigned*>(base);
+    a.chosen = a.keys + cap;
+    a.equal = a.chosen + selection_words(cap);
+    return a;
 }
 
-// Pooled key ``entry`` has the score ``v`` (>= 0): raises the key of every candidate block it overlaps.
-__device__ __forceinline__ void note_score(const Selection& s, unsigned long long* __restrict__ keys, int init_blocks,
-                                           int entry, float v) {
+// Clears the candidates' keys and the bit masks; all threads call it, a barrier must follow.
+__device__ __forceinline__ void clear_selection(const Selection& s, const SelectionArrays& a) {
+    for (int i = threadIdx.x; i < s.n_cand; i += blockDim.x) a.keys[i] = 0u;
+    for (int i = threadIdx.x; i < (s.n_cand + 31) / 32; i += blockDim.x) a.chosen[i] = a.equal[i] = 0u;
+}
+
+// Pooled key ``entry`` has the score ``v`` (>= 0): raises the key of every candidate block it overlaps
+// (a native 32-bit atomic maximum in shared memory).
+__device__ __forceinline__ void note_score(const Selection& s, const SelectionArrays& a, int init_blocks, int entry, float v) {
     const unsigned bits = __float_as_uint(v);
-    const unsigned long long mono = (unsigned long long)((bits & 0x80000000u) ? ~bits : (bits | 0x80000000u)) << 32;
+    const unsigned mono = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
     const int k_hi = min((entry + s.reach_back) / s.per_block, init_blocks + s.n_cand - 1);
-    for (int k = max(entry / s.per_block, init_blocks); k <= k_hi; ++k) {
-        const int i = k - init_blocks;
-        atomicMax(&keys[i], mono | (unsigned)(0x7fffffff - i));
-    }
+    for (int k = max(entry / s.per_block, init_blocks); k <= k_hi; ++k) atomicMax(&a.keys[k - init_blocks], mono);
 }
 
-// The ``rank``-th largest (1 <= rank <= n) of keys[0..n): eight passes over the keys' bytes from the top one down.
-// Each pass counts, in 256 bins, the next byte of the keys that agree with the bytes found so far, and one warp
-// walks the bins from the high end to the one that holds the rank.  All threads call it (at least one warp) and
-// all get the value; the keys stay as they are.  The selection needs the set of the best keys, not their order,
-// so this stands where a sort would: 8 short passes whatever the count, against 45 barriers for 512 keys.
-__device__ unsigned long long kth_largest(const unsigned long long* __restrict__ keys, int n, int rank) {
-    __shared__ unsigned bins[256];
-    __shared__ unsigned long long found;
-    __shared__ int rank_left;
+// The ``rank``-th largest (1 <= rank <= n) of keys[0..n), and in ``with_it`` how many keys of that value belong to
+// the ``rank`` largest: eight passes over the keys' 4-bit digits from the top one down.  In each pass a warp
+// counts, for every value of the digit, its keys that agree with the digits found so far (one ballot per value:
+// no contention, however the keys are spread; scores of one query share their exponent, so whole passes have
+// all keys under one value), lanes 0..15 add the warp's counts to the pass's 16 bins, and after one barrier
+// every thread walks the bins from the high end to the one that holds the rank.  All threads call it (whole
+// warps) and all get the values; the keys stay as they are.  The selection needs the set of the best keys, not
+// their order, so this stands where a sort would: 10 barriers whatever the count, against 45 for 512 keys.
+__device__ unsigned kth_largest(const unsigned* __restrict__ keys, int n, int rank, int* with_it) {
+    __shared__ unsigned bins[8][16];
     const int tid = threadIdx.x, n_threads = blockDim.x, lane = tid & 31;
-    if (tid == 0) {
-        found = 0ull;
-        rank_left = rank;
-    }
-    unsigned long long prefix = 0ull, mask = 0ull;
-    for (int shift = 56; shift >= 0; shift -= 8) {
-        for (int i = tid; i < 256; i += n_threads) bins[i] = 0u;
-        __syncthreads();
-        for (int i = tid; i < n; i += n_threads) {
-            const unsigned long long k = keys[i];
-            if ((k & mask) == prefix) atomicAdd(&bins[(unsigned)(k >> shift) & 255u], 1u);
-        }
-        __syncthreads();
-        if (tid < 32) {                                   // lane L owns bins 255 - 8L down to 248 - 8L
-            const unsigned r = (unsigned)rank_left;
-            unsigned c[8], sum = 0u;
+    __syncthreads();                                        // nobody still reads the bins of an earlier call
+    if (tid < 128) bins[tid >> 4][tid & 15] = 0u;
+    __syncthreads();
+    unsigned prefix = 0u, mask = 0u, left = (unsigned)rank;
+#pragma unroll 1
+    for (int pass = 0; pass < 8; ++pass) {
+        const int shift = 28 - 4 * pass;
+        unsigned mine = 0u;                                 // lane b < 16: this warp's keys with digit b
+        for (int first = 0; first < n; first += n_threads) {
+            const int i = first + tid;
+            const unsigned k = i < n ? keys[i] : 0u;
+            const bool counts = i < n && (k & mask) == prefix;
+            const unsigned digit = (k >> shift) & 15u;
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                c[j] = bins[255 - 8 * lane - j];
-                sum += c[j];
-            }
-            unsigned upto = sum;                          // keys in this lane's bins and in all higher ones
-#pragma unroll
-            for (int off = 1; off < 32; off <<= 1) {
-                const unsigned t = __shfl_up_sync(0xffffffffu, upto, off);
-                if (lane >= off) upto += t;
-            }
-            unsigned above = upto - sum;
-            if (above < r && r <= upto) {                 // true in exactly one lane
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    if (above < r && r <= above + c[j]) {
-                        found = prefix | ((unsigned long long)(255 - 8 * lane - j) << shift);
-                        rank_left = (int)(r - above);
-                    }
-                    above += c[j];
-                }
+            for (int b = 0; b < 16; ++b) {
+                const unsigned votes = __ballot_sync(0xffffffffu, counts && digit == (unsigned)b);
+                if (lane == b) mine += __popc(votes);
             }
         }
+        if (lane < 16 && mine) atomicAdd(&bins[pass][lane], mine);
         __syncthreads();
-        prefix = found;
-        mask |= 0xffull << shift;
+        unsigned above = 0u, digit = 0u, within = left;
+#pragma unroll
+        for (int b = 15; b >= 0; --b) {
+            const unsigned c = bins[pass][b];
+            if (above < left && left <= above + c) {
+                digit = (unsigned)b;
+                within = left - above;
+            }
+            above += c;
+        }
+        left = within;
+        prefix |= digit << shift;
+        mask |= 15u << shift;
     }
+    *with_it = (int)left;
     return prefix;
 }
 
-// keys: [n_cand] filled by note_score; chosen: [(n_cand + 31) / 32] cleared.  All threads call this
-// after a barrier that follows the last note_score.  A key holds the score above the block's inverted
-// number, so no two are equal and the best ``room`` of them are those not below the room-th largest.
-__device__ void finish_selection(const Selection& s, const unsigned long long* __restrict__ keys, unsigned* __restrict__ chosen,
-                                 int* __restrict__ list, int list_cap, int init_blocks, int topk) {
+// keys: [n_cand] filled by note_score; chosen, equal: cleared.  All threads call this after a barrier that
+// follows the last note_score.  Taken are the candidates above the room-th largest score, and of those equal to
+// it the lowest blocks, as many as still fit.
+__device__ void finish_selection(const Selection& s, const SelectionArrays& a, int* __restrict__ list, int list_cap,
+                                 int init_blocks, int topk) {
     const int tid = threadIdx.x, n_threads = blockDim.x;
     const int n_cand = s.n_cand;
+    const unsigned* keys = a.keys;
+    unsigned* chosen = a.chosen;
     const int room = min(max(0, topk - init_blocks), n_cand);
-    unsigned long long least = ~0ull;                     // no room: nothing is chosen
-    if (room >= n_cand) least = 0ull;                     // room for every candidate
-    else if (room > 0) least = kth_largest(keys, n_cand, room);
-    for (int i = tid; i < n_cand; i += n_threads) {
-        const unsigned long long key = keys[i];
-        if (key != 0ull && key >= least) atomicOr(&chosen[i >> 5], 1u << (i & 31));
+    if (room >= n_cand) {                                 // room for every candidate that has a score
+        for (int i = tid; i < n_cand; i += n_threads)
+            if (keys[i] != 0u) atomicOr(&chosen[i >> 5], 1u << (i & 31));
+    } else if (room > 0) {
+        int with_it = 0;
+        const unsigned least = kth_largest(keys, n_cand, room, &with_it);
+        for (int i = tid; i < n_cand; i += n_threads) {
+            const unsigned key = keys[i];
+            if (key == 0u) continue;
+            if (key > least) atomicOr(&chosen[i >> 5], 1u << (i & 31));
+            else if (key == least) atomicOr(&a.equal[i >> 5], 1u << (i & 31));
+        }
+        __syncthreads();
+        for (int i = tid; i < n_cand; i += n_threads) {
+            const unsigned w = a.equal[i >> 5];
+            if ((w >> (i & 31)) & 1u) {
+                int before = __popc(w & ((1u << (i & 31)) - 1u));
+                for (int j = 0; j < (i >> 5); ++j) before += __popc(a.equal[j]);
+                if (before < with_it) atomicOr(&chosen[i >> 5], 1u << (i & 31));
+            }
+        }
     }
     __syncthreads();
     // the list in rising order: first blocks, the chosen ones, the local window; every entry's place follows
@@ -265,9 +288,8 @@ select_blocks_kernel(const T* __restrict__ q, const float* __restrict__ pooled, 
                      int n_heads, int n_kv, int d, float scale, int kernel, int stride, int block_size,
                      int init_blocks, int topk, int local_blocks, int dense_len, int sort_cap) {
     extern __shared__ __align__(16) unsigned char sm_raw[];
-    unsigned long long* keys = (unsigned long long*)sm_raw;                    // [sort_cap]
-    unsigned* chosen = (unsigned*)(keys + sort_cap);                          // [sort_cap / 32 + 1]
-    float* qs = (float*)(chosen + ((sort_cap / 32 + 4) & ~3));               // [group][d]
+    const SelectionArrays arrays = selection_arrays(sm_raw, sort_cap);
+    float* qs = (float*)(sm_raw + selection_bytes(sort_cap));                 // [group][d]
     const int group = n_heads / n_kv;
     float* stat_m = qs + group * d;                      // [warps][kMaxGroup]
     float* stat_l = stat_m + kSelectWarps * kMaxGroup;   // [warps][kMaxGroup]
@@ -284,7 +306,7 @@ select_blocks_kernel(const T* __restrict__ q, const float* __restrict__ pooled, 
     const int n_vis = p + 1 >= kernel ? (p + 1 - kernel) / stride + 1 : 0;
     const Selection sel = selection_of(p, kernel, stride, block_size, init_blocks, local_blocks, sort_cap);
     if (tid == 0 && p / block_size - local_blocks + 1 - init_blocks > sort_cap) g_select_overflow = 1;
-    clear_selection(sel, keys, chosen);
+    clear_selection(sel, arrays);
 
     for (int i = tid; i < group * d; i += kSelectThreads)
         qs[i] = to_f32(q[((int64_t)t * n_heads + kvh * group) * d + i]);
@@ -327,11 +349,11 @@ select_blocks_kernel(const T* __restrict__ q, const float* __restrict__ pooled, 
             if (h == lane) mine = dots[h];
         const float prob = lane < group ? expf(mine - head_m) * head_inv : 0.f;
         const float total = warp_sum(prob);
-        if (lane == 0) note_score(sel, keys, init_blocks, i, total);
+        if (lane == 0) note_score(sel, arrays, init_blocks, i, total);
     }
     __syncthreads();
 
-    finish_selection(sel, keys, chosen, list, list_cap, init_blocks, topk);
+    finish_selection(sel, arrays, list, list_cap, init_blocks, topk);
 }
 
 // ---------------------------------------------------------------------------
@@ -400,9 +422,8 @@ select_blocks_mma_kernel(const bf16* __restrict__ q, const float* __restrict__ p
                          int n_heads, int n_kv, float scale_log2, int kernel, int stride, int block_size,
                          int init_blocks, int topk, int local_blocks, int dense_len, int sort_cap) {
     extern __shared__ __align__(16) unsigned char sm_raw[];
-    unsigned long long* keys = (unsigned long long*)sm_raw;                   // [sort_cap]
-    unsigned* chosen = (unsigned*)(keys + sort_cap);                         // [sort_cap / 32 + 1]
-    float* stat_m = (float*)(chosen + ((sort_cap / 32 + 4) & ~3));          // [warps][16]
+    const SelectionArrays arrays = selection_arrays(sm_raw, sort_cap);
+    float* stat_m = (float*)(sm_raw + selection_bytes(sort_cap));            // [warps][16]
     float* stat_l = stat_m + kSelMmaWarps * 16;                              // [warps][16]
     const int t = blockIdx.x, kvh = blockIdx.y, tid = threadIdx.x;
     const int warp = tid >> 5, lane = tid & 31, g = lane >> 2, j = lane & 3;
@@ -419,7 +440,7 @@ select_blocks_mma_kernel(const bf16* __restrict__ q, const float* __restrict__ p
     const int n_tiles = (n_vis + 7) / 8;
     const Selection sel = selection_of(p, kernel, stride, block_size, init_blocks, local_blocks, sort_cap);
     if (tid == 0 && p / block_size - local_blocks + 1 - init_blocks > sort_cap) g_select_overflow = 1;
-    clear_selection(sel, keys, chosen);                       // the barrier between the two walks orders it
+    clear_selection(sel, arrays);                       // the barrier between the two walks orders it
 
     uint4 qf[2][D / 32];
 #pragma unroll
@@ -501,12 +522,12 @@ select_blocks_mma_kernel(const bf16* __restrict__ q, const float* __restrict__ p
         }
         const int c0 = tile * 8 + 2 * j;
         if (g == 0) {
-            if (c0 < n_vis) note_score(sel, keys, init_blocks, c0, col0);
-            if (c0 + 1 < n_vis) note_score(sel, keys, init_blocks, c0 + 1, col1);
+            if (c0 < n_vis) note_score(sel, arrays, init_blocks, c0, col0);
+            if (c0 + 1 < n_vis) note_score(sel, arrays, init_blocks, c0 + 1, col1);
         }
     }
     __syncthreads();
-    finish_selection(sel, keys, chosen, list, list_cap, init_blocks, topk);
+    finish_selection(sel, arrays, list, list_cap, init_blocks, topk);
 }
 
 // ---------------------------------------------------------------------------
@@ -622,24 +643,25 @@ select_finish_kernel(const float* __restrict__ raw, const float* __restrict__ st
                      int kernel, int stride, int block_size, int init_blocks, int topk, int local_blocks, int dense_len,
                      int max_entries, int sort_cap) {
     extern __shared__ __align__(16) unsigned char sm_raw[];
-    unsigned long long* keys = (unsigned long long*)sm_raw;                   // [sort_cap]
-    unsigned* chosen = (unsigned*)(keys + sort_cap);                         // [sort_cap / 32 + 1]
+    const SelectionArrays arrays = selection_arrays(sm_raw, sort_cap);
     __shared__ float head_m[16], head_inv[16];
     const int t = blockIdx.x, kvh = blockIdx.y, tid = threadIdx.x;
     int* list = lists + ((int64_t)t * n_kv + kvh) * list_cap;
+    // The step's positions are written before the step's first kernel, by a launch that everything after it waits
+    // for in full; the arrays cleared here are this block's own.  Only the scores need the kernel ahead.
     pdl_launch_dependents();
-    pdl_wait();
     const int p = positions[t];
-    if (p + 1 <= dense_len) {
-        if (tid == 0) list[0] = -2;
-        return;
-    }
     const int group = n_heads / n_kv;
     const int64_t unit = (int64_t)t * n_kv + kvh;
     const int n_vis = min(p + 1 >= kernel ? (p + 1 - kernel) / stride + 1 : 0, max_entries);
     const Selection sel = selection_of(p, kernel, stride, block_size, init_blocks, local_blocks, sort_cap);
+    if (p + 1 > dense_len) clear_selection(sel, arrays);
+    pdl_wait();
+    if (p + 1 <= dense_len) {
+        if (tid == 0) list[0] = -2;
+        return;
+    }
     if (tid == 0 && p / block_size - local_blocks + 1 - init_blocks > sort_cap) g_select_overflow = 1;
-    clear_selection(sel, keys, chosen);
     {
         // The slices' statistics, merged by all threads: thread (head = tid % 16, lot = tid / 16) takes the slices
         // lot, lot + 32, ... (sixteen threads walking them one after the other waited for one load at a time:
@@ -672,20 +694,33 @@ select_finish_kernel(const float* __restrict__ raw, const float* __restrict__ st
         }
     }
     __syncthreads();
+    // a thread's next row is asked for before its current one is worked on
     const float* my_raw = raw + unit * max_entries * 16;
+    float4 next[4];
+    if (tid < n_vis) {
+        const float4* row = reinterpret_cast<const float4*>(my_raw + (int64_t)tid * 16);
+#pragma unroll
+        for (int c = 0; c < 4; ++c) next[c] = row[c];
+    }
     for (int i = tid; i < n_vis; i += kFinishThreads) {
-        const float4* row = reinterpret_cast<const float4*>(my_raw + (int64_t)i * 16);
+        float4 v[4];
+#pragma unroll
+        for (int c = 0; c < 4; ++c) v[c] = next[c];
+        if (i + kFinishThreads < n_vis) {
+            const float4* row = reinterpret_cast<const float4*>(my_raw + (int64_t)(i + kFinishThreads) * 16);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) next[c] = row[c];
+        }
         float total = 0.f;
 #pragma unroll
         for (int c = 0; c < 4; ++c) {
-            const float4 v = row[c];
-            total += exp2f(v.x - head_m[4 * c]) * head_inv[4 * c] + exp2f(v.y - head_m[4 * c + 1]) * head_inv[4 * c + 1]
-                   + exp2f(v.z - head_m[4 * c + 2]) * head_inv[4 * c + 2] + exp2f(v.w - head_m[4 * c + 3]) * head_inv[4 * c + 3];
+            total += exp2f(v[c].x - head_m[4 * c]) * head_inv[4 * c] + exp2f(v[c].y - head_m[4 * c + 1]) * head_inv[4 * c + 1]
+                   + exp2f(v[c].z - head_m[4 * c + 2]) * head_inv[4 * c + 2] + exp2f(v[c].w - head_m[4 * c + 3]) * head_inv[4 * c + 3];
         }
-        note_score(sel, keys, init_blocks, i, total);
+        note_score(sel, arrays, init_blocks, i, total);
     }
     __syncthreads();
-    finish_selection(sel, keys, chosen, list, list_cap, init_blocks, topk);
+    finish_selection(sel, arrays, list, list_cap, init_blocks, topk);
 }
 
 // Floats of scratch the two-kernel path needs (raw scores and slice statistics).
@@ -705,7 +740,7 @@ static int launch_select_mma(const void* q, const float* pooled, const int* posi
                              int n_tokens, int n_heads, int n_kv, float scale, int kernel, int stride, int block_size,
                              int init_blocks, int topk, int local_blocks, int dense_len, int sort_cap,
                              cudaStream_t stream) {
-    const size_t smem = (size_t)sort_cap * 8 + (size_t)((sort_cap / 32 + 4) & ~3) * 4 + 2 * 16 * 16 * sizeof(float);
+    const size_t smem = selection_bytes(sort_cap) + 2 * 16 * 16 * sizeof(float);
     if (smem > 227 * 1024) return CPM_BAD_ARGUMENT;
     const bool few = n_tokens * n_kv < 148;
     auto kern = few ? select_blocks_mma_kernel<D, 16> : select_blocks_mma_kernel<D, 4>;
@@ -727,7 +762,7 @@ static int launch_select_sliced(const void* q, const float* pooled, const int* p
                                 int n_tokens, int n_heads, int n_kv, float scale, int kernel, int stride, int block_size,
                                 int init_blocks, int topk, int local_blocks, int dense_len, int max_entries, int sort_cap,
                                 float* scratch, int n_slices, cudaStream_t stream) {
-    const size_t smem = (size_t)sort_cap * 8 + (size_t)((sort_cap / 32 + 4) & ~3) * 4;
+    const size_t smem = selection_bytes(sort_cap);
     if (smem > 200 * 1024 || n_tokens > 65535) return CPM_BAD_ARGUMENT;
     float* raw = scratch;
     float* stats = scratch + (int64_t)n_tokens * n_kv * max_entries * 16;
@@ -778,7 +813,7 @@ CPM_API int cpm_select_blocks(const void* q, const float* pooled, const int* pos
         if (d == 128) CPM_SELECT_MMA(128);
 #undef CPM_SELECT_MMA
     }
-    const size_t smem = (size_t)sort_cap * 8 + (size_t)((sort_cap / 32 + 4) & ~3) * 4
+    const size_t smem = selection_bytes(sort_cap)
                         + ((size_t)group * d + 2 * kSelectWarps * kMaxGroup) * sizeof(float);
     if (smem > 227 * 1024) return CPM_BAD_ARGUMENT;
     dim3 grid(n_tokens, n_kv);

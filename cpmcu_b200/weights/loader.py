@@ -20,6 +20,11 @@ from .safetensors_io import SafetensorsError, SafetensorsFile, model_files
 
 
 class WeightError(ValueError):
+    """Everything that is wrong with a checkpoint, in one message: missing tensors, unexpected tensors, wrong
+    shapes, and other problems (a tensor that cannot be read, a floating tensor where an integer table belongs).
+    A stored dtype that differs from the one the tensor is held in is not an error: the tensor is converted
+    (see ``target_dtype``)."""
+
     def __init__(self, missing: List[str], unexpected: List[str], wrong_shape: List[str], other: List[str] = ()):
         self.missing, self.unexpected, self.wrong_shape, self.other = list(missing), list(unexpected), list(wrong_shape), list(other)
         lines = ["the checkpoint does not fit the model:"]
