@@ -714,12 +714,233 @@ listed_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
     }
 }
 
+// ---------------------------------------------------------------------------
+// attention over listed key blocks for the many tokens of a prompt chunk: a block of threads takes seven
+// consecutive tokens, one per warp, and an eighth warp brings the key blocks
+// ---------------------------------------------------------------------------
+// The kernel above has every token bring its own 96 blocks from L2: 12.9 GB per layer and 2,048-token chunk
+// of the 8B sizes, which is what bounds it.  Consecutive tokens of a prompt share the local window and the
+// leading blocks and part of the rest, so here the tokens of a tile share what is brought: every warp marks
+// its token's blocks in a bit mask, the union of the masks is walked in rising order, the producer warp
+// copies each of its blocks once into a ring of shared-memory stages, and a token's warp attends to the
+// blocks its token listed and passes over the others.  The warps meet only through the ring's barriers
+// (full: the copies of a stage have landed; empty: all seven warps are done with it), so a warp that has
+// nothing to do with a block runs ahead by up to the ring's length instead of waiting for the others at
+// every block (with one barrier of all warps per block the warps idled 45 % of the steps on random data,
+// where the union of seven lists is 175 blocks).  A tile whose tokens belong to several sequences (packed
+// prompts) is done in passes, one per sequence.  Rows, masking and arithmetic are those of the kernel above.
+// Every wait is bounded; a wait that runs out raises the block's abort flag, which ends the others' waits.
+constexpr int kTileTokens = 7;
+constexpr int kTileWarps = kTileTokens + 1;
+constexpr int kTileStages = 6;
+constexpr uint32_t kTileSpinLimit = 1u << 22;
+
+__device__ int g_listed_tile_error = 0;
+
+struct BlockCursor {            // walks the set bits of a mask in rising order
+    int word;
+    unsigned bits;
+};
+__device__ __forceinline__ int next_block(BlockCursor& c, const unsigned* __restrict__ mask, int words) {
+    while (c.bits == 0u) {
+        if (++c.word >= words) return -1;
+        c.bits = mask[c.word];
+    }
+    const int b = __ffs(c.bits) - 1;
+    c.bits &= c.bits - 1u;
+    return c.word * 32 + b;
+}
+
+__device__ __forceinline__ void tile_bar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" :: "r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void tile_bar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" :: "r"(bar) : "memory");
+}
+// The barrier gets this thread's arrival when all its earlier cp.async copies have landed.
+__device__ __forceinline__ void tile_bar_arrive_after_copies(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" :: "r"(bar) : "memory");
+}
+// Waits for the phase of this parity; false when the tries ran out or another warp gave up.
+__device__ __forceinline__ bool tile_bar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < kTileSpinLimit; ++i) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\t"
+                     "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                     "selp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+        if (ok) return true;
+        if ((i & 255u) == 255u && *abort_flag) return false;
+    }
+    return false;
+}
+
+template <int D>
+__global__ void __launch_bounds__(kTileWarps * 32, 1)
+listed_tile_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
+                   bf16* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ token_seq,
+                   const int* __restrict__ slots, const int* __restrict__ page_table, int max_pages,
+                   const int* __restrict__ block_list, int list_cap, int n_tokens, int n_heads, int n_kv, int m_tiles,
+                   float scale_log2, int words) {
+    using S = DecodeSmem<D>;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[kTileStages], empty_bar[kTileStages];
+    __shared__ int abort_flag;
+    unsigned* all = reinterpret_cast<unsigned*>(smem_raw + kTileStages * S::kStageBytes);      // [words] the union
+    unsigned* mine = all + words;                                                               // [tokens][words]
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const bool producer = warp == kTileTokens;
+    const int t0 = blockIdx.x * kTileTokens, t = t0 + warp;
+    const int kvh = blockIdx.y / m_tiles, mt = blockIdx.y % m_tiles;
+    const int group = n_heads / n_kv;
+    const int j = lane & 3, g = lane >> 2;
+    const uint32_t stages = (uint32_t)__cvta_generic_to_shared(smem_raw);
+    const int64_t page_elems = (int64_t)n_kv * kPageTokens * D;
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kTileStages; ++s) {
+            tile_bar_init((uint32_t)__cvta_generic_to_shared(&full_bar[s]), 32);            // the producer's lanes
+            tile_bar_init((uint32_t)__cvta_generic_to_shared(&empty_bar[s]), kTileTokens);  // one arrival per token's warp
+        }
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    pdl_launch_dependents();
+    pdl_wait();
+    const bool live = !producer && t < n_tokens;
+    const int p = live ? positions[t] : 0;
+    const int* list = block_list + ((int64_t)(live ? t : 0) * n_kv + kvh) * list_cap;
+
+    TileState<D> st;
+    st.init();
+    uint4 qf[2][D / 32];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int local = min(mt * 16 + g + 8 * r, group - 1);
+        const bf16* qrow = q + ((int64_t)(live ? t : 0) * n_heads + kvh * group + local) * D + 8 * j;
+#pragma unroll
+        for (int w = 0; w < D / 32; ++w) qf[r][w] = __ldg(reinterpret_cast<const uint4*>(qrow + 32 * w));
+    }
+
+    const int tile_tokens = min(kTileTokens, n_tokens - t0);
+    uint32_t it = 0;                                            // blocks that have gone through the ring, all passes
+    bool ok = true;
+    for (int first = 0; first < tile_tokens;) {                // one pass per sequence in the tile
+        const int seq = token_seq[t0 + first];
+        int end = first + 1;
+        while (end < tile_tokens && token_seq[t0 + end] == seq) ++end;
+        const bool member = !producer && warp >= first && warp < end;
+        const int* pages = page_table + (int64_t)slots[seq] * max_pages;
+        // ---- the tokens' masks and their union ----
+        for (int i = threadIdx.x; i < (kTileTokens + 1) * words; i += kTileWarps * 32) all[i] = 0u;
+        __syncthreads();
+        if (member) {
+            unsigned* m = mine + warp * words;
+            if (list[0] == -2) {                                // "dense": every block up to the token's own
+                const int last = p / kPageTokens;
+                for (int w = lane; w <= (last >> 5) && w < words; w += 32)
+                    m[w] = w < (last >> 5) ? 0xffffffffu : (0xffffffffu >> (31 - (last & 31)));
+            } else {
+                for (int base = 0; base < list_cap; base += 32) {      // the list ends at its first negative entry;
+                    const int i = base + lane;                          // what lies behind it is not the list's
+                    const int b = i < list_cap ? list[i] : -1;
+                    const unsigned ended = __ballot_sync(0xffffffffu, b < 0);
+                    const int n_valid = ended ? __ffs(ended) - 1 : 32;
+                    if (lane < n_valid && (b >> 5) < words) atomicOr(&m[b >> 5], 1u << (b & 31));
+                    if (ended) break;
+                }
+            }
+        }
+        __syncthreads();
+        for (int w = threadIdx.x; w < words; w += kTileWarps * 32) {
+            unsigned u = 0u;
+            for (int k = first; k < end; ++k) u |= mine[k * words + w];
+            all[w] = u;
+        }
+        __syncthreads();
+        // ---- the union's blocks through the ring ----
+        ok = ok && !*(volatile int*)&abort_flag;
+        BlockCursor cursor{-1, 0u};
+        if (producer) {
+            for (int b = ok ? next_block(cursor, all, words) : -1; b >= 0; b = next_block(cursor, all, words), ++it) {
+                const uint32_t s = it % kTileStages, use = it / kTileStages;
+                if (use > 0 && !tile_bar_wait((uint32_t)__cvta_generic_to_shared(&empty_bar[s]), (use - 1) & 1u, &abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                const int64_t base = (int64_t)CPM_PAGE(pages, b, max_pages) * page_elems + (int64_t)kvh * kPageTokens * D;
+                copy_page_async<D, 32>(stages + s * S::kStageBytes, k_cache + base, v_cache + base, lane);
+                tile_bar_arrive_after_copies((uint32_t)__cvta_generic_to_shared(&full_bar[s]));
+            }
+        } else {
+            const unsigned* my_mask = mine + warp * words;
+            for (int b = ok ? next_block(cursor, all, words) : -1; b >= 0; b = next_block(cursor, all, words), ++it) {
+                const uint32_t s = it % kTileStages, use = it / kTileStages;
+                if (!tile_bar_wait((uint32_t)__cvta_generic_to_shared(&full_bar[s]), use & 1u, &abort_flag)) {
+                    ok = false;
+                    break;
+                }
+                if (member && ((my_mask[b >> 5] >> (b & 31)) & 1u))
+                    attend_page_smem<D>(st, qf, stages + s * S::kStageBytes, b * kPageTokens, p, p, scale_log2, lane);
+                __syncwarp();
+                if (lane == 0) tile_bar_arrive((uint32_t)__cvta_generic_to_shared(&empty_bar[s]));
+            }
+        }
+        if (!ok) {                                              // a wait ran out: say so, and end the others' waits
+            atomicExch(&abort_flag, 1);
+            atomicCAS(&g_listed_tile_error, 0, 1);
+        }
+        asm volatile("cp.async.wait_all;\n" ::: "memory");     // the producer's copies, before its stages are given up or reused
+        __syncthreads();                                        // the masks are free for the next pass
+        if (*(volatile int*)&abort_flag) return;
+        // both kinds of warp have counted the same blocks; a warp that broke off has left through the line above
+        first = end;
+    }
+    if (!live) return;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 1);
+        st.l[r] += __shfl_xor_sync(0xffffffffu, st.l[r], 2);
+    }
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int local = mt * 16 + g + 8 * r;
+        if (local >= group) continue;
+        const float inv = st.l[r] > 0.f ? 1.f / st.l[r] : 0.f;
+        bf16* orow = out + ((int64_t)t * n_heads + kvh * group + local) * D + 2 * j;
+#pragma unroll
+        for (int nt = 0; nt < D / 8; ++nt)
+            *reinterpret_cast<__nv_bfloat162*>(orow + 8 * nt) =
+                __floats2bfloat162_rn(st.o[nt][2 * r] * inv, st.o[nt][2 * r + 1] * inv);
+    }
+}
+
+// 1 when a wait inside listed_tile_kernel ran out since the last call (and reset).  Synchronises the device.
+CPM_API int cpm_listed_tile_error() {
+    int code = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&code, g_listed_tile_error, sizeof(int)) != cudaSuccess) return -1;
+    if (code) cudaMemcpyToSymbol(g_listed_tile_error, &zero, sizeof(int));
+    return code;
+}
+
 template <int D>
 static int launch_listed(const void* q, const void* k_cache, const void* v_cache, void* out, const int* positions,
                          const int* token_seq, const int* slots, const int* page_table, int max_pages,
                          const int* block_list, int list_cap, int n_tokens, int n_heads, int n_kv, float scale,
-                         float* scratch, int n_splits, cudaStream_t stream) {
+                         float* scratch, int n_splits, bool tiles, cudaStream_t stream) {
     const int m_tiles = (n_heads / n_kv + 15) / 16;
+    // (a page table too wide for the masks to fit beside the ring: the kernel of one token per block)
+    if (tiles && kTileStages * DecodeSmem<D>::kStageBytes + (kTileTokens + 1) * ((max_pages + 31) / 32) * 4 <= 227 * 1024 - 256) {
+        const int words = (max_pages + 31) / 32;
+        const int smem = kTileStages * DecodeSmem<D>::kStageBytes + (kTileTokens + 1) * words * 4;
+        auto kern = listed_tile_kernel<D>;
+        static bool configured[kMaxDevices] = {};
+        if (int st = ensure_dynamic_smem(kern, 227 * 1024 - 256, configured)) return st;       // less the kernel's static part
+        cpm_launch(kLaunchAttention, kern, dim3((n_tokens + kTileTokens - 1) / kTileTokens, n_kv * m_tiles), kTileWarps * 32,
+                   (size_t)smem, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, positions,
+                   token_seq, slots, page_table, max_pages, block_list, list_cap, n_tokens, n_heads, n_kv, m_tiles,
+                   scale * 1.4426950408889634f, words);
+        return launch_status();
+    }
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (int64_t)n_tokens * n_kv * m_tiles * n_splits * 16 * D : nullptr;
     auto kern = listed_attention_kernel<D>;
@@ -736,21 +957,24 @@ static int launch_listed(const void* q, const void* k_cache, const void* v_cache
 }
 
 // q, out [tokens, heads, d] bf16; block_list int32 [tokens, kv_heads, list_cap] of 64-token blocks.
+// tiles != 0 (n_splits 1 only): the tokens are those of prompts, consecutive ones mostly of one sequence; seven of
+// them share the blocks that are brought (listed_tile_kernel).
 CPM_API int cpm_listed_attention_bf16(const void* q, const void* k_cache, const void* v_cache, void* out,
                                       const int* positions, const int* token_seq, const int* slots,
                                       const int* page_table, int max_pages, const int* block_list, int list_cap,
                                       int n_tokens, int n_heads, int n_kv, int d, float scale, float* scratch,
-                                      int n_splits, cudaStream_t stream) {
+                                      int n_splits, int tiles, cudaStream_t stream) {
     // scratch: cpm_decode_attention_scratch_floats(n_tokens, ...) floats when n_splits > 1, else unused
     if (n_tokens <= 0) return CPM_OK;
     if (n_kv <= 0 || n_heads % n_kv || !block_list || list_cap < 1 || n_kv * ((n_heads / n_kv + 15) / 16) > 65535 ||
-        n_splits < 1 || n_splits > 65535 || (n_splits > 1 && (!scratch || n_tokens > 65535)))
+        n_splits < 1 || n_splits > 65535 || (n_splits > 1 && (!scratch || n_tokens > 65535)) || (tiles && n_splits != 1))
         return CPM_BAD_ARGUMENT;
+    const bool tl = tiles != 0;
     switch (d) {
-        case 32: return launch_listed<32>(q, k_cache, v_cache, out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_tokens, n_heads, n_kv, scale, scratch, n_splits, stream);
-        case 64: return launch_listed<64>(q, k_cache, v_cache, out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_tokens, n_heads, n_kv, scale, scratch, n_splits, stream);
-        case 96: return launch_listed<96>(q, k_cache, v_cache, out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_tokens, n_heads, n_kv, scale, scratch, n_splits, stream);
-        case 128: return launch_listed<128>(q, k_cache, v_cache, out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_tokens, n_heads, n_kv, scale, scratch, n_splits, stream);
+        case 32: return launch_listed<32>(q, k_cache, v_cache, out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_tokens, n_heads, n_kv, scale, scratch, n_splits, tl, stream);
+        case 64: return launch_listed<64>(q, k_cache, v_cache, out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_tokens, n_heads, n_kv, scale, scratch, n_splits, tl, stream);
+        case 96: return launch_listed<96>(q, k_cache, v_cache, out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_tokens, n_heads, n_kv, scale, scratch, n_splits, tl, stream);
+        case 128: return launch_listed<128>(q, k_cache, v_cache, out, positions, token_seq, slots, page_table, max_pages, block_list, list_cap, n_tokens, n_heads, n_kv, scale, scratch, n_splits, tl, stream);
         default: return CPM_BAD_ARGUMENT;
     }
 }

@@ -43,7 +43,7 @@ _SIGNATURES = {
     "cpm_prefill_attention_bf16": [_P, _P, _P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_float,
                                    _P],
     "cpm_listed_attention_bf16": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, _P, c_int, c_int, c_int, c_int, c_int, c_float, _P,
-                                  c_int, _P],
+                                  c_int, c_int, _P],
     "cpm_gemm_bf16_tcgen05": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
     "cpm_prefill_attention_tcgen05": [_P, _P, _P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
                                       c_float, _P, c_int, _P],
@@ -107,6 +107,8 @@ def load() -> ctypes.CDLL:
         lib.cpm_select_blocks_scratch_floats.restype = c_int64
         lib.cpm_select_blocks_error.argtypes = []
         lib.cpm_select_blocks_error.restype = c_int
+        lib.cpm_listed_tile_error.argtypes = []
+        lib.cpm_listed_tile_error.restype = c_int
         lib.cpm_decode_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int, c_int]
         lib.cpm_decode_attention_scratch_floats.restype = c_int64
         for name, argtypes in _SIGNATURES.items():

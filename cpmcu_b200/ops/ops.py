@@ -177,6 +177,7 @@ class Ops:
     # product takes 51 us and the activation kernel 4 us more.
     TCGEN05_MIN_ROWS = int(os.environ.get("CPMCU_TCGEN05_MIN_ROWS", "9"))
     MAX_DECODE_SPLITS = int(os.environ.get("CPMCU_MAX_SPLITS", "16"))     # most shares a sequence's pages are cut into
+    LISTED_TILE_MIN_TOKENS = int(os.environ.get("CPMCU_LISTED_TILE_MIN", "32"))   # from here on prompt tokens share their blocks in tiles of eight
     SELECT_SCRATCH_BYTES = 64 << 20     # most scratch the sliced block selection may take (raw scores of all pooled keys)
 
     def _skinny_ok(self, M: int, K: int) -> bool:
@@ -329,7 +330,8 @@ class Ops:
         if (self.code == BF16 and block_list is not None and block_size == PAGE_TOKENS and not window
                 and d in FAST_HEAD_DIMS):
             return self.listed_attention(q, lane.k, lane.v, ctx.positions, ctx.token_seq, ctx.slot_dev,
-                                         lane.page_table, block_list, n_kv, scale)
+                                         lane.page_table, block_list, n_kv, scale,
+                                         tiles=not ctx.is_decode and n >= self.LISTED_TILE_MIN_TOKENS)
         return self.attention_generic(q, lane.k, lane.v, ctx.positions, ctx.token_seq, ctx.slot_dev,
                                       lane.page_table, n_kv, scale, window, block_list, block_size)
 
@@ -499,6 +501,9 @@ class Ops:
         arena = self.workspace.persistent.arena if self.workspace is not None else None
         if arena is not None and arena.guards:
             arena.check_guards()
+        if int(self.lib.cpm_listed_tile_error()):
+            raise RuntimeError("the block-list attention of a prompt chunk gave up waiting on a barrier; the results of "
+                               "this step are not valid")
         if int(self.lib.cpm_select_blocks_error()):
             raise RuntimeError("block selection met a query with more candidate key blocks than the launch made room "
                                "for (a sequence longer than the bound the step gave); the results of this step are not valid")
@@ -524,13 +529,15 @@ class Ops:
 
     def listed_attention(self, q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, positions: torch.Tensor,
                          token_seq: torch.Tensor, slots: torch.Tensor, page_table: torch.Tensor,
-                         block_list: torch.Tensor, n_kv: int, scale: float) -> torch.Tensor:
-        """Attention of every token over the 64-token key blocks its list names (block-sparse)."""
+                         block_list: torch.Tensor, n_kv: int, scale: float, tiles: bool = False) -> torch.Tensor:
+        """Attention of every token over the 64-token key blocks its list names (block-sparse).  ``tiles``: the
+        tokens are those of prompts (consecutive tokens mostly of one sequence); eight of them then share the
+        blocks they bring from the cache."""
         self._act(q, "q")
         self._i32(block_list, "block list")
         n, n_heads, d = q.shape
         out = self.empty(n, n_heads * d)
-        n_splits = self.decode_splits(n, n_heads, n_kv)          # few tokens (decode): share a token's blocks out
+        n_splits = 1 if tiles else self.decode_splits(n, n_heads, n_kv)      # few tokens (decode): share a token's blocks out
         scratch = None
         if n_splits > 1:
             scratch = self.empty(self.lib.cpm_decode_attention_scratch_floats(n, n_heads, n_kv, d, n_splits),
@@ -538,7 +545,7 @@ class Ops:
         check(self.lib.cpm_listed_attention_bf16(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(positions),
                                                  _ptr(token_seq), _ptr(slots), _ptr(page_table), page_table.shape[1],
                                                  _ptr(block_list), block_list.shape[-1], n, n_heads, n_kv, d,
-                                                 float(scale), _ptr(scratch), n_splits, self._stream()),
+                                                 float(scale), _ptr(scratch), n_splits, 1 if tiles else 0, self._stream()),
               f"block-list attention (head_dim {d})")
         return out
 

@@ -109,7 +109,8 @@ def _paged_setup(ops, lens, n_kv, d, seed, dtype):
     from cpmcu_b200.cache import Cache
     from cpmcu_b200.parts.base import CacheNeeds
 
-    cache = Cache([CacheNeeds(kv_heads=n_kv, head_dim=d)], max_tokens=64 * 40, dtype=DT[dtype], device="cuda:0")
+    cache = Cache([CacheNeeds(kv_heads=n_kv, head_dim=d)], max_tokens=max(64 * 40, sum(lens) + 64 * 12), dtype=DT[dtype],
+                  device="cuda:0")
     # scramble the page order so that logical and physical pages differ
     junk = cache.open_sequences(3)
     for j, s in enumerate(junk):
@@ -318,12 +319,16 @@ def test_skinny_gemm(M, N, K):
     assert torch.equal(one[0], got32[0])
 
 
+@pytest.mark.parametrize("tiles", [False, True])
 @pytest.mark.parametrize("n_heads,n_kv,d", [(4, 1, 32), (6, 2, 64), (32, 2, 128), (20, 1, 64)])
-def test_block_list_attention_against_generic(n_heads, n_kv, d):
-    """The bf16 block-list kernel against the generic kernel given the same lists: random subsets of
-    pages that always hold the token's own page, and tokens whose list says "dense"."""
+def test_block_list_attention_against_generic(n_heads, n_kv, d, tiles):
+    """The bf16 block-list kernels against the generic kernel given the same lists: random subsets of
+    pages that always hold the token's own page, and tokens whose list says "dense".  ``tiles``: the kernel in
+    which eight consecutive tokens share the blocks they bring; the sequences' ends (300, 364) fall inside
+    tiles, so some tiles hold tokens of two sequences, and the longest sequence has more than 32 blocks (a
+    second word of the block masks)."""
     ops = _ops("bfloat16")
-    lens = [300, 64, 700]
+    lens = [300, 64, 2300]
     cache, slots = _paged_setup(ops, lens, n_kv, d, 0, "bfloat16")
     lane = cache.lane(0)
     g = torch.Generator().manual_seed(12)
@@ -349,7 +354,8 @@ def test_block_list_attention_against_generic(n_heads, n_kv, d):
     scale = 1 / math.sqrt(d)
     want = ops.attention_generic(q, lane.k, lane.v, positions.cuda(), token_seq, sl, lane.page_table, n_kv, scale,
                                  block_list=lists, block_size=64)
-    got = ops.listed_attention(q, lane.k, lane.v, positions.cuda(), token_seq, sl, lane.page_table, lists, n_kv, scale)
+    got = ops.listed_attention(q, lane.k, lane.v, positions.cuda(), token_seq, sl, lane.page_table, lists, n_kv, scale,
+                               tiles=tiles)
     assert _err(got, want) < KTOL["bfloat16"]
 
 
