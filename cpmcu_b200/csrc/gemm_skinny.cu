@@ -46,8 +46,9 @@ __device__ __forceinline__ uint4 ld_stream16(const void* p) {
 // keeping the loads of eight K steps in flight instead of saving them for occupancy; with it the kernel
 // went from 4.5 to 6.1 TB/s on the down projection.  With two tiles of token columns (9 to 16 rows) the
 // kernel would take 166 registers and lose the second block per SM, so there the bound is two blocks (53
-// instead of 59 us on the gate_up shape, which is what cuBLAS with the activation kernel takes: the engine
-// leaves more than 8 rows to cuBLAS).
+// instead of 59 us on the gate_up shape, which is what cuBLAS with the activation kernel takes).  Every block
+// reads all the activations from L1 and L2, so the engine hands it 9 to 16 rows only for the products whose
+// blocks * rows * K stays small (QKV, O and down of the 8B sizes, not gate_up or the head).
 template <int NT, int EPI, int kSkinnyWarps>
 __global__ void __launch_bounds__(kSkinnyWarps * 32, NT == 1 ? 1 : 2)
 skinny_gemm_kernel(const bf16* __restrict__ W, const bf16* __restrict__ X, void* __restrict__ out, int M, int N, int K,

@@ -175,13 +175,23 @@ class Ops:
     # decode batch, but the product is bound by streaming the weights, not by the tensor cores: at 16 to 128 rows
     # it takes 51 us on the 8B gate_up shape (5.2 TB/s) with the activation applied in the epilogue, where the library
     # product takes 51 us and the activation kernel 4 us more.
+    SKINNY_WIDE_BYTES = int(os.environ.get("CPMCU_SKINNY_WIDE_MB", "128")) << 20   # see _skinny_ok
     TCGEN05_MIN_ROWS = int(os.environ.get("CPMCU_TCGEN05_MIN_ROWS", "9"))
     MAX_DECODE_SPLITS = int(os.environ.get("CPMCU_MAX_SPLITS", "16"))     # most shares a sequence's pages are cut into
     LISTED_TILE_MIN_TOKENS = int(os.environ.get("CPMCU_LISTED_TILE_MIN", "32"))   # from here on prompt tokens share their blocks in tiles of eight
     SELECT_SCRATCH_BYTES = 64 << 20     # most scratch the sliced block selection may take (raw scores of all pooled keys)
 
-    def _skinny_ok(self, M: int, K: int) -> bool:
-        return self.code == BF16 and M <= self.SKINNY_MAX_ROWS and K % 32 == 0
+    def _skinny_ok(self, M: int, K: int, N: int = 0) -> bool:
+        """The weight-streaming product takes it: up to SKINNY_MAX_ROWS rows always; 9 to 16 rows (two tiles of token
+        columns) while what its blocks read of the activations (every block all of them) stays small: at 16 rows
+        the QKV, O and down products of the 8B sizes (not gate_up and the head), where it took 3.8 % off the step
+        against the library's kernels (which stand outside the chain of dependent launches).  With four and eight tiles (up to 64 rows) the kernel
+        lost to the library at every size tried, the 0.5B sizes included, and is not built."""
+        if self.code != BF16 or K % 32 != 0:
+            return False
+        if M <= self.SKINNY_MAX_ROWS:
+            return True
+        return 0 < N and M <= 16 and -(-N // 16) * M * K * 2 <= self.SKINNY_WIDE_BYTES
 
     def linear(self, a: torch.Tensor, w: torch.Tensor, alpha: float = 1.0,
                out_f32: bool = False, result: bool = False) -> torch.Tensor:
@@ -199,7 +209,7 @@ class Ops:
             check(self.lib.cpm_gemm_f32(_ptr(a), _ptr(w), _ptr(c), M, N, K, K, K, N, float(alpha), self._stream()),
                   "fp32 matrix product")
             return c
-        if self._skinny_ok(M, K):
+        if self._skinny_ok(M, K, N):
             c = make(M, N, dtype=torch.float32 if out_f32 else self.dtype)
             check(self.lib.cpm_gemm_skinny_bf16(_ptr(w), _ptr(a), _ptr(c), M, N, K, float(alpha), 1 if out_f32 else 0,
                                                 self._stream()), "skinny matrix product")
@@ -238,7 +248,7 @@ class Ops:
     def gated_linear(self, a: torch.Tensor, w_gate_up: torch.Tensor, interleave: int) -> torch.Tensor:
         """silu(a @ gate^T) * (a @ up^T) for a gate_up matrix [2*inter, K] laid out as ``interleave`` says."""
         M, K = a.shape
-        if interleave == 8 and self._skinny_ok(M, K) and w_gate_up.shape[0] % 16 == 0:
+        if interleave == 8 and self._skinny_ok(M, K, w_gate_up.shape[0]) and w_gate_up.shape[0] % 16 == 0:
             self._act(a, "linear input")
             self._act(w_gate_up, "gate_up weight")
             h = self.empty(M, w_gate_up.shape[0] // 2)

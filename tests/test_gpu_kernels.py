@@ -319,6 +319,15 @@ def test_skinny_gemm(M, N, K):
     assert torch.equal(one[0], got32[0])
 
 
+def test_which_products_of_9_to_16_rows_take_the_weight_streaming_kernel():
+    """At 9 to 16 rows the engine keeps a product on the weight-streaming kernel while the bytes its blocks read of
+    the activations stay small: the QKV, O and down products of the 8B sizes, not gate_up, the head or 17 rows."""
+    ops = _ops("bfloat16")
+    assert ops._skinny_ok(16, 4096, 4608) and ops._skinny_ok(9, 4096, 4096) and ops._skinny_ok(16, 14336, 4096)
+    assert not ops._skinny_ok(16, 4096, 32768) and not ops._skinny_ok(16, 4096, 73448)
+    assert not ops._skinny_ok(17, 4096, 4608) and ops._skinny_ok(8, 4096, 73448)
+
+
 @pytest.mark.parametrize("tiles", [False, True])
 @pytest.mark.parametrize("n_heads,n_kv,d", [(4, 1, 32), (6, 2, 64), (32, 2, 128), (20, 1, 64)])
 def test_block_list_attention_against_generic(n_heads, n_kv, d, tiles):
