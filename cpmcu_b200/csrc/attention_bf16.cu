@@ -221,26 +221,33 @@ __device__ __forceinline__ void attend_page_smem(TileState<D>& st, const uint4 (
             }
         }
     }
+    // Row maxima of the raw scores; a page that lies wholly at or before both rows' limits (all pages but a
+    // sequence's last) needs no mask.  The scale goes into the exponent's multiply-add: exp2(s * scale - m).
     float mx0 = -INFINITY, mx1 = -INFINITY;
+    if (key0 + kPageTokens - 1 > min(limit0, limit1)) {
+#pragma unroll
+        for (int u = 0; u < 2; ++u)
+#pragma unroll
+            for (int t = 0; t < 4; ++t)
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                    const int key = key0 + 32 * u + 8 * j + 2 * t + e;
+                    if (key > limit0) s[u][t][e] = -INFINITY;
+                    if (key > limit1) s[u][t][2 + e] = -INFINITY;
+                }
+    }
 #pragma unroll
     for (int u = 0; u < 2; ++u)
 #pragma unroll
-        for (int t = 0; t < 4; ++t)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int key = key0 + 32 * u + 8 * j + 2 * t + e;
-                const float a = key <= limit0 ? s[u][t][e] * scale_log2 : -INFINITY;
-                const float b = key <= limit1 ? s[u][t][2 + e] * scale_log2 : -INFINITY;
-                s[u][t][e] = a;
-                s[u][t][2 + e] = b;
-                mx0 = fmaxf(mx0, a);
-                mx1 = fmaxf(mx1, b);
-            }
+        for (int t = 0; t < 4; ++t) {
+            mx0 = fmaxf(mx0, fmaxf(s[u][t][0], s[u][t][1]));
+            mx1 = fmaxf(mx1, fmaxf(s[u][t][2], s[u][t][3]));
+        }
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
-    const float mn0 = fmaxf(st.m[0], mx0), mn1 = fmaxf(st.m[1], mx1);
+    const float mn0 = fmaxf(st.m[0], mx0 * scale_log2), mn1 = fmaxf(st.m[1], mx1 * scale_log2);
     const float use0 = mn0 == -INFINITY ? 0.f : mn0, use1 = mn1 == -INFINITY ? 0.f : mn1;
     const float corr0 = exp2f(st.m[0] - use0), corr1 = exp2f(st.m[1] - use1);
     st.m[0] = mn0;
@@ -252,7 +259,7 @@ __device__ __forceinline__ void attend_page_smem(TileState<D>& st, const uint4 (
         for (int t = 0; t < 4; ++t)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-                const float a = exp2f(s[u][t][e] - use0), b = exp2f(s[u][t][2 + e] - use1);
+                const float a = exp2f(fmaf(s[u][t][e], scale_log2, -use0)), b = exp2f(fmaf(s[u][t][2 + e], scale_log2, -use1));
                 s[u][t][e] = a;
                 s[u][t][2 + e] = b;
                 sum0 += a;
@@ -267,6 +274,8 @@ __device__ __forceinline__ void attend_page_smem(TileState<D>& st, const uint4 (
         st.o[nt][2] *= corr1;
         st.o[nt][3] *= corr1;
     }
+    // Four output tiles at a time: their four value loads, then the four products of the keys' first half and the
+    // four of the second, so that the two products into one accumulator do not follow each other directly.
     const uint32_t vbase = stage + S::kKeyBytes;
 #pragma unroll
     for (int u = 0; u < 2; ++u) {
@@ -275,11 +284,17 @@ __device__ __forceinline__ void attend_page_smem(TileState<D>& st, const uint4 (
         const uint32_t c0 = pack_bf16(s[u][2][0], s[u][2][1]), c1 = pack_bf16(s[u][2][2], s[u][2][3]);
         const uint32_t c2 = pack_bf16(s[u][3][0], s[u][3][1]), c3 = pack_bf16(s[u][3][2], s[u][3][3]);
 #pragma unroll
-        for (int nt = 0; nt < D / 8; ++nt) {
-            const int row = 8 * nt + n;
-            const uint4 vv = lds16(vbase + (row * 8 + ((4 * u + j) ^ ((row & 1) << 2))) * 16);
-            mma_16816(st.o[nt], a0, a1, a2, a3, vv.x, vv.y);
-            mma_16816(st.o[nt], c0, c1, c2, c3, vv.z, vv.w);
+        for (int nt0 = 0; nt0 < D / 8; nt0 += 4) {
+            uint4 vv[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const int row = 8 * (nt0 + i) + n;
+                vv[i] = lds16(vbase + (row * 8 + ((4 * u + j) ^ ((row & 1) << 2))) * 16);
+            }
+#pragma unroll
+            for (int i = 0; i < 4; ++i) mma_16816(st.o[nt0 + i], a0, a1, a2, a3, vv[i].x, vv[i].y);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) mma_16816(st.o[nt0 + i], c0, c1, c2, c3, vv[i].z, vv[i].w);
         }
     }
 }
