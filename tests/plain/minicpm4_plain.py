@@ -5,10 +5,13 @@ float32 on the CPU (or float64 with ``dtype=torch.float64``).  It shares no code
 with the ``cpmcu_b200`` package: it reads the raw ``config.json`` dictionary and a
 dictionary of tensors by checkpoint name.
 
-It rests on the reference's formulas, not on its code being run: OpenBMB/CPM.cu has no
-CPU path (every operation is a CUDA kernel or a cuBLAS call), its extension cannot
-be compiled here (the cutlass submodule its attention needs is absent) and there is
-no GPU on the machine the tests are written on.  Each function cites the file and
+It is written from the reference's formulas: OpenBMB/CPM.cu has no CPU path (every
+operation is a CUDA kernel or a cuBLAS call), so its code cannot run where the tests
+are written.  It was compared with the reference's own code once on a GPU, for dense
+attention with plain rotary encoding: tests/golden holds the logits the unmodified
+reference produced for two tiny random models, with the script that made them, and
+tests/test_cpu_golden.py compares this implementation with them at every run.  The
+sparse path and LongRoPE rest on the formulas alone.  Each function cites the file and
 lines of the reference (paths inside the CPM.cu project) that state its formula.
 Where the reference's behaviour is not followed, the docstring says so and why.
 """

@@ -284,3 +284,46 @@ def test_full_prompt_chunks_through_a_recorded_graph(model_folders, name, make, 
     from cpmcu_b200.registry import architecture
     toy = architecture(toy_arch.NAME)
     assert not Model(toy.model_spec(toy.config_class.from_dict(toy_arch.config_dict())), None).recordable_prompt()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["hd64", "hd128"])
+def test_engine_against_the_reference_golden(tmp_path, name, dtype):
+    """The engine's logits against those the unmodified reference produced for the same tiny random model
+    (tests/golden, made on a GPU by tests/golden/make_reference_golden.py): the prompt in chunks of 32 tokens as
+    the reference ran it, then tokens one by one, in fp32 and in bf16.  The reference computed in bf16."""
+    import json
+    import os
+
+    import numpy as np
+    from safetensors.torch import save_file
+
+    from cpmcu_b200.engine import SequenceStep
+    from tests.golden import make_reference_golden as golden
+
+    data = np.load(os.path.join(os.path.dirname(__file__), "golden", f"reference_{name}.npz"))
+    cfg = json.loads(str(data["config"]))
+    ids, positions = data["ids"].tolist(), data["positions"].tolist()
+    want = torch.from_numpy(data["logits"])
+    folder = str(tmp_path / name)
+    os.makedirs(folder)
+    with open(os.path.join(folder, "config.json"), "w") as f:
+        json.dump(dict(cfg, architectures=["MiniCPMForCausalLM"], model_type="minicpm", torch_dtype="bfloat16"), f)
+    save_file(golden.make_weights(cfg, int(data["seed"])), os.path.join(folder, "model.safetensors"))
+    _, st = _stepper(folder, dtype, chunk_tokens=32)
+    slot = st.open(1)[0]
+    prompt = golden.PROMPT
+    rows = {}
+    wanted = [p for p in positions if p < prompt]
+    got = st.step([SequenceStep(slot, ids[:prompt], wanted)])
+    for p, row in zip(wanted, got):
+        rows[p] = row
+    for at in range(prompt, len(ids)):
+        rows[at] = st.step([SequenceStep(slot, [ids[at]], [0])])[0]
+    st.close(slot)
+    got = torch.stack([rows[p] for p in positions]).float().cpu()
+    err = float((got - want).abs().max() / want.abs().max())
+    assert err < 2e-2, (name, dtype, err)
+    top2 = want.topk(2, dim=-1).values
+    firm = (top2[:, 0] - top2[:, 1]) > 4e-2 * float(want.abs().max())
+    assert torch.equal(got.argmax(-1)[firm], want.argmax(-1)[firm])
