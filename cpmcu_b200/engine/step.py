@@ -159,8 +159,11 @@ class Stepper:
                 if len(chunks) == 1 and len(rows_here) == len(wanted):
                     logits = out
                 else:
-                    idx = torch.tensor([k for k, _ in rows_here], dtype=torch.int64, device=self.ops.device)
-                    logits.index_copy_(0, idx, out)
+                    ks = [k for k, _ in rows_here]
+                    if ks == list(range(ks[0], ks[0] + len(ks))):          # the usual case: one plain copy
+                        logits[ks[0]:ks[0] + len(ks)].copy_(out)
+                    else:
+                        logits.index_copy_(0, torch.tensor(ks, dtype=torch.int64, device=self.ops.device), out)
         for s, h, n in zip(batch, history, lengths):
             self.cache.set_length(s.slot, h + n)
         return logits
