@@ -120,8 +120,8 @@ def reference_arm(steps: int, warmup: int) -> int:
     header tree that ships with an installed package, built with CPMCU_CUDA_ARCH=100 CPMCU_DTYPE=bf16."""
     ref = os.path.join(ROOT, "baseline", "_ref")
     if not os.path.isdir(os.path.join(ref, "cpmcu")):
-        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref holds no installed reference (see DESIGN.md "
-                          "for the install command; it needs the CUTLASS headers of an installed package)"}))
+        print(json.dumps({"impl": "reference", "unavailable": "baseline/_ref holds no installed reference (pip install --no-index --no-build-isolation "
+                          "--target baseline/_ref of a copy of the reference whose src/cutlass holds CUTLASS headers)"}))
         return 0
     cfgd = dict(MODEL)
     cfgd["rope_scaling"] = {"rope_type": "longrope", "long_factor": long_factors(64), "short_factor": [1.0] * 64,

@@ -266,16 +266,16 @@ def test_full_prompt_chunks_through_a_recorded_graph(model_folders, name, make, 
     st = Stepper(model, cache, chunk_tokens=chunk, graph_prompts=True)
     assert st.graph_prompts
     limit = min(cfg.max_position_embeddings, 330) if name != "tiny_a" else 120
-    for round_, n in enumerate((limit, limit - 70, limit - 3)):
-        ids = helpers.random_ids(cfg.vocab_size, n + 3, 300 + round_)
+    for pass_, n in enumerate((limit, limit - 70, limit - 3)):
+        ids = helpers.random_ids(cfg.vocab_size, n + 3, 300 + pass_)
         places = sorted(p for p in {0, 5, 63, 64, 65, 127, 128, n // 2, n - 2, n - 1} if p < n)
         slot = st.open(1)[0]
         got = st.step([SequenceStep(slot, ids[:n], places)])
-        helpers.check_rows(got, folder, ids, places, dtype, (name, round_, "prompt"))
+        helpers.check_rows(got, folder, ids, places, dtype, (name, pass_, "prompt"))
         tail = torch.cat([st.step([SequenceStep(slot, ids[i:i + 1], [0])]) for i in range(n, n + 3)])
-        helpers.check_rows(tail, folder, ids, range(n, n + 3), dtype, (name, round_, "decoded"))
-        if round_ != 1:
-            st.close(slot)                                    # round 2 runs beside round 1's sequence, in another slot
+        helpers.check_rows(tail, folder, ids, range(n, n + 3), dtype, (name, pass_, "decoded"))
+        if pass_ != 1:
+            st.close(slot)                                    # the third pass runs beside the second pass's sequence, in another slot
     assert len(st.prompt_graphs) >= 1 and all(k[0] == chunk and k[2] == 1024 for k in st.prompt_graphs)
     st.ops.raise_on_kernel_error()
     # a model with a part that reads the batch on the host keeps to the ordinary way
