@@ -387,6 +387,331 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     }
 }
 
+
+// ---------------------------------------------------------------------------
+// Attention over listed key blocks (block-sparse) for the tokens of prompt chunks, head size 128, 16 query heads
+// per key/value head: the 128 rows of the MMA tile are 8 consecutive tokens x the 16 heads of their group.
+// ---------------------------------------------------------------------------
+// Every token has its own list of 64-key blocks (the selection's choice, or "all" below the dense length).  The
+// eight tokens of a block of threads share what is brought: each token's blocks are marked in a bit mask, the union
+// of the masks is walked in rising order, and every block of the union is one step: K and V page by TMA, S = Q K^T
+// (128 x 64) into tensor memory, the softmax threads (one per row) mask the rows whose token did not list the
+// block and the keys behind the token's position, write P as bf16 over S, and O += P V takes P from tensor
+// memory.  One S and one O accumulator (256 TMEM columns) and 105 KB of shared memory let two blocks share an SM:
+// one block's tensor-core work runs while the other's rows are in the softmax.  Rows of tokens that did not list
+// a block cost the tensor cores their share all the same (on random data the union of eight lists of 96 blocks
+// holds about 185), but a step of 64 keys is 0.3 us of tensor work against 2 us for a warp of the mma.sync kernel.
+// A tile whose tokens belong to several sequences (packed prompts) is done in passes, one per sequence.
+// Waits are bounded as in the kernel above.
+constexpr int kSparseTokens = 8;
+constexpr int kSparseThreads = 192;                      // warps 0-3: softmax, one row a thread; 4: MMA issue; 5: TMA
+constexpr int kSparseStages = 2;
+constexpr int kSparseTmemCols = 256;                     // S (and P over it) at columns 0-63, O at 64-191
+constexpr int kSparseQBytes = 128 * 128 * 2;             // 8 tokens x 16 heads x 128
+constexpr int kSparseKvBytes = 2 * 64 * 128 * 2;         // a key page and a value page
+constexpr uint32_t kSparseIdescQK = instr_desc_bf16(128, 64);
+constexpr uint32_t kSparseIdescPV = instr_desc_bf16(128, 128);
+
+struct UnionCursor {             // walks the set bits of a mask in rising order
+    int word;
+    unsigned bits;
+};
+__device__ __forceinline__ int next_listed(UnionCursor& c, const unsigned* __restrict__ mask, int words) {
+    while (c.bits == 0u) {
+        if (++c.word >= words) return -1;
+        c.bits = mask[c.word];
+    }
+    const int b = __ffs(c.bits) - 1;
+    c.bits &= c.bits - 1u;
+    return c.word * 32 + b;
+}
+
+__global__ void __launch_bounds__(kSparseThreads, 2)
+listed_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                                const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out,
+                                const int* __restrict__ positions, const int* __restrict__ token_seq,
+                                const int* __restrict__ slots, const int* __restrict__ page_table, int max_pages,
+                                int n_pages, const int* __restrict__ block_list, int list_cap, int n_tokens, int n_heads,
+                                int n_kv, float scale_log2, int words) {
+    constexpr int kD = 128;
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t q_full, kv_full[kSparseStages], kv_empty[kSparseStages], s_full, p_full, o_full;
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t0 = blockIdx.x * kSparseTokens, kvh = blockIdx.y;
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t q_smem = base, kv_smem = base + kSparseQBytes;
+    unsigned* all = reinterpret_cast<unsigned*>(smem_raw + (base - smem_u32(smem_raw)) + kSparseQBytes + kSparseStages * kSparseKvBytes);
+    unsigned* mine = all + words;                                          // [tokens][words]
+
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&q_full), 1);
+        for (int s = 0; s < kSparseStages; ++s) {
+            mbar_init(smem_u32(&kv_full[s]), 1);
+            mbar_init(smem_u32(&kv_empty[s]), 1);
+        }
+        mbar_init(smem_u32(&s_full), 1);
+        mbar_init(smem_u32(&p_full), 4);                                   // the four softmax warps
+        mbar_init(smem_u32(&o_full), 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 4) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;"
+                     :: "r"(smem_u32(&tmem_base_slot)), "r"((uint32_t)kSparseTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    tcgen05_fence_after();
+    const uint32_t tmem_base = tmem_base_slot;
+    pdl_launch_dependents();
+    pdl_wait();
+
+    auto fail = [&](int code) {
+        atomicCAS(&g_error, 0, code);
+        atomicExch(&abort_flag, 1);
+    };
+    auto aborted = [&]() { return *(volatile int*)&abort_flag != 0; };
+
+    // the softmax thread's row: token r / 16 of the tile, head r % 16 of the group
+    const int r = (warp & 3) * 32 + lane;
+    const int my_token = r >> 4;
+    const bool row_live = warp < 4 && t0 + my_token < n_tokens;
+    const int my_pos = row_live ? positions[t0 + my_token] : -1;
+    const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
+    const uint32_t s_addr = lane_base, o_addr = lane_base + 64;
+    float m_ref = -INFINITY, l = 0.f;
+
+    if (warp == 5 && lane == 0) {                                          // the queries: two halves of 64 dims
+        mbar_expect_tx(smem_u32(&q_full), kSparseQBytes);
+        for (int half = 0; half < 2; ++half)
+            tma_load_3d(q_smem + half * (kSparseQBytes / 2), &map_q, smem_u32(&q_full), half * 64, kvh * 16, t0);
+    }
+
+    const int tile_tokens = min(kSparseTokens, n_tokens - t0);
+    uint32_t it = 0;                                                       // steps so far, all passes
+    bool ok = true;
+    for (int first = 0; first < tile_tokens;) {                           // one pass per sequence in the tile
+        const int seq = token_seq[t0 + first];
+        int end = first + 1;
+        while (end < tile_tokens && token_seq[t0 + end] == seq) ++end;
+        const int* pages = page_table + (int64_t)slots[seq] * max_pages;
+        // ---- the tokens' masks and their union ----
+        for (int i = threadIdx.x; i < (kSparseTokens + 1) * words; i += kSparseThreads) all[i] = 0u;
+        __syncthreads();
+        for (int tl = first + warp; tl < end; tl += kSparseThreads / 32) {
+            unsigned* m = mine + tl * words;
+            const int* list = block_list + ((int64_t)(t0 + tl) * n_kv + kvh) * list_cap;
+            if (list[0] == -2) {                                          // "dense": every block up to the token's own
+                const int last = positions[t0 + tl] / kPageTokens;
+                for (int w = lane; w <= (last >> 5) && w < words; w += 32)
+                    m[w] = w < (last >> 5) ? 0xffffffffu : (0xffffffffu >> (31 - (last & 31)));
+            } else {
+                for (int b0 = 0; b0 < list_cap; b0 += 32) {              // the list ends at its first negative entry
+                    const int i = b0 + lane;
+                    const int b = i < list_cap ? list[i] : -1;
+                    const unsigned ended = __ballot_sync(0xffffffffu, b < 0);
+                    const int n_valid = ended ? __ffs(ended) - 1 : 32;
+                    if (lane < n_valid && (b >> 5) < words) atomicOr(&m[b >> 5], 1u << (b & 31));
+                    if (ended) break;
+                }
+            }
+        }
+        __syncthreads();
+        for (int w = threadIdx.x; w < words; w += kSparseThreads) {
+            unsigned u = 0u;
+            for (int k = first; k < end; ++k) u |= mine[k * words + w];
+            all[w] = u;
+        }
+        __syncthreads();
+        int n_steps = 0;                                                   // the same number in every thread
+        for (int w = 0; w < words; ++w) n_steps += __popc(all[w]);
+        ok = ok && !aborted();
+        if (!ok) n_steps = 0;
+
+        if (warp == 5) {
+            // ---- TMA producer ----
+            if (lane == 0) {
+                UnionCursor cursor{-1, 0u};
+                for (int j = 0; j < n_steps; ++j, ++it) {
+                    const int b = next_listed(cursor, all, words);
+                    const uint32_t s = it & 1u, use = it >> 1;
+                    if (use > 0 && !mbar_wait_bounded(smem_u32(&kv_empty[s]), (use - 1) & 1u)) { fail(ERR_K_EMPTY); ok = false; break; }
+                    if (aborted()) { ok = false; break; }
+                    const int page = min(max(CPM_PAGE(pages, b, max_pages), 0), n_pages - 1);
+                    const uint32_t bar = smem_u32(&kv_full[s]), dst = kv_smem + s * kSparseKvBytes;
+                    mbar_expect_tx(bar, kSparseKvBytes);
+                    tma_load_2d(dst, &map_k, bar, 0, (page * n_kv + kvh) * kPageTokens);
+                    tma_load_2d(dst + 64 * 64 * 2, &map_k, bar, 64, (page * n_kv + kvh) * kPageTokens);
+                    tma_load_2d(dst + kSparseKvBytes / 2, &map_v, bar, 0, (page * n_kv + kvh) * kD);
+                }
+            }
+        } else if (warp == 4) {
+            // ---- MMA issue ----
+            if (lane == 0 && n_steps > 0) {
+                auto issue_qk = [&](uint32_t s) {
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        const uint64_t da = smem_desc_sw128(q_smem + half * (kSparseQBytes / 2));
+                        const uint64_t db = smem_desc_sw128(kv_smem + s * kSparseKvBytes + half * (64 * 64 * 2));
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            tcgen05_mma_f16(tmem_base, da + 2 * k, db + 2 * k, kSparseIdescQK, (half | k) != 0);
+                    }
+                };
+                auto issue_pv = [&](uint32_t s, bool accumulate) {
+                    const uint64_t db = smem_desc_sw128(kv_smem + s * kSparseKvBytes + kSparseKvBytes / 2);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        tcgen05_mma_f16_ts(tmem_base + 64, tmem_base + k * 8, db + 2 * k, kSparseIdescPV, accumulate || k != 0);
+                };
+                if (it == 0 && !mbar_wait_bounded(smem_u32(&q_full), 0)) { fail(ERR_Q); ok = false; }
+                if (ok && !mbar_wait_bounded(smem_u32(&kv_full[it & 1u]), (it >> 1) & 1u)) { fail(ERR_K_FULL); ok = false; }
+                if (ok) {
+                    tcgen05_fence_after();
+                    issue_qk(it & 1u);
+                    tcgen05_commit(smem_u32(&s_full));
+                }
+                for (int j = 0; ok && j < n_steps; ++j, ++it) {
+                    if (aborted()) { ok = false; break; }
+                    if (!mbar_wait_bounded(smem_u32(&p_full), it & 1u)) { fail(ERR_P_FULL); ok = false; break; }
+                    tcgen05_fence_after();
+                    issue_pv(it & 1u, it > 0);
+                    tcgen05_commit(smem_u32(&kv_empty[it & 1u]));          // the stage is free when this product is done
+                    if (j + 1 < n_steps) {
+                        const uint32_t nx = it + 1;
+                        if (!mbar_wait_bounded(smem_u32(&kv_full[nx & 1u]), (nx >> 1) & 1u)) { fail(ERR_K_FULL); ok = false; break; }
+                        tcgen05_fence_after();
+                        issue_qk(nx & 1u);
+                        tcgen05_commit(smem_u32(&s_full));                 // also covers the product into O before it
+                    }
+                }
+            } else {
+                it += n_steps;
+            }
+            it = __shfl_sync(0xffffffffu, it, 0);
+        } else {
+            // ---- softmax: one row a thread ----
+            const bool member = row_live && my_token >= first && my_token < end;
+            const unsigned* my_mask = mine + my_token * words;
+            UnionCursor cursor{-1, 0u};
+            for (int j = 0; j < n_steps; ++j, ++it) {
+                const int b = next_listed(cursor, all, words);
+                if (__any_sync(0xffffffffu, aborted())) { ok = false; break; }
+                if (!__all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&s_full), it & 1u))) {
+                    if (lane == 0) fail(ERR_S_FULL);
+                    ok = false;
+                    break;
+                }
+                tcgen05_fence_after();
+                uint32_t v[2][32];
+                tmem_load_32cols(s_addr, v[0]);
+                tmem_load_32cols(s_addr + 32, v[1]);
+                tmem_load_wait();
+                const bool listed = member && ((my_mask[b >> 5] >> (b & 31)) & 1u);
+                const int visible = listed ? min(64, my_pos - b * kPageTokens + 1) : 0;      // keys of the block this row sees
+                if (visible < 64) {
+#pragma unroll
+                    for (int c = 0; c < 2; ++c)
+#pragma unroll
+                        for (int e = 0; e < 32; ++e)
+                            if (c * 32 + e >= visible) v[c][e] = 0xff800000u;              // -inf
+                }
+                float mx = -INFINITY;
+#pragma unroll
+                for (int c = 0; c < 2; ++c)
+#pragma unroll
+                    for (int e = 0; e < 32; e += 2) mx = max3(mx, __uint_as_float(v[c][e]), __uint_as_float(v[c][e + 1]));
+                const float m_new = mx * scale_log2;
+                const bool grow = m_new > m_ref + kRescaleThreshold || (m_ref == -INFINITY && m_new > -INFINITY);
+                if (__any_sync(0xffffffffu, grow)) {
+                    const float alpha = grow ? ex2(m_ref - m_new) : 1.f;             // 0 the first time
+                    l *= alpha;
+                    if (it > 0) {
+#pragma unroll 1
+                        for (int c = 0; c < kD / 32; ++c) {
+                            uint32_t o[32];
+                            tmem_load_32cols(o_addr + c * 32, o);
+                            tmem_load_wait();
+#pragma unroll
+                            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+                            tmem_store_32cols(o_addr + c * 32, o);
+                        }
+                    }
+                    if (grow) m_ref = m_new;
+                }
+                const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+                float2 sum2 = make_float2(0.f, 0.f);
+                const float2 scale2 = make_float2(scale_log2, scale_log2), minus_m2 = make_float2(-m_use, -m_use);
+                uint32_t packed[32];
+#pragma unroll
+                for (int e = 0; e < 32; ++e) {
+                    const float2 x = fma2(make_float2(__uint_as_float(v[e >> 4][(2 * e) & 31]),
+                                                      __uint_as_float(v[e >> 4][(2 * e + 1) & 31])), scale2, minus_m2);
+                    const float2 pp = make_float2(ex2(x.x), ex2(x.y));
+                    sum2 = add2(sum2, pp);
+                    packed[e] = pack_bf16(pp.x, pp.y);
+                }
+                tmem_store_32cols(s_addr, packed);
+                l += sum2.x + sum2.y;
+                tmem_store_wait();
+                tcgen05_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(smem_u32(&p_full));
+            }
+        }
+        if (!ok) atomicExch(&abort_flag, 1);
+        __syncthreads();                                                   // the masks are free for the next pass
+        if (aborted()) break;
+        // every role has counted the pass's steps
+        if (warp == 5) it = __shfl_sync(0xffffffffu, it, 0);
+        first = end;
+    }
+
+    if (warp == 4 && lane == 0 && !aborted() && it > 0) tcgen05_commit(smem_u32(&o_full));      // after the tile's last product
+    if (warp < 4 && !aborted() && it > 0) {
+        // ---- epilogue: the rows' results ----
+        if (!__all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&o_full), 0))) {
+            if (lane == 0) fail(ERR_O_FULL);
+        } else {
+            tcgen05_fence_after();
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            bf16* orow = out + ((int64_t)min(t0 + my_token, n_tokens - 1) * n_heads + kvh * 16 + (r & 15)) * kD;
+#pragma unroll 1
+            for (int c = 0; c < kD / 32; ++c) {
+                uint32_t o[32];
+                tmem_load_32cols(o_addr + c * 32, o);
+                tmem_load_wait();
+                if (row_live) {
+#pragma unroll
+                    for (int e = 0; e < 32; e += 8) {
+                        uint4 w;
+                        w.x = pack_bf16(__uint_as_float(o[e]) * inv, __uint_as_float(o[e + 1]) * inv);
+                        w.y = pack_bf16(__uint_as_float(o[e + 2]) * inv, __uint_as_float(o[e + 3]) * inv);
+                        w.z = pack_bf16(__uint_as_float(o[e + 4]) * inv, __uint_as_float(o[e + 5]) * inv);
+                        w.w = pack_bf16(__uint_as_float(o[e + 6]) * inv, __uint_as_float(o[e + 7]) * inv);
+                        *reinterpret_cast<uint4*>(orow + c * 32 + e) = w;
+                    }
+                }
+            }
+        }
+    }
+    if (warp == 5 && lane == 0 && aborted()) {
+        // copies that nobody consumed: wait for them (bounded), so that none is in flight at the exit
+        mbar_wait_bounded(smem_u32(&q_full), 0);
+        for (uint32_t j = it > kSparseStages ? it - kSparseStages : 0; j < it; ++j)
+            mbar_wait_bounded(smem_u32(&kv_full[j & 1u]), (j >> 1) & 1u);
+    }
+    tcgen05_fence_before();
+    __syncthreads();
+    if (warp == 4) {
+        tcgen05_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" :: "r"(tmem_base), "r"((uint32_t)kSparseTmemCols) : "memory");
+    }
+}
+
 }  // namespace fa5
 
 namespace fa5 {
@@ -458,6 +783,43 @@ CPM_API int cpm_prefill_attention_tcgen05(const void* q, const void* k_cache, co
                                 n_tokens, n_pages, n_heads, n_kv, scale, scratch, n_splits, stream);
     return fa5::launch<64>(q, k_cache, v_cache, out, tile_seq, tile_row, n_tiles, cu_q, kv_len, slots, page_table, max_pages,
                            n_tokens, n_pages, n_heads, n_kv, scale, scratch, n_splits, stream);
+}
+
+// Block-list attention of prompt tokens on the tensor cores (see listed_attention_tcgen05_kernel): q, out [tokens, heads,
+// 128] bf16, 16 query heads per key/value head, block_list int32 [tokens, kv_heads, list_cap] of 64-token blocks
+// (first entry -2 = all blocks up to the token's own).  Other shapes, and page tables too wide for the masks to fit
+// beside the tiles (more than cpm_listed_attention_tcgen05_max_pages() pages a sequence), are refused: the caller
+// takes the mma.sync kernel for them.
+CPM_API int cpm_listed_attention_tcgen05_max_pages() {
+    return ((110 * 1024 - 1024 - fa5::kSparseQBytes - fa5::kSparseStages * fa5::kSparseKvBytes) / ((fa5::kSparseTokens + 1) * 4)) * 32;
+}
+
+CPM_API int cpm_listed_attention_tcgen05(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                         const int* positions, const int* token_seq, const int* slots,
+                                         const int* page_table, int max_pages, int n_pages, const int* block_list,
+                                         int list_cap, int n_tokens, int n_heads, int n_kv, int d, float scale,
+                                         cudaStream_t stream) {
+    using namespace fa5;
+    if (n_tokens <= 0) return CPM_OK;
+    if (d != 128 || n_kv <= 0 || n_heads != 16 * n_kv || !block_list || list_cap < 1 || n_pages <= 0 || n_kv > 65535 ||
+        ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 15))
+        return CPM_BAD_ARGUMENT;
+    const int words = (max_pages + 31) / 32;
+    const int smem = 1024 + kSparseQBytes + kSparseStages * kSparseKvBytes + (kSparseTokens + 1) * words * 4;
+    if (smem > 110 * 1024) return CPM_BAD_ARGUMENT;                  // two blocks share an SM's shared memory
+    CUtensorMap map_q, map_k, map_v;
+    if (!tc5::make_map_3d_bf16(&map_q, q, 128, (uint64_t)n_heads, (uint64_t)n_tokens, 128 * 2, (uint64_t)n_heads * 128 * 2, 64, 16,
+                               kSparseTokens) ||
+        !tc5::make_map_2d_bf16(&map_k, k_cache, (uint64_t)n_pages * n_kv * kPageTokens, 128, 128 * 2, 64, kPageTokens) ||
+        !tc5::make_map_2d_bf16(&map_v, v_cache, (uint64_t)n_pages * n_kv * 128, kPageTokens, kPageTokens * 2, 64, 128))
+        return CPM_BAD_ARGUMENT;
+    auto kern = listed_attention_tcgen05_kernel;
+    static bool configured[kMaxDevices] = {};
+    if (int st = ensure_dynamic_smem(kern, 110 * 1024, configured)) return st;
+    cpm_launch(kLaunchAttention, kern, dim3((n_tokens + kSparseTokens - 1) / kSparseTokens, n_kv), dim3(kSparseThreads),
+               (size_t)smem, stream, map_q, map_k, map_v, (bf16*)out, positions, token_seq, slots, page_table, max_pages, n_pages,
+               block_list, list_cap, n_tokens, n_heads, n_kv, scale * 1.4426950408889634f, words);
+    return launch_status();
 }
 
 // Error code recorded by the kernel since the last call (0 = none), and reset.  Synchronises the device.

@@ -30,6 +30,10 @@ class _NoLibrary:
     def cpm_select_blocks_scratch_floats(n_tokens, n_kv, max_entries, n_slices):
         return n_tokens * n_kv * (max_entries * 16 + n_slices * 32)
 
+    @staticmethod
+    def cpm_listed_attention_tcgen05_max_pages():
+        return 11808
+
     def __getattr__(self, name):
         return lambda *args: 0
 
@@ -44,7 +48,7 @@ class DryOps(Ops):
         self.lib = _NoLibrary()
         self.element_size = 4 if dtype == torch.float32 else 2
         self.sm_count = sm_count
-        self.use_tcgen05 = self.use_tcgen05_attention = True
+        self.use_tcgen05 = self.use_tcgen05_attention = self.use_tcgen05_listed = True
         self.tcgen05_pair = False
         arena = Arena(None, None)
         self.workspace = Workspace(arena.carve("persistent", None), [arena.carve("frame0", None), arena.carve("frame1", None)])

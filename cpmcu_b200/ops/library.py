@@ -48,6 +48,7 @@ _SIGNATURES = {
     "cpm_prefill_attention_tcgen05": [_P, _P, _P, _P, _P, _P, c_int, _P, _P, _P, _P, c_int, c_int, c_int, c_int, c_int, c_int,
                                       c_float, _P, c_int, _P],
     "cpm_gemm_bf16_tcgen05_pair": [_P, _P, _P, c_int, c_int, c_int, c_int, c_int, _P],
+    "cpm_listed_attention_tcgen05": [_P, _P, _P, _P, _P, _P, _P, _P, c_int, c_int, _P, c_int, c_int, c_int, c_int, c_int, c_float, _P],
     "cpm_sample_rows": [_P, c_int64, c_int, c_int, _P, _P, _P, c_uint64, _P, _P, _P],
 }
 
@@ -109,6 +110,8 @@ def load() -> ctypes.CDLL:
         lib.cpm_select_blocks_error.restype = c_int
         lib.cpm_listed_tile_error.argtypes = []
         lib.cpm_listed_tile_error.restype = c_int
+        lib.cpm_listed_attention_tcgen05_max_pages.argtypes = []
+        lib.cpm_listed_attention_tcgen05_max_pages.restype = c_int
         lib.cpm_decode_attention_scratch_floats.argtypes = [c_int, c_int, c_int, c_int, c_int]
         lib.cpm_decode_attention_scratch_floats.restype = c_int64
         for name, argtypes in _SIGNATURES.items():

@@ -61,6 +61,7 @@ class Ops:
         self.sm_count = torch.cuda.get_device_properties(self.device).multi_processor_count
         self.use_tcgen05 = os.environ.get("CPMCU_TCGEN05", "1") != "0"
         self.use_tcgen05_attention = os.environ.get("CPMCU_TCGEN05_ATTENTION", "1") != "0"
+        self.use_tcgen05_listed = os.environ.get("CPMCU_TCGEN05_LISTED", "1") != "0"      # block-list attention of prompts
         self.tcgen05_pair = os.environ.get("CPMCU_TCGEN05_PAIR", "0") == "1"      # pairs of blocks on 256-row tiles
         self.workspace = None       # cpmcu_b200.memory.Workspace: where a step's intermediates live (None: torch's allocator)
         self.weights = None         # cpmcu_b200.memory.Region that holds the weights (None: torch's allocator)
@@ -547,6 +548,15 @@ class Ops:
         self._i32(block_list, "block list")
         n, n_heads, d = q.shape
         out = self.empty(n, n_heads * d)
+        if (tiles and self.use_tcgen05_attention and self.use_tcgen05_listed and d == 128 and n_heads == 16 * n_kv
+                and page_table.shape[1] <= self.lib.cpm_listed_attention_tcgen05_max_pages()):
+            # prompt tokens of the long-context shape: eight tokens x sixteen heads are one tensor-core tile
+            check(self.lib.cpm_listed_attention_tcgen05(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(positions),
+                                                        _ptr(token_seq), _ptr(slots), _ptr(page_table), page_table.shape[1],
+                                                        k_cache.shape[0], _ptr(block_list), block_list.shape[-1], n, n_heads,
+                                                        n_kv, d, float(scale), self._stream()),
+                  "block-list attention on tcgen05")
+            return out
         n_splits = 1 if tiles else self.decode_splits(n, n_heads, n_kv)      # few tokens (decode): share a token's blocks out
         scratch = None
         if n_splits > 1:

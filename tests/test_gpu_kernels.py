@@ -328,15 +328,19 @@ def test_which_products_of_9_to_16_rows_take_the_weight_streaming_kernel():
     assert not ops._skinny_ok(17, 4096, 4608) and ops._skinny_ok(8, 4096, 73448)
 
 
-@pytest.mark.parametrize("tiles", [False, True])
-@pytest.mark.parametrize("n_heads,n_kv,d", [(4, 1, 32), (6, 2, 64), (32, 2, 128), (20, 1, 64)])
+@pytest.mark.parametrize("tiles", ["no", "mma", "tcgen05"])
+@pytest.mark.parametrize("n_heads,n_kv,d", [(4, 1, 32), (6, 2, 64), (32, 2, 128), (20, 1, 64), (16, 1, 128)])
 def test_block_list_attention_against_generic(n_heads, n_kv, d, tiles):
     """The bf16 block-list kernels against the generic kernel given the same lists: random subsets of
-    pages that always hold the token's own page, and tokens whose list says "dense".  ``tiles``: the kernel in
-    which eight consecutive tokens share the blocks they bring; the sequences' ends (300, 364) fall inside
-    tiles, so some tiles hold tokens of two sequences, and the longest sequence has more than 32 blocks (a
-    second word of the block masks)."""
+    pages that always hold the token's own page, and tokens whose list says "dense".  ``tiles``: the kernels in
+    which consecutive tokens share the blocks that are brought ("mma": seven tokens on mma.sync; "tcgen05": eight
+    tokens x sixteen heads as one tensor-core tile, which takes head size 128 with sixteen heads per key/value
+    head and leaves the other shapes to the first); the sequences' ends (300, 364) fall inside tiles, so some
+    tiles hold tokens of two sequences, and the longest sequence has more than 32 blocks (a second word of the
+    block masks)."""
+    from cpmcu_b200.ops import library
     ops = _ops("bfloat16")
+    ops.use_tcgen05_listed = tiles == "tcgen05"
     lens = [300, 64, 2300]
     cache, slots = _paged_setup(ops, lens, n_kv, d, 0, "bfloat16")
     lane = cache.lane(0)
@@ -364,7 +368,9 @@ def test_block_list_attention_against_generic(n_heads, n_kv, d, tiles):
     want = ops.attention_generic(q, lane.k, lane.v, positions.cuda(), token_seq, sl, lane.page_table, n_kv, scale,
                                  block_list=lists, block_size=64)
     got = ops.listed_attention(q, lane.k, lane.v, positions.cuda(), token_seq, sl, lane.page_table, lists, n_kv, scale,
-                               tiles=tiles)
+                               tiles=tiles != "no")
+    ops.use_tcgen05_listed = True
+    ops.raise_on_kernel_error()
     assert _err(got, want) < KTOL["bfloat16"]
 
 
