@@ -610,20 +610,24 @@ listed_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const
                 tmem_load_32cols(s_addr, v[0]);
                 tmem_load_32cols(s_addr + 32, v[1]);
                 tmem_load_wait();
+                // A row whose token did not list the block takes no part in the step's arithmetic: its P is zero.  (The
+                // loads and stores of tensor memory are the warp's, so its lanes still go through them.)
                 const bool listed = member && ((my_mask[b >> 5] >> (b & 31)) & 1u);
                 const int visible = listed ? min(64, my_pos - b * kPageTokens + 1) : 0;      // keys of the block this row sees
-                if (visible < 64) {
+                float mx = -INFINITY;
+                if (visible > 0) {
+                    if (visible < 64) {
+#pragma unroll
+                        for (int c = 0; c < 2; ++c)
+#pragma unroll
+                            for (int e = 0; e < 32; ++e)
+                                if (c * 32 + e >= visible) v[c][e] = 0xff800000u;          // -inf
+                    }
 #pragma unroll
                     for (int c = 0; c < 2; ++c)
 #pragma unroll
-                        for (int e = 0; e < 32; ++e)
-                            if (c * 32 + e >= visible) v[c][e] = 0xff800000u;              // -inf
+                        for (int e = 0; e < 32; e += 2) mx = max3(mx, __uint_as_float(v[c][e]), __uint_as_float(v[c][e + 1]));
                 }
-                float mx = -INFINITY;
-#pragma unroll
-                for (int c = 0; c < 2; ++c)
-#pragma unroll
-                    for (int e = 0; e < 32; e += 2) mx = max3(mx, __uint_as_float(v[c][e]), __uint_as_float(v[c][e + 1]));
                 const float m_new = mx * scale_log2;
                 const bool grow = m_new > m_ref + kRescaleThreshold || (m_ref == -INFINITY && m_new > -INFINITY);
                 if (__any_sync(0xffffffffu, grow)) {
@@ -642,17 +646,22 @@ listed_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const
                     }
                     if (grow) m_ref = m_new;
                 }
-                const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-                float2 sum2 = make_float2(0.f, 0.f);
-                const float2 scale2 = make_float2(scale_log2, scale_log2), minus_m2 = make_float2(-m_use, -m_use);
                 uint32_t packed[32];
+                float2 sum2 = make_float2(0.f, 0.f);
+                if (visible > 0) {
+                    const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+                    const float2 scale2 = make_float2(scale_log2, scale_log2), minus_m2 = make_float2(-m_use, -m_use);
 #pragma unroll
-                for (int e = 0; e < 32; ++e) {
-                    const float2 x = fma2(make_float2(__uint_as_float(v[e >> 4][(2 * e) & 31]),
-                                                      __uint_as_float(v[e >> 4][(2 * e + 1) & 31])), scale2, minus_m2);
-                    const float2 pp = make_float2(ex2(x.x), ex2(x.y));
-                    sum2 = add2(sum2, pp);
-                    packed[e] = pack_bf16(pp.x, pp.y);
+                    for (int e = 0; e < 32; ++e) {
+                        const float2 x = fma2(make_float2(__uint_as_float(v[e >> 4][(2 * e) & 31]),
+                                                          __uint_as_float(v[e >> 4][(2 * e + 1) & 31])), scale2, minus_m2);
+                        const float2 pp = make_float2(ex2(x.x), ex2(x.y));
+                        sum2 = add2(sum2, pp);
+                        packed[e] = pack_bf16(pp.x, pp.y);
+                    }
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 32; ++e) packed[e] = 0u;
                 }
                 tmem_store_32cols(s_addr, packed);
                 l += sum2.x + sum2.y;
