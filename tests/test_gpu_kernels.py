@@ -363,6 +363,7 @@ def test_block_list_attention_against_generic(n_heads, n_kv, d, tiles):
             others = torch.randperm(own, generator=g)[:min(own, 4)].tolist() if own > 0 else []
             blocks = sorted(set(others + [own]))
             lists[t, h, :len(blocks)] = torch.tensor(blocks, dtype=torch.int32)
+            lists[t, h, len(blocks) + 1:] = 12345                # what lies behind the terminator is not the list's
     lists = lists.cuda()
     scale = 1 / math.sqrt(d)
     want = ops.attention_generic(q, lane.k, lane.v, positions.cuda(), token_seq, sl, lane.page_table, n_kv, scale,
