@@ -66,6 +66,9 @@ def plan_chunks(lengths: Sequence[int], chunk_tokens: int) -> List[Chunk]:
     return chunks
 
 
+MAX_GRAPH_PIECES = 16        # most sequences whose pieces a recorded chunk may hold
+
+
 class _PromptGraph:
     """A recorded prompt chunk: its input buffer [ids | positions | keys after the chunk, slot | wanted rows], the
     buffers that never change (token -> sequence, offsets, query tiles), the graph and its logits."""
@@ -80,10 +83,12 @@ class Stepper:
     """Drives a model over a cache, step by step."""
 
     def __init__(self, model: Model, cache: Cache, chunk_tokens: int = 2048, graph_prompts: bool = False):
-        """``graph_prompts``: a full chunk of one sequence's prompt (``chunk_tokens`` tokens: all chunks of a long prompt
-        but the last) is recorded into a CUDA graph the first time it runs and replayed from then on, whatever the
-        history, because every kernel reads lengths, positions and pages from device memory.  It takes the host out of
-        the prompt (about ten launches a layer otherwise) and needs a model whose parts are all ``recordable_prompt``."""
+        """``graph_prompts``: a full chunk of prompt tokens (``chunk_tokens`` tokens: all chunks of a long prompt but the
+        last, and the full chunks of a batch of prompts, which hold pieces of up to MAX_GRAPH_PIECES sequences) is
+        recorded into a CUDA graph the first time its kind runs and replayed from then on, whatever the sequences and
+        their histories, because every kernel reads lengths, positions, offsets and pages from device memory.  It takes
+        the host out of the prompt (about ten launches a layer otherwise) and needs a model whose parts are all
+        ``recordable_prompt``."""
         self.model = model
         self.cache = cache
         self.ops = model.ops
@@ -91,7 +96,8 @@ class Stepper:
         self.vocab_size = model.spec.vocab_size
         self.taps: Optional[dict] = None      # when set, parts may leave intermediate results in it (ctx.extras["taps"])
         self.graph_prompts = bool(graph_prompts) and model.recordable_prompt()
-        self.prompt_graphs: Dict[Tuple[int, int, int], "_PromptGraph"] = {}
+        # recorded chunks by (tokens, wanted rows, bound on the sequences' lengths, pieces of several sequences?)
+        self.prompt_graphs: Dict[Tuple[int, int, int, bool], "_PromptGraph"] = {}
 
     # ---- sequences ----
     def open(self, n: int) -> List[int]:
@@ -172,7 +178,7 @@ class Stepper:
         """A full chunk of one sequence through its recorded graph; None if there is none yet (the chunk then runs
         the ordinary way, and is recorded afterwards for the chunks to come)."""
         n = int(tokens.shape[0])
-        g = self.prompt_graphs[(n, len(want_rows), self._length_bound(start + n))]
+        g = self.prompt_graphs[(n, len(want_rows), self._length_bound(start + n), False)]
         host = np.concatenate([tokens, np.arange(start, start + n, dtype=np.int32),
                                np.asarray([start + n, slot] + list(want_rows), dtype=np.int32)])
         g.inputs.copy_(torch.from_numpy(host))
@@ -216,21 +222,116 @@ class Stepper:
         with torch.cuda.graph(graph):
             g.logits = body()
         g.graph = graph
-        self.prompt_graphs[(n, n_want, bound)] = g
+        self.prompt_graphs[(n, n_want, bound, False)] = g
 
     def _run_chunk(self, batch, arrays, history, chunk: Chunk, want_rows: List[int]) -> Optional[torch.Tensor]:
-        record = False
-        if self.graph_prompts and self.taps is None and len(chunk.pieces) == 1 and chunk.pieces[0][2] == self.chunk_tokens \
-                and self.chunk_tokens > 1:
-            i, first, count = chunk.pieces[0]
-            bound = self._length_bound(history[i] + first + count)
-            if (count, len(want_rows), bound) in self.prompt_graphs:
+        record = None
+        if self.graph_prompts and self.taps is None and chunk.end - chunk.begin == self.chunk_tokens and self.chunk_tokens > 1 \
+                and len(chunk.pieces) <= MAX_GRAPH_PIECES:
+            packed = len(chunk.pieces) > 1
+            ws = self.ops.workspace
+            if packed and ws is not None and ws.sized_seqs and ws.sized_seqs < MAX_GRAPH_PIECES + 1:
+                return self._run_chunk_eager(batch, arrays, history, chunk, want_rows)      # a workspace made for fewer sequences
+            bound = self._length_bound(max(history[i] + first + count for i, first, count in chunk.pieces))
+            key = (self.chunk_tokens, len(want_rows), bound, packed)
+            if key in self.prompt_graphs:
+                if packed:
+                    return self._graph_packed_chunk(self.prompt_graphs[key], batch, arrays, history, chunk, want_rows)
+                i, first, count = chunk.pieces[0]
                 return self._graph_chunk(arrays[i][first:first + count], batch[i].slot, history[i] + first, want_rows)
-            record = True                     # this one runs the ordinary way (it also warms the kernels up), then the graph is made
+            record = key                      # this one runs the ordinary way (it also warms the kernels up), then the graph is made
         out = self._run_chunk_eager(batch, arrays, history, chunk, want_rows)
-        if record:
-            self._record_chunk(chunk.pieces[0][2], len(want_rows), bound)
+        if record is not None:
+            if record[3]:
+                self._record_packed_chunk(record[0], record[1], record[2])
+            else:
+                self._record_chunk(record[0], record[1], record[2])
         return out
+
+    # ---- full chunks that hold pieces of several sequences ----
+    def _packed_layout(self, n: int, n_want: int) -> Dict[str, Tuple[int, int]]:
+        """Where the parts of a packed chunk's description lie in its input buffer: name -> (offset, length).  The
+        sequence axis has room for MAX_GRAPH_PIECES pieces and one sequence more that is always empty (the query tiles
+        that a chunk does not fill point at it); the tile axis has room for every piece's last, partial tile."""
+        seqs = MAX_GRAPH_PIECES + 1
+        tiles = n // PREFILL_TILE_ROWS + MAX_GRAPH_PIECES
+        layout, at = {}, 0
+        for name, length in (("ids", n), ("positions", n), ("token_seq", n), ("cu_q", seqs + 1), ("kv_len", seqs), ("slot", seqs),
+                             ("want", n_want), ("tile_seq", tiles), ("tile_row", tiles)):
+            layout[name] = (at, length)
+            at += length
+        layout["total"] = (0, at)
+        return layout
+
+    def _record_packed_chunk(self, n: int, n_want: int, bound: int) -> None:
+        """Records the graph of a full chunk of ``n`` tokens from several sequences.  Nothing runs."""
+        ops, dev = self.ops, self.ops.device
+        lay = self._packed_layout(n, n_want)
+        inputs = torch.zeros(lay["total"][1], dtype=torch.int32, device=dev)
+        g = _PromptGraph(inputs, inputs[:0])
+
+        def part(name: str) -> torch.Tensor:
+            o, length = lay[name]
+            return inputs[o:o + length]
+
+        def body():
+            ws = ops.workspace
+            if ws is not None:
+                ws.require(n, MAX_GRAPH_PIECES + 1)
+            ops.begin_step()
+            ctx = StepContext(
+                n_tokens=n, n_seqs=MAX_GRAPH_PIECES + 1, is_decode=False, captured=True, q_lens=[n], kv_lens=[], slots=[],
+                max_q_len=n, max_kv_len=bound, token_ids=part("ids"), positions=part("positions"), token_seq=part("token_seq"),
+                cu_q=part("cu_q"), kv_len_dev=part("kv_len"), slot_dev=part("slot"), cache=self.cache)
+            ctx.q_tiles = (part("tile_seq"), part("tile_row"), lay["tile_seq"][1])
+            ctx.extras["step_begun"] = True
+            return self.model.forward(ctx, part("want") if n_want else None)
+
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            g.logits = body()
+        g.graph = graph
+        self.prompt_graphs[(n, n_want, bound, True)] = g
+
+    def _graph_packed_chunk(self, g: "_PromptGraph", batch, arrays, history, chunk: Chunk, want_rows: List[int]) -> Optional[torch.Tensor]:
+        n = self.chunk_tokens
+        lay = self._packed_layout(n, len(want_rows))
+        host = np.zeros(lay["total"][1], dtype=np.int32)
+        seqs = MAX_GRAPH_PIECES + 1
+        cu_q = np.full(seqs + 1, n, dtype=np.int32)          # sequences behind the chunk's pieces: no tokens, no keys
+        kv_len = np.zeros(seqs, dtype=np.int32)
+        slot = np.full(seqs, batch[chunk.pieces[0][0]].slot, dtype=np.int32)
+        at = 0
+        tile_seq, tile_row = [], []
+        for k, (i, first, count) in enumerate(chunk.pieces):
+            start = history[i] + first
+            o = lay["ids"][0] + at
+            host[o:o + count] = arrays[i][first:first + count]
+            o = lay["positions"][0] + at
+            host[o:o + count] = np.arange(start, start + count, dtype=np.int32)
+            o = lay["token_seq"][0] + at
+            host[o:o + count] = k
+            cu_q[k] = at
+            kv_len[k] = start + count
+            slot[k] = batch[i].slot
+            rows = np.arange(0, count, PREFILL_TILE_ROWS, dtype=np.int32)
+            tile_seq.append(np.full(rows.shape[0], k, dtype=np.int32))
+            tile_row.append(rows)
+            at += count
+        n_tiles = lay["tile_seq"][1]
+        ts = np.full(n_tiles, seqs - 1, dtype=np.int32)       # unused tiles belong to the empty sequence
+        tr = np.zeros(n_tiles, dtype=np.int32)
+        used = np.concatenate(tile_seq)
+        ts[:used.shape[0]] = used
+        tr[:used.shape[0]] = np.concatenate(tile_row)
+        for name, values in (("cu_q", cu_q), ("kv_len", kv_len), ("slot", slot), ("want", np.asarray(want_rows, dtype=np.int32)),
+                             ("tile_seq", ts), ("tile_row", tr)):
+            o, length = lay[name]
+            host[o:o + length] = values
+        g.inputs.copy_(torch.from_numpy(host))
+        g.graph.replay()
+        return None if g.logits is None else g.logits.clone()
 
     def _run_chunk_eager(self, batch, arrays, history, chunk: Chunk, want_rows: List[int]) -> Optional[torch.Tensor]:
         kv_lens: List[int] = []

@@ -327,3 +327,44 @@ def test_engine_against_the_reference_golden(tmp_path, name, dtype):
     top2 = want.topk(2, dim=-1).values
     firm = (top2[:, 0] - top2[:, 1]) > 4e-2 * float(want.abs().max())
     assert torch.equal(got.argmax(-1)[firm], want.argmax(-1)[firm])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name,make,seed", [("tiny_a", configs.tiny_a, 1), ("tiny_e", configs.tiny_e, 6), ("tiny_f", configs.tiny_f, 7)])
+def test_packed_chunks_through_a_recorded_graph(model_folders, name, make, seed, dtype):
+    """A batch of unequal prompts in chunks of 128 packed tokens: full chunks hold pieces of several sequences
+    (58 tokens of one, then 70 of the next, ...) and are recorded into graphs the first time their kind runs.  Three
+    batches with other tokens and other lengths: the first records as it goes, the others replay; every wanted
+    row is compared with the plain implementation.  Unused query tiles and sequences of the recorded shape are
+    empty ones."""
+    from cpmcu_b200.cache import Cache
+    from cpmcu_b200.engine import SequenceStep, Stepper
+    from cpmcu_b200.loading import load_model
+
+    folder = model_folders(name, make(), seed, dtype)
+    _, cfg, model = load_model(folder, dtype)
+    limit = min(cfg.max_position_embeddings, 230)
+    cache = Cache(model.cache_needs(), max_tokens=4096, dtype=model.ops.dtype, device="cuda:0")
+    st = Stepper(model, cache, chunk_tokens=128, graph_prompts=True)
+    replayed = 0
+    for pass_, lens in enumerate(([70, 130, 40, limit, 90], [128, 60, limit, 33, 100, 64], [limit, 5, 200, 120, 70])):
+        lens = [min(n, limit) for n in lens]
+        seqs = [helpers.random_ids(cfg.vocab_size, n, 500 + 10 * pass_ + k) for k, n in enumerate(lens)]
+        slots = st.open(len(lens))
+        wants = [sorted({0, n // 2, n - 1}) for n in lens]
+        before = len(st.prompt_graphs)
+        got = st.step([SequenceStep(s, ids, w) for s, ids, w in zip(slots, seqs, wants)])
+        replayed += before
+        at = 0
+        for k, (ids, w) in enumerate(zip(seqs, wants)):
+            helpers.check_rows(got[at:at + len(w)], folder, ids, w, dtype, (name, pass_, k))
+            at += len(w)
+        tail = st.step([SequenceStep(s, [7], [0]) for s in slots])                  # and the cache is whole: one more token each
+        for k, ids in enumerate(seqs):
+            helpers.check_rows(tail[k:k + 1], folder, list(ids) + [7], [len(ids)], dtype, (name, pass_, k, "next"))
+        for s in slots:
+            st.close(s)
+    assert any(key[3] for key in st.prompt_graphs), "no chunk of several sequences was recorded"
+    assert replayed > 0
+    st.ops.raise_on_kernel_error()
+    st.cache.check_consistent()
