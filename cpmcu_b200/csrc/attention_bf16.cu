@@ -164,7 +164,6 @@ __device__ __forceinline__ uint4 lds16(uint32_t smem_addr) {
     return v;
 }
 
-constexpr int kDecodeWarps = 3;
 constexpr int kDecodeStages = 2;
 
 template <int D>
@@ -173,7 +172,11 @@ struct DecodeSmem {
     static constexpr bool kSwizzleKeys = (kChunksPerKeyRow % 8) == 0;
     static constexpr int kKeyBytes = kPageTokens * D * 2;
     static constexpr int kStageBytes = 2 * kKeyBytes;                      // a key page and a value page
-    static constexpr int kTotal = kDecodeWarps * kDecodeStages * kStageBytes;
+    // Warps of a block, each with its own two stages: three fill an SM's shared memory at head size 128 (196 KB);
+    // smaller heads have smaller pages, and more warps keep as many bytes in flight per SM (six at head size 64:
+    // the 0.5B sizes' decode step at batch 64 went from 2.29 to 1.93 ms).
+    static constexpr int kWarps = D >= 128 ? 3 : D >= 96 ? 4 : D >= 64 ? 6 : 8;
+    static constexpr int kTotal = kWarps * kDecodeStages * kStageBytes;
 };
 
 // Copies one key page and one value page (both contiguous in global memory) into a stage.
@@ -370,7 +373,7 @@ __device__ __forceinline__ void put_new_token(unsigned char* stage, const bf16* 
 }
 
 template <int D>
-__global__ void __launch_bounds__(kDecodeWarps * 32, 1)
+__global__ void __launch_bounds__(DecodeSmem<D>::kWarps * 32, 1)
 decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                         const int* __restrict__ kv_len, const int* __restrict__ slots,
                         const int* __restrict__ page_table, int max_pages, float* __restrict__ part_o,
@@ -381,7 +384,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
     // per sequence the block writes the final result to ``out`` itself and no combine kernel follows.
     using S = DecodeSmem<D>;
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ float sm_m[kDecodeWarps][16], sm_l[kDecodeWarps][16];
+    __shared__ float sm_m[DecodeSmem<D>::kWarps][16], sm_l[DecodeSmem<D>::kWarps][16];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int split = blockIdx.x;
     const int kvh = blockIdx.y / m_tiles, mt = blockIdx.y % m_tiles, b = blockIdx.z;
@@ -400,7 +403,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
     const int64_t page_elems = (int64_t)n_kv * kPageTokens * D;
 
     auto issue = [&](int k) {           // the warp's k-th page into stage k % kDecodeStages
-        const int p = p0 + warp + k * kDecodeWarps;
+        const int p = p0 + warp + k * DecodeSmem<D>::kWarps;
         if (p < p1) {
             const int64_t base = (int64_t)CPM_PAGE(pages, p, max_pages) * page_elems + (int64_t)kvh * kPageTokens * D;
             copy_page_async<D>(my_stages + (k % kDecodeStages) * S::kStageBytes, k_cache + base, v_cache + base, lane);
@@ -408,7 +411,7 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
         cp_async_commit();
     };
     // the warp whose first two pages include the last page waits first (its copies must stay in order)
-    const bool early = rope.early && p0 + warp != n_pages - 1 && p0 + warp + kDecodeWarps != n_pages - 1;
+    const bool early = rope.early && p0 + warp != n_pages - 1 && p0 + warp + DecodeSmem<D>::kWarps != n_pages - 1;
     if (early) {
         issue(0);
         issue(1);
@@ -448,10 +451,10 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
             }
         }
     }
-    for (int k = 0; p0 + warp + k * kDecodeWarps < p1; ++k) {
+    for (int k = 0; p0 + warp + k * DecodeSmem<D>::kWarps < p1; ++k) {
         cp_async_wait<kDecodeStages - 1>();
         __syncwarp();
-        const int p = p0 + warp + k * kDecodeWarps;
+        const int p = p0 + warp + k * DecodeSmem<D>::kWarps;
         if constexpr (D == 64 || D == 128) {
             if (rope.qkv && rope.write_cache && p == n_pages - 1) {
                 // the step's own token is not in the cache yet: this warp holds its page and puts it there
@@ -491,15 +494,15 @@ decode_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
     __syncthreads();
     const int64_t unit = (((int64_t)b * n_kv + kvh) * m_tiles + mt) * n_splits + split;
     float* po = part_o + unit * 16 * D;
-    for (int i = threadIdx.x; i < 16 * D; i += kDecodeWarps * 32) {
+    for (int i = threadIdx.x; i < 16 * D; i += DecodeSmem<D>::kWarps * 32) {
         const int row = i / D, c = i - row * D;
         float mx = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < kDecodeWarps; ++w) mx = fmaxf(mx, sm_m[w][row]);
+        for (int w = 0; w < DecodeSmem<D>::kWarps; ++w) mx = fmaxf(mx, sm_m[w][row]);
         const float use = mx == -INFINITY ? 0.f : mx;
         float o = 0.f, l = 0.f;
 #pragma unroll
-        for (int w = 0; w < kDecodeWarps; ++w) {
+        for (int w = 0; w < DecodeSmem<D>::kWarps; ++w) {
             const float f = exp2f(sm_m[w][row] - use);
             o += sm_o[(w * 16 + row) * kLd + c] * f;
             l += sm_l[w][row] * f;
@@ -567,7 +570,7 @@ static int launch_decode(const void* q, const void* k_cache, const void* v_cache
     constexpr int smem = DecodeSmem<D>::kTotal;
     static bool configured[kMaxDevices] = {};            // per kernel and per device
     if (int st = ensure_dynamic_smem(kern, smem, configured)) return st;
-    cpm_launch(kLaunchAttention, kern, grid, kDecodeWarps * 32, smem, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
+    cpm_launch(kLaunchAttention, kern, grid, DecodeSmem<D>::kWarps * 32, smem, stream, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
                kv_len, slots, page_table, max_pages, part_o, part_ml, (bf16*)out, n_heads, n_kv, m_tiles, n_splits,
                scale * 1.4426950408889634f, rope);
     if (n_splits > 1)
@@ -620,7 +623,7 @@ CPM_API int cpm_decode_attention_rope_bf16(const void* qkv, void* k_cache, void*
 // block-mask flash kernel with 16-head tiles (src/flash_attn/src/flash_fwd_kernel.h:580-1170,
 // src/flash_attn/src/flash_blockmask.h:5-109).
 template <int D>
-__global__ void __launch_bounds__(kDecodeWarps * 32, 1)
+__global__ void __launch_bounds__(DecodeSmem<D>::kWarps * 32, 1)
 listed_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
                         bf16* __restrict__ out, const int* __restrict__ positions, const int* __restrict__ token_seq,
                         const int* __restrict__ slots, const int* __restrict__ page_table, int max_pages,
@@ -630,7 +633,7 @@ listed_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
     // gridDim.z blocks of threads, which write unnormalised partial results for combine_splits_kernel.
     using S = DecodeSmem<D>;
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    __shared__ float sm_m[kDecodeWarps][16], sm_l[kDecodeWarps][16];
+    __shared__ float sm_m[DecodeSmem<D>::kWarps][16], sm_l[DecodeSmem<D>::kWarps][16];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
     const int kvh = blockIdx.y / m_tiles, mt = blockIdx.y % m_tiles;
@@ -651,9 +654,9 @@ listed_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
     const uint32_t my_stages = (uint32_t)__cvta_generic_to_shared(smem_raw) + warp * kDecodeStages * S::kStageBytes;
     const int64_t page_elems = (int64_t)n_kv * kPageTokens * D;
 
-    auto block_of = [&](int k) { const int i = item0 + warp + k * kDecodeWarps; return dense ? i : list[i]; };
+    auto block_of = [&](int k) { const int i = item0 + warp + k * DecodeSmem<D>::kWarps; return dense ? i : list[i]; };
     auto issue = [&](int k) {
-        if (item0 + warp + k * kDecodeWarps < n_items) {
+        if (item0 + warp + k * DecodeSmem<D>::kWarps < n_items) {
             const int64_t base = (int64_t)CPM_PAGE(pages, block_of(k), max_pages) * page_elems + (int64_t)kvh * kPageTokens * D;
             copy_page_async<D>(my_stages + (k % kDecodeStages) * S::kStageBytes, k_cache + base, v_cache + base, lane);
         }
@@ -672,7 +675,7 @@ listed_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
 #pragma unroll
         for (int w = 0; w < D / 32; ++w) qf[r][w] = __ldg(reinterpret_cast<const uint4*>(qrow + 32 * w));
     }
-    for (int k = 0; item0 + warp + k * kDecodeWarps < n_items; ++k) {
+    for (int k = 0; item0 + warp + k * DecodeSmem<D>::kWarps < n_items; ++k) {
         cp_async_wait<kDecodeStages - 1>();
         __syncwarp();
         attend_page_smem<D>(st, qf, my_stages + (k % kDecodeStages) * S::kStageBytes, block_of(k) * kPageTokens, p, p,
@@ -701,17 +704,17 @@ listed_attention_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k_c
         sm_l[warp][g + 8] = st.l[1];
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < 16 * D; i += kDecodeWarps * 32) {
+    for (int i = threadIdx.x; i < 16 * D; i += DecodeSmem<D>::kWarps * 32) {
         const int row = i / D, c = i - row * D;
         const int local = mt * 16 + row;
         if (local >= group) continue;
         float mx = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < kDecodeWarps; ++w) mx = fmaxf(mx, sm_m[w][row]);
+        for (int w = 0; w < DecodeSmem<D>::kWarps; ++w) mx = fmaxf(mx, sm_m[w][row]);
         const float use = mx == -INFINITY ? 0.f : mx;
         float o = 0.f, l = 0.f;
 #pragma unroll
-        for (int w = 0; w < kDecodeWarps; ++w) {
+        for (int w = 0; w < DecodeSmem<D>::kWarps; ++w) {
             const float f = exp2f(sm_m[w][row] - use);
             o += sm_o[(w * 16 + row) * kLd + c] * f;
             l += sm_l[w][row] * f;
@@ -962,7 +965,7 @@ static int launch_listed(const void* q, const void* k_cache, const void* v_cache
     constexpr int smem = DecodeSmem<D>::kTotal;
     static bool configured[kMaxDevices] = {};            // per kernel and per device
     if (int st = ensure_dynamic_smem(kern, smem, configured)) return st;
-    cpm_launch(kLaunchAttention, kern, dim3(n_tokens, n_kv * m_tiles, n_splits), kDecodeWarps * 32, smem, stream, (const bf16*)q,
+    cpm_launch(kLaunchAttention, kern, dim3(n_tokens, n_kv * m_tiles, n_splits), DecodeSmem<D>::kWarps * 32, smem, stream, (const bf16*)q,
                (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, positions, token_seq, slots, page_table, max_pages,
                block_list, list_cap, n_heads, n_kv, m_tiles, scale * 1.4426950408889634f, part_o, part_ml, n_splits);
     if (n_splits > 1)
