@@ -63,7 +63,8 @@ class CacheGroup:
                 if PAGE_TOKENS % needs.pooled_stride:
                     raise ValueError(f"pooled-key stride {needs.pooled_stride} must divide the page size {PAGE_TOKENS}")
                 per_page = PAGE_TOKENS // needs.pooled_stride
-                # pooled keys are kept in fp32 whatever the cache's type: block selection compares them
+                # four bytes a dimension whatever the cache's type: fp32, or with a bf16 cache the two bf16 terms that the
+                # selection's tensor-core scores take as operands (the kernels that write and read them know which)
                 self.pooled = make("pages", (n, n_pages, needs.kv_heads, per_page, needs.head_dim), torch.float32, False)
 
     def bytes_per_token(self) -> int:

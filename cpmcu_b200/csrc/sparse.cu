@@ -13,13 +13,42 @@
 // fixes 32/16/64 and a group of 16); everything is decided per query from the keys at or
 // before it, so the result does not depend on how tokens are cut into steps (the
 // reference's pooled keys and selection see earlier chunks only); the local window is
-// always attended; scores, pooling and the choice are fp32, and pooled keys are stored
-// in fp32 whatever the cache's type.
+// always attended; scores, pooling and the choice are fp32; pooled keys are stored in fp32
+// with an fp32 cache and as two bf16 terms (the mean to 16 bits) with a bf16 cache.
 #include "common.cuh"
 
 // One block per (token, kv head).  If the token at position pos completes a pooling
 // window [first, first + kernel) with first = pos + 1 - kernel a multiple of stride,
 // the mean of those cached keys is stored as pooled entry first / stride.
+// How a pooled key lies in its d floats of storage.  With an fp32 cache: d floats.  With a bf16 cache: two bf16
+// terms whose sum is the fp32 mean to 16 bits, d leading terms (the mean rounded to bf16) and then d residuals
+// (the rest rounded to bf16); these are the two B operands that the tensor-core scores use, so the kernels that
+// score load fragments straight from them (splitting the floats in registers, for every token and in both walks,
+// was three quarters of the prefill selection kernel's instructions).
+template <typename T>
+__device__ __forceinline__ void store_pooled(float* __restrict__ pooled, int64_t entry, int d, int c, float mean) {
+    pooled[entry + c] = mean;
+}
+template <>
+__device__ __forceinline__ void store_pooled<bf16>(float* __restrict__ pooled, int64_t entry, int d, int c, float mean) {
+    bf16* terms = reinterpret_cast<bf16*>(pooled + entry);
+    const bf16 lead = __float2bfloat16_rn(mean);
+    terms[c] = lead;
+    terms[d + c] = __float2bfloat16_rn(mean - __bfloat162float(lead));
+}
+// Four consecutive dims of a pooled key as floats, from either form.
+template <bool kTerms>
+__device__ __forceinline__ float4 load_pooled4(const float* __restrict__ row, int d, int c) {
+    if (!kTerms) return __ldg(reinterpret_cast<const float4*>(row + c));
+    const bf16* terms = reinterpret_cast<const bf16*>(row);
+    const uint2 lead = __ldg(reinterpret_cast<const uint2*>(terms + c)), rest = __ldg(reinterpret_cast<const uint2*>(terms + d + c));
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&lead.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&lead.y));
+    const float2 e = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rest.x));
+    const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&rest.y));
+    return make_float4(a.x + e.x, a.y + e.y, b.x + f.x, b.y + f.y);
+}
+
 template <typename T>
 __global__ void pool_keys_kernel(const T* __restrict__ k_cache, float* __restrict__ pooled,
                                  const int* __restrict__ positions, const int* __restrict__ token_seq,
@@ -41,7 +70,7 @@ __global__ void pool_keys_kernel(const T* __restrict__ k_cache, float* __restric
             const int j = first + r;
             s += to_f32(k_cache[page_row_offset(CPM_PAGE(pages, j / kPageTokens, max_pages), kvh, j % kPageTokens, n_kv, d) + c]);
         }
-        pooled[dst + c] = s * inv;
+        store_pooled<T>(pooled, dst, d, c, s * inv);
     }
 }
 
@@ -249,6 +278,7 @@ __device__ __forceinline__ const float* pooled_row(const float* __restrict__ poo
 
 // Dot products of one pooled key with every head of the group; every lane returns all of them
 // through ``dots`` (dots[h] valid for h < group).
+template <bool kTerms>
 __device__ __forceinline__ void group_dots(const float* __restrict__ row, const float* __restrict__ qs, int group, int d,
                                            int lane, float scale, float* dots /* [kMaxGroup] in registers */) {
 #pragma unroll
@@ -256,7 +286,7 @@ __device__ __forceinline__ void group_dots(const float* __restrict__ row, const 
     for (int c0 = 0; c0 < d; c0 += 128) {
         const int c = c0 + 4 * lane;
         if (c < d) {
-            const float4 kv = __ldg(reinterpret_cast<const float4*>(row + c));
+            const float4 kv = load_pooled4<kTerms>(row, d, c);
 #pragma unroll
             for (int h = 0; h < kMaxGroup; ++h) {
                 if (h < group) {
@@ -307,7 +337,7 @@ select_blocks_kernel(const T* __restrict__ q, const float* __restrict__ pooled, 
     float dots[kMaxGroup];
     float my_m = -INFINITY, my_l = 0.f;
     for (int i = warp; i < n_vis; i += kSelectWarps) {
-        group_dots(pooled_row(pooled, pages, i, stride, per_page, n_kv, kvh, d), qs, group, d, lane, scale, dots);
+        group_dots<sizeof(T) == 2>(pooled_row(pooled, pages, i, stride, per_page, n_kv, kvh, d), qs, group, d, lane, scale, dots);
         float mine = -INFINITY;
 #pragma unroll
         for (int h = 0; h < kMaxGroup; ++h)
@@ -333,7 +363,7 @@ select_blocks_kernel(const T* __restrict__ q, const float* __restrict__ pooled, 
     }
     // second walk: probabilities, summed over the heads of the group
     for (int i = warp; i < n_vis; i += kSelectWarps) {
-        group_dots(pooled_row(pooled, pages, i, stride, per_page, n_kv, kvh, d), qs, group, d, lane, scale, dots);
+        group_dots<sizeof(T) == 2>(pooled_row(pooled, pages, i, stride, per_page, n_kv, kvh, d), qs, group, d, lane, scale, dots);
         float mine = 0.f;
 #pragma unroll
         for (int h = 0; h < kMaxGroup; ++h)
@@ -350,8 +380,8 @@ select_blocks_kernel(const T* __restrict__ q, const float* __restrict__ pooled, 
 // ---------------------------------------------------------------------------
 // The same selection with the scores on the tensor cores (bf16 queries, groups of up to 16 heads).
 // The 16 rows of an mma tile are the query heads of the group, the 8 columns pooled keys.  A pooled
-// key is fp32; it enters as the sum of two bf16 numbers (its rounding and the rounding of the
-// remainder), so that the product with the bf16 query keeps about 16 bits beyond bf16.
+// key enters as the sum of two bf16 numbers (the mean's rounding and the rounding of the remainder,
+// stored so by pool_keys_kernel), so that the product with the bf16 query keeps about 16 bits beyond bf16.
 // ---------------------------------------------------------------------------
 __device__ __forceinline__ void mma_16816_sel(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
                                               uint32_t b0, uint32_t b1) {
@@ -360,24 +390,16 @@ __device__ __forceinline__ void mma_16816_sel(float (&c)[4], uint32_t a0, uint32
         : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ void split_pair(float x, float y, uint32_t& hi, uint32_t& lo) {
-    const __nv_bfloat162 h = __floats2bfloat162_rn(x, y);
-    const float2 hf = __bfloat1622float2(h);
-    const __nv_bfloat162 l = __floats2bfloat162_rn(x - hf.x, y - hf.y);
-    hi = *reinterpret_cast<const uint32_t*>(&h);
-    lo = *reinterpret_cast<const uint32_t*>(&l);
-}
-
-
-// This thread's part of a pooled key: 8 consecutive dims of every 32-dim window.
+// This thread's part of a pooled key: 8 consecutive dims of every 32-dim window, leading terms and residuals.
 template <int D>
 struct RawKey {
-    float4 v[D / 32][2];
+    uint4 lead[D / 32], rest[D / 32];
     __device__ __forceinline__ void load(const float* __restrict__ row, int j) {
+        const bf16* terms = reinterpret_cast<const bf16*>(row);
 #pragma unroll
         for (int w = 0; w < D / 32; ++w) {
-            v[w][0] = __ldg(reinterpret_cast<const float4*>(row + 32 * w + 8 * j));
-            v[w][1] = __ldg(reinterpret_cast<const float4*>(row + 32 * w + 8 * j + 4));
+            lead[w] = __ldg(reinterpret_cast<const uint4*>(terms + 32 * w + 8 * j));
+            rest[w] = __ldg(reinterpret_cast<const uint4*>(terms + D + 32 * w + 8 * j));
         }
     }
 };
@@ -389,16 +411,11 @@ __device__ __forceinline__ void score_tile(float (&sc)[4], const uint4 (&qf)[2][
     sc[0] = sc[1] = sc[2] = sc[3] = 0.f;
 #pragma unroll
     for (int w = 0; w < D / 32; ++w) {
-        const float4 lo4 = raw.v[w][0], hi4 = raw.v[w][1];
-        uint32_t h01, l01, h23, l23, h45, l45, h67, l67;
-        split_pair(lo4.x, lo4.y, h01, l01);
-        split_pair(lo4.z, lo4.w, h23, l23);
-        split_pair(hi4.x, hi4.y, h45, l45);
-        split_pair(hi4.z, hi4.w, h67, l67);
-        mma_16816_sel(sc, qf[0][w].x, qf[1][w].x, qf[0][w].y, qf[1][w].y, h01, h23);
-        mma_16816_sel(sc, qf[0][w].x, qf[1][w].x, qf[0][w].y, qf[1][w].y, l01, l23);
-        mma_16816_sel(sc, qf[0][w].z, qf[1][w].z, qf[0][w].w, qf[1][w].w, h45, h67);
-        mma_16816_sel(sc, qf[0][w].z, qf[1][w].z, qf[0][w].w, qf[1][w].w, l45, l67);
+        const uint4 h = raw.lead[w], l = raw.rest[w];
+        mma_16816_sel(sc, qf[0][w].x, qf[1][w].x, qf[0][w].y, qf[1][w].y, h.x, h.y);
+        mma_16816_sel(sc, qf[0][w].x, qf[1][w].x, qf[0][w].y, qf[1][w].y, l.x, l.y);
+        mma_16816_sel(sc, qf[0][w].z, qf[1][w].z, qf[0][w].w, qf[1][w].w, h.z, h.w);
+        mma_16816_sel(sc, qf[0][w].z, qf[1][w].z, qf[0][w].w, qf[1][w].w, l.z, l.w);
     }
 #pragma unroll
     for (int i = 0; i < 4; ++i) sc[i] *= scale_log2;
@@ -448,13 +465,20 @@ select_blocks_mma_kernel(const bf16* __restrict__ q, const float* __restrict__ p
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     // As column g of a tile this thread loads pooled key tile*8 + g; the next tile's key is asked for
     // before the current one is worked on.
-    auto row_of = [&](int tile) {
-        return pooled_row(pooled, pages, min(tile * 8 + g, n_vis - 1), stride, per_page, n_kv, kvh, D);
+    // The page numbers of the keys two and three tiles ahead are asked for while the key one tile ahead is: a row's
+    // address needs its page's number, and with both loads in one iteration a tile cost their two latencies in a row.
+    auto page_of = [&](int tile) { return CPM_PAGE(pages, min(tile * 8 + g, n_vis - 1) * stride / kPageTokens, 0x7fffffff); };
+    auto row_at = [&](int tile, int page) {
+        const int tok = min(tile * 8 + g, n_vis - 1) * stride;
+        return pooled + (((int64_t)page * n_kv + kvh) * per_page + (tok % kPageTokens) / stride) * D;
     };
     RawKey<D> cur, nxt;
-    if (warp < n_tiles) cur.load(row_of(warp), j);
+    int page1 = page_of(warp + kSelMmaWarps), page2 = page_of(warp + 2 * kSelMmaWarps);
+    if (warp < n_tiles) cur.load(row_at(warp, page_of(warp)), j);
     for (int tile = warp; tile < n_tiles; tile += kSelMmaWarps) {
-        if (tile + kSelMmaWarps < n_tiles) nxt.load(row_of(tile + kSelMmaWarps), j);
+        if (tile + kSelMmaWarps < n_tiles) nxt.load(row_at(tile + kSelMmaWarps, page1), j);
+        page1 = page2;
+        page2 = page_of(tile + 3 * kSelMmaWarps);
         float sc[4];
         score_tile<D>(sc, qf, cur, scale_log2);
         cur = nxt;
@@ -498,9 +522,13 @@ select_blocks_mma_kernel(const bf16* __restrict__ q, const float* __restrict__ p
         head_inv[r] = (row < group && sum > 0.f) ? 1.f / sum : 0.f;     // rows beyond the group count for nothing
     }
     // second walk: probabilities summed over the heads
-    if (warp < n_tiles) cur.load(row_of(warp), j);
+    page1 = page_of(warp + kSelMmaWarps);
+    page2 = page_of(warp + 2 * kSelMmaWarps);
+    if (warp < n_tiles) cur.load(row_at(warp, page_of(warp)), j);
     for (int tile = warp; tile < n_tiles; tile += kSelMmaWarps) {
-        if (tile + kSelMmaWarps < n_tiles) nxt.load(row_of(tile + kSelMmaWarps), j);
+        if (tile + kSelMmaWarps < n_tiles) nxt.load(row_at(tile + kSelMmaWarps, page1), j);
+        page1 = page2;
+        page2 = page_of(tile + 3 * kSelMmaWarps);
         float sc[4];
         score_tile<D>(sc, qf, cur, scale_log2);
         cur = nxt;
