@@ -106,6 +106,7 @@ struct Selection {
     int n_cand;         // candidates: blocks init_blocks .. last_choice
     int per_block;      // pooled keys that start inside one block
     int reach_back;     // pooled keys before a block's first that still overlap it
+    int per_block_shift;   // log2(per_block) when it is a power of two (it is for every configuration seen), else -1
 };
 
 __device__ __forceinline__ Selection selection_of(int p, int kernel, int stride, int block_size, int init_blocks,
@@ -114,6 +115,7 @@ __device__ __forceinline__ Selection selection_of(int p, int kernel, int stride,
     s.qb = p / block_size;
     s.last_choice = s.qb - local_blocks;
     s.per_block = block_size / stride;
+    s.per_block_shift = (s.per_block & (s.per_block - 1)) == 0 ? __ffs(s.per_block) - 1 : -1;
     s.reach_back = kernel / stride - 1;
     s.n_cand = min(max(0, s.last_choice + 1 - init_blocks), sort_cap);
     return s;
@@ -146,8 +148,11 @@ __device__ __forceinline__ void clear_selection(const Selection& s, const Select
 __device__ __forceinline__ void note_score(const Selection& s, const SelectionArrays& a, int init_blocks, int entry, float v) {
     const unsigned bits = __float_as_uint(v);
     const unsigned mono = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);
-    const int k_hi = min((entry + s.reach_back) / s.per_block, init_blocks + s.n_cand - 1);
-    for (int k = max(entry / s.per_block, init_blocks); k <= k_hi; ++k) atomicMax(&a.keys[k - init_blocks], mono);
+    const bool shift = s.per_block_shift >= 0;              // a division costs the few lanes that come here some twenty instructions
+    const int first = shift ? entry >> s.per_block_shift : entry / s.per_block;
+    const int last = shift ? (entry + s.reach_back) >> s.per_block_shift : (entry + s.reach_back) / s.per_block;
+    const int k_hi = min(last, init_blocks + s.n_cand - 1);
+    for (int k = max(first, init_blocks); k <= k_hi; ++k) atomicMax(&a.keys[k - init_blocks], mono);
 }
 
 // The ``rank``-th largest (1 <= rank <= n) of keys[0..n), and in ``with_it`` how many keys of that value belong to
@@ -272,8 +277,9 @@ constexpr int kMaxGroup = 32;              // query heads per kv head this kerne
 
 __device__ __forceinline__ const float* pooled_row(const float* __restrict__ pooled, const int* __restrict__ pages,
                                                    int entry, int stride, int per_page, int n_kv, int kvh, int d) {
-    const int tok = entry * stride;
-    return pooled + (((int64_t)CPM_PAGE(pages, tok / kPageTokens, 0x7fffffff) * n_kv + kvh) * per_page + (tok % kPageTokens) / stride) * d;
+    // the stride divides the page, so per_page is a power of two: entry / per_page is the page, the rest the place in it
+    const int shift = __ffs(per_page) - 1;
+    return pooled + (((int64_t)CPM_PAGE(pages, entry >> shift, 0x7fffffff) * n_kv + kvh) * per_page + (entry & (per_page - 1))) * d;
 }
 
 // Dot products of one pooled key with every head of the group; every lane returns all of them
@@ -467,10 +473,10 @@ select_blocks_mma_kernel(const bf16* __restrict__ q, const float* __restrict__ p
     // before the current one is worked on.
     // The page numbers of the keys two and three tiles ahead are asked for while the key one tile ahead is: a row's
     // address needs its page's number, and with both loads in one iteration a tile cost their two latencies in a row.
-    auto page_of = [&](int tile) { return CPM_PAGE(pages, min(tile * 8 + g, n_vis - 1) * stride / kPageTokens, 0x7fffffff); };
+    const int page_shift = __ffs(per_page) - 1;             // the stride divides the page: per_page is a power of two
+    auto page_of = [&](int tile) { return CPM_PAGE(pages, min(tile * 8 + g, n_vis - 1) >> page_shift, 0x7fffffff); };
     auto row_at = [&](int tile, int page) {
-        const int tok = min(tile * 8 + g, n_vis - 1) * stride;
-        return pooled + (((int64_t)page * n_kv + kvh) * per_page + (tok % kPageTokens) / stride) * D;
+        return pooled + (((int64_t)page * n_kv + kvh) * per_page + (min(tile * 8 + g, n_vis - 1) & (per_page - 1))) * D;
     };
     RawKey<D> cur, nxt;
     int page1 = page_of(warp + kSelMmaWarps), page2 = page_of(warp + 2 * kSelMmaWarps);
