@@ -394,22 +394,28 @@ prefill_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
 // ---------------------------------------------------------------------------
 // Every token has its own list of 64-key blocks (the selection's choice, or "all" below the dense length).  The
 // eight tokens of a block of threads share what is brought: each token's blocks are marked in a bit mask, the union
-// of the masks is walked in rising order, and every block of the union is one step: K and V page by TMA, S = Q K^T
-// (128 x 64) into tensor memory, the softmax threads (one per row) mask the rows whose token did not list the
-// block and the keys behind the token's position, write P as bf16 over S, and O += P V takes P from tensor
-// memory.  One S and one O accumulator (256 TMEM columns) and 105 KB of shared memory let two blocks share an SM:
-// one block's tensor-core work runs while the other's rows are in the softmax.  Rows of tokens that did not list
-// a block cost the tensor cores their share all the same (on random data the union of eight lists of 96 blocks
-// holds about 185), but a step of 64 keys is 0.3 us of tensor work against 2 us for a warp of the mma.sync kernel.
+// of the masks is walked in rising order, two blocks of the union a step: their K pages side by side and their V
+// pages by TMA, S = Q K^T (128 x 128) into tensor memory, the softmax threads (one per row) mask the rows whose
+// token did not list a block and the keys behind the token's position, write P as bf16 over S, and O += P V takes P
+// from tensor memory.  An odd union repeats its last block in the second place, masked for every row.  Keys and
+// values have one buffer each: the next step's keys are brought while the rows are in the softmax, its values while
+// the next S is computed.  One S and one O accumulator (256 TMEM columns) and 105 KB of shared memory let two blocks
+// share an SM: one block's tensor-core work runs while the other's rows are in the softmax.  Rows of tokens that did
+// not list a block cost the tensor cores their share all the same (on random data the union of eight lists of 96
+// blocks holds about 185), but 64 keys are 0.15 us of tensor work against 2 us for a warp of the mma.sync kernel.
+// Two blocks a step rather than one: half as many hand-offs between the roles per key.  A row's scores of the
+// second block are read from tensor memory twice (for the maximum, then for the exponentials), which keeps the
+// thread within the registers that two blocks an SM leave it.
 // A tile whose tokens belong to several sequences (packed prompts) is done in passes, one per sequence.
 // Waits are bounded as in the kernel above.
 constexpr int kSparseTokens = 8;
 constexpr int kSparseThreads = 192;                      // warps 0-3: softmax, one row a thread; 4: MMA issue; 5: TMA
-constexpr int kSparseStages = 2;
-constexpr int kSparseTmemCols = 256;                     // S (and P over it) at columns 0-63, O at 64-191
+constexpr int kSparseTmemCols = 256;                     // S at columns 0-127 (P over its first 64), O at 128-255
 constexpr int kSparseQBytes = 128 * 128 * 2;             // 8 tokens x 16 heads x 128
-constexpr int kSparseKvBytes = 2 * 64 * 128 * 2;         // a key page and a value page
-constexpr uint32_t kSparseIdescQK = instr_desc_bf16(128, 64);
+constexpr int kSparseKBytes = 2 * 64 * 128 * 2;          // two key pages, as two halves of 64 dims x 128 rows
+constexpr int kSparseVBytes = 2 * 64 * 128 * 2;          // two value pages
+constexpr int kSparseTileBytes = kSparseQBytes + kSparseKBytes + kSparseVBytes;
+constexpr uint32_t kSparseIdescQK = instr_desc_bf16(128, 128);
 constexpr uint32_t kSparseIdescPV = instr_desc_bf16(128, 128);
 
 struct UnionCursor {             // walks the set bits of a mask in rising order
@@ -435,22 +441,22 @@ listed_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const
                                 int n_kv, float scale_log2, int words) {
     constexpr int kD = 128;
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t q_full, kv_full[kSparseStages], kv_empty[kSparseStages], s_full, p_full, o_full;
+    __shared__ __align__(8) uint64_t q_full, k_full, k_empty, v_full, v_empty, s_full, p_full, o_full;
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t0 = blockIdx.x * kSparseTokens, kvh = blockIdx.y;
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t q_smem = base, kv_smem = base + kSparseQBytes;
-    unsigned* all = reinterpret_cast<unsigned*>(smem_raw + (base - smem_u32(smem_raw)) + kSparseQBytes + kSparseStages * kSparseKvBytes);
+    const uint32_t q_smem = base, k_smem = base + kSparseQBytes, v_smem = k_smem + kSparseKBytes;
+    unsigned* all = reinterpret_cast<unsigned*>(smem_raw + (base - smem_u32(smem_raw)) + kSparseTileBytes);
     unsigned* mine = all + words;                                          // [tokens][words]
 
     if (threadIdx.x == 0) {
         mbar_init(smem_u32(&q_full), 1);
-        for (int s = 0; s < kSparseStages; ++s) {
-            mbar_init(smem_u32(&kv_full[s]), 1);
-            mbar_init(smem_u32(&kv_empty[s]), 1);
-        }
+        mbar_init(smem_u32(&k_full), 1);
+        mbar_init(smem_u32(&k_empty), 1);
+        mbar_init(smem_u32(&v_full), 1);
+        mbar_init(smem_u32(&v_empty), 1);
         mbar_init(smem_u32(&s_full), 1);
         mbar_init(smem_u32(&p_full), 4);                                   // the four softmax warps
         mbar_init(smem_u32(&o_full), 1);
@@ -481,8 +487,9 @@ listed_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const
     const bool row_live = warp < 4 && t0 + my_token < n_tokens;
     const int my_pos = row_live ? positions[t0 + my_token] : -1;
     const uint32_t lane_base = tmem_base + ((uint32_t)((warp & 3) * 32) << 16);
-    const uint32_t s_addr = lane_base, o_addr = lane_base + 64;
+    const uint32_t s_addr = lane_base, o_addr = lane_base + 128;
     float m_ref = -INFINITY, l = 0.f;
+    uint32_t k_loads = 0, v_loads = 0;                                     // the producer's, for the abort path
 
     if (warp == 5 && lane == 0) {                                          // the queries: two halves of 64 dims
         mbar_expect_tx(smem_u32(&q_full), kSparseQBytes);
@@ -526,8 +533,9 @@ listed_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const
             all[w] = u;
         }
         __syncthreads();
-        int n_steps = 0;                                                   // the same number in every thread
-        for (int w = 0; w < words; ++w) n_steps += __popc(all[w]);
+        int n_blocks = 0;                                                  // the same number in every thread
+        for (int w = 0; w < words; ++w) n_blocks += __popc(all[w]);
+        int n_steps = (n_blocks + 1) / 2;
         ok = ok && !aborted();
         if (!ok) n_steps = 0;
 
@@ -536,56 +544,72 @@ listed_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const
             if (lane == 0) {
                 UnionCursor cursor{-1, 0u};
                 for (int j = 0; j < n_steps; ++j, ++it) {
-                    const int b = next_listed(cursor, all, words);
-                    const uint32_t s = it & 1u, use = it >> 1;
-                    if (use > 0 && !mbar_wait_bounded(smem_u32(&kv_empty[s]), (use - 1) & 1u)) { fail(ERR_K_EMPTY); ok = false; break; }
+                    const int b0 = next_listed(cursor, all, words);
+                    const int b1 = 2 * j + 1 < n_blocks ? next_listed(cursor, all, words) : b0;
+                    const int page0 = min(max(CPM_PAGE(pages, b0, max_pages), 0), n_pages - 1);
+                    const int page1 = min(max(CPM_PAGE(pages, b1, max_pages), 0), n_pages - 1);
+                    if (it > 0 && !mbar_wait_bounded(smem_u32(&k_empty), (it - 1) & 1u)) { fail(ERR_K_EMPTY); ok = false; break; }
                     if (aborted()) { ok = false; break; }
-                    const int page = min(max(CPM_PAGE(pages, b, max_pages), 0), n_pages - 1);
-                    const uint32_t bar = smem_u32(&kv_full[s]), dst = kv_smem + s * kSparseKvBytes;
-                    mbar_expect_tx(bar, kSparseKvBytes);
-                    tma_load_2d(dst, &map_k, bar, 0, (page * n_kv + kvh) * kPageTokens);
-                    tma_load_2d(dst + 64 * 64 * 2, &map_k, bar, 64, (page * n_kv + kvh) * kPageTokens);
-                    tma_load_2d(dst + kSparseKvBytes / 2, &map_v, bar, 0, (page * n_kv + kvh) * kD);
+                    const uint32_t kbar = smem_u32(&k_full), vbar = smem_u32(&v_full);
+                    mbar_expect_tx(kbar, kSparseKBytes);
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        tma_load_2d(k_smem + half * (kSparseKBytes / 2), &map_k, kbar, half * 64, (page0 * n_kv + kvh) * kPageTokens);
+                        tma_load_2d(k_smem + half * (kSparseKBytes / 2) + kSparseKBytes / 4, &map_k, kbar, half * 64,
+                                    (page1 * n_kv + kvh) * kPageTokens);
+                    }
+                    ++k_loads;
+                    if (it > 0 && !mbar_wait_bounded(smem_u32(&v_empty), (it - 1) & 1u)) { fail(ERR_V_EMPTY); ok = false; break; }
+                    mbar_expect_tx(vbar, kSparseVBytes);
+                    tma_load_2d(v_smem, &map_v, vbar, 0, (page0 * n_kv + kvh) * kD);
+                    tma_load_2d(v_smem + kSparseVBytes / 2, &map_v, vbar, 0, (page1 * n_kv + kvh) * kD);
+                    ++v_loads;
                 }
             }
         } else if (warp == 4) {
             // ---- MMA issue ----
             if (lane == 0 && n_steps > 0) {
-                auto issue_qk = [&](uint32_t s) {
+                auto issue_qk = [&]() {
 #pragma unroll
                     for (int half = 0; half < 2; ++half) {
                         const uint64_t da = smem_desc_sw128(q_smem + half * (kSparseQBytes / 2));
-                        const uint64_t db = smem_desc_sw128(kv_smem + s * kSparseKvBytes + half * (64 * 64 * 2));
+                        const uint64_t db = smem_desc_sw128(k_smem + half * (kSparseKBytes / 2));
 #pragma unroll
                         for (int k = 0; k < 4; ++k)
                             tcgen05_mma_f16(tmem_base, da + 2 * k, db + 2 * k, kSparseIdescQK, (half | k) != 0);
                     }
                 };
-                auto issue_pv = [&](uint32_t s, bool accumulate) {
-                    const uint64_t db = smem_desc_sw128(kv_smem + s * kSparseKvBytes + kSparseKvBytes / 2);
+                auto issue_pv = [&](bool accumulate) {
 #pragma unroll
-                    for (int k = 0; k < 4; ++k)
-                        tcgen05_mma_f16_ts(tmem_base + 64, tmem_base + k * 8, db + 2 * k, kSparseIdescPV, accumulate || k != 0);
+                    for (int x = 0; x < 2; ++x) {
+                        const uint64_t db = smem_desc_sw128(v_smem + x * (kSparseVBytes / 2));
+#pragma unroll
+                        for (int k = 0; k < 4; ++k)
+                            tcgen05_mma_f16_ts(tmem_base + 128, tmem_base + x * 32 + k * 8, db + 2 * k, kSparseIdescPV,
+                                               accumulate || (x | k) != 0);
+                    }
                 };
                 if (it == 0 && !mbar_wait_bounded(smem_u32(&q_full), 0)) { fail(ERR_Q); ok = false; }
-                if (ok && !mbar_wait_bounded(smem_u32(&kv_full[it & 1u]), (it >> 1) & 1u)) { fail(ERR_K_FULL); ok = false; }
+                if (ok && !mbar_wait_bounded(smem_u32(&k_full), it & 1u)) { fail(ERR_K_FULL); ok = false; }
                 if (ok) {
                     tcgen05_fence_after();
-                    issue_qk(it & 1u);
+                    issue_qk();
                     tcgen05_commit(smem_u32(&s_full));
+                    tcgen05_commit(smem_u32(&k_empty));
                 }
                 for (int j = 0; ok && j < n_steps; ++j, ++it) {
                     if (aborted()) { ok = false; break; }
                     if (!mbar_wait_bounded(smem_u32(&p_full), it & 1u)) { fail(ERR_P_FULL); ok = false; break; }
+                    if (!mbar_wait_bounded(smem_u32(&v_full), it & 1u)) { fail(ERR_V_FULL); ok = false; break; }
                     tcgen05_fence_after();
-                    issue_pv(it & 1u, it > 0);
-                    tcgen05_commit(smem_u32(&kv_empty[it & 1u]));          // the stage is free when this product is done
+                    issue_pv(it > 0);
+                    tcgen05_commit(smem_u32(&v_empty));                    // the values are free when this product is done
                     if (j + 1 < n_steps) {
-                        const uint32_t nx = it + 1;
-                        if (!mbar_wait_bounded(smem_u32(&kv_full[nx & 1u]), (nx >> 1) & 1u)) { fail(ERR_K_FULL); ok = false; break; }
+                        if (!mbar_wait_bounded(smem_u32(&k_full), (it + 1) & 1u)) { fail(ERR_K_FULL); ok = false; break; }
                         tcgen05_fence_after();
-                        issue_qk(nx & 1u);
+                        issue_qk();
                         tcgen05_commit(smem_u32(&s_full));                 // also covers the product into O before it
+                        tcgen05_commit(smem_u32(&k_empty));
                     }
                 }
             } else {
@@ -598,7 +622,8 @@ listed_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const
             const unsigned* my_mask = mine + my_token * words;
             UnionCursor cursor{-1, 0u};
             for (int j = 0; j < n_steps; ++j, ++it) {
-                const int b = next_listed(cursor, all, words);
+                const int b0 = next_listed(cursor, all, words);
+                const int b1 = 2 * j + 1 < n_blocks ? next_listed(cursor, all, words) : -1;
                 if (__any_sync(0xffffffffu, aborted())) { ok = false; break; }
                 if (!__all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&s_full), it & 1u))) {
                     if (lane == 0) fail(ERR_S_FULL);
@@ -606,27 +631,29 @@ listed_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const
                     break;
                 }
                 tcgen05_fence_after();
-                uint32_t v[2][32];
-                tmem_load_32cols(s_addr, v[0]);
-                tmem_load_32cols(s_addr + 32, v[1]);
-                tmem_load_wait();
-                // A row whose token did not list the block takes no part in the step's arithmetic: its P is zero.  (The
-                // loads and stores of tensor memory are the warp's, so its lanes still go through them.)
-                const bool listed = member && ((my_mask[b >> 5] >> (b & 31)) & 1u);
-                const int visible = listed ? min(64, my_pos - b * kPageTokens + 1) : 0;      // keys of the block this row sees
+                int visible[2];                                            // keys of each block this row sees
+                visible[0] = member && ((my_mask[b0 >> 5] >> (b0 & 31)) & 1u) ? min(64, my_pos - b0 * kPageTokens + 1) : 0;
+                visible[1] = b1 >= 0 && member && ((my_mask[b1 >> 5] >> (b1 & 31)) & 1u) ? min(64, my_pos - b1 * kPageTokens + 1) : 0;
                 float mx = -INFINITY;
-                if (visible > 0) {
-                    if (visible < 64) {
+                uint32_t v[2][32];
+#pragma unroll
+                for (int x = 1; x >= 0; --x) {                             // the first block's scores stay in registers
+                    tmem_load_32cols(s_addr + x * 64, v[0]);
+                    tmem_load_32cols(s_addr + x * 64 + 32, v[1]);
+                    tmem_load_wait();
+                    if (visible[x] > 0) {
+                        if (visible[x] < 64) {
+#pragma unroll
+                            for (int c = 0; c < 2; ++c)
+#pragma unroll
+                                for (int e = 0; e < 32; ++e)
+                                    if (c * 32 + e >= visible[x]) v[c][e] = 0xff800000u;          // -inf
+                        }
 #pragma unroll
                         for (int c = 0; c < 2; ++c)
 #pragma unroll
-                            for (int e = 0; e < 32; ++e)
-                                if (c * 32 + e >= visible) v[c][e] = 0xff800000u;          // -inf
+                            for (int e = 0; e < 32; e += 2) mx = max3(mx, __uint_as_float(v[c][e]), __uint_as_float(v[c][e + 1]));
                     }
-#pragma unroll
-                    for (int c = 0; c < 2; ++c)
-#pragma unroll
-                        for (int e = 0; e < 32; e += 2) mx = max3(mx, __uint_as_float(v[c][e]), __uint_as_float(v[c][e + 1]));
                 }
                 const float m_new = mx * scale_log2;
                 const bool grow = m_new > m_ref + kRescaleThreshold || (m_ref == -INFINITY && m_new > -INFINITY);
@@ -635,35 +662,50 @@ listed_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const
                     l *= alpha;
                     if (it > 0) {
 #pragma unroll 1
-                        for (int c = 0; c < kD / 32; ++c) {
-                            uint32_t o[32];
-                            tmem_load_32cols(o_addr + c * 32, o);
+                        for (int c = 0; c < kD / 16; ++c) {
+                            uint32_t o[16];
+                            tmem_load_16cols(o_addr + c * 16, o);
                             tmem_load_wait();
 #pragma unroll
-                            for (int e = 0; e < 32; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
-                            tmem_store_32cols(o_addr + c * 32, o);
+                            for (int e = 0; e < 16; ++e) o[e] = __float_as_uint(__uint_as_float(o[e]) * alpha);
+                            tmem_store_16cols(o_addr + c * 16, o);
                         }
                     }
                     if (grow) m_ref = m_new;
                 }
-                uint32_t packed[32];
+                const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+                const float2 scale2 = make_float2(scale_log2, scale_log2), minus_m2 = make_float2(-m_use, -m_use);
                 float2 sum2 = make_float2(0.f, 0.f);
-                if (visible > 0) {
-                    const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-                    const float2 scale2 = make_float2(scale_log2, scale_log2), minus_m2 = make_float2(-m_use, -m_use);
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) {
-                        const float2 x = fma2(make_float2(__uint_as_float(v[e >> 4][(2 * e) & 31]),
-                                                          __uint_as_float(v[e >> 4][(2 * e + 1) & 31])), scale2, minus_m2);
-                        const float2 pp = make_float2(ex2(x.x), ex2(x.y));
-                        sum2 = add2(sum2, pp);
-                        packed[e] = pack_bf16(pp.x, pp.y);
+                for (int x = 0; x < 2; ++x) {
+                    if (x == 1) {                                          // the second block's scores again (the whole warp loads)
+                        tmem_load_32cols(s_addr + 64, v[0]);
+                        tmem_load_32cols(s_addr + 96, v[1]);
+                        tmem_load_wait();
+                        if (visible[1] > 0 && visible[1] < 64) {
+#pragma unroll
+                            for (int c = 0; c < 2; ++c)
+#pragma unroll
+                                for (int e = 0; e < 32; ++e)
+                                    if (c * 32 + e >= visible[1]) v[c][e] = 0xff800000u;
+                        }
                     }
-                } else {
+                    uint32_t packed[32];
+                    if (visible[x] > 0) {
 #pragma unroll
-                    for (int e = 0; e < 32; ++e) packed[e] = 0u;
+                        for (int e = 0; e < 32; ++e) {
+                            const float2 xx = fma2(make_float2(__uint_as_float(v[e >> 4][(2 * e) & 31]),
+                                                               __uint_as_float(v[e >> 4][(2 * e + 1) & 31])), scale2, minus_m2);
+                            const float2 pp = make_float2(ex2(xx.x), ex2(xx.y));
+                            sum2 = add2(sum2, pp);
+                            packed[e] = pack_bf16(pp.x, pp.y);
+                        }
+                    } else {
+#pragma unroll
+                        for (int e = 0; e < 32; ++e) packed[e] = 0u;
+                    }
+                    tmem_store_32cols(s_addr + x * 32, packed);
                 }
-                tmem_store_32cols(s_addr, packed);
                 l += sum2.x + sum2.y;
                 tmem_store_wait();
                 tcgen05_fence_before();
@@ -710,8 +752,8 @@ listed_attention_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const
     if (warp == 5 && lane == 0 && aborted()) {
         // copies that nobody consumed: wait for them (bounded), so that none is in flight at the exit
         mbar_wait_bounded(smem_u32(&q_full), 0);
-        for (uint32_t j = it > kSparseStages ? it - kSparseStages : 0; j < it; ++j)
-            mbar_wait_bounded(smem_u32(&kv_full[j & 1u]), (j >> 1) & 1u);
+        if (k_loads > 0) mbar_wait_bounded(smem_u32(&k_full), (k_loads - 1) & 1u);
+        if (v_loads > 0) mbar_wait_bounded(smem_u32(&v_full), (v_loads - 1) & 1u);
     }
     tcgen05_fence_before();
     __syncthreads();
@@ -800,7 +842,7 @@ CPM_API int cpm_prefill_attention_tcgen05(const void* q, const void* k_cache, co
 // beside the tiles (more than cpm_listed_attention_tcgen05_max_pages() pages a sequence), are refused: the caller
 // takes the mma.sync kernel for them.
 CPM_API int cpm_listed_attention_tcgen05_max_pages() {
-    return ((110 * 1024 - 1024 - fa5::kSparseQBytes - fa5::kSparseStages * fa5::kSparseKvBytes) / ((fa5::kSparseTokens + 1) * 4)) * 32;
+    return ((110 * 1024 - 1024 - fa5::kSparseTileBytes) / ((fa5::kSparseTokens + 1) * 4)) * 32;
 }
 
 CPM_API int cpm_listed_attention_tcgen05(const void* q, const void* k_cache, const void* v_cache, void* out,
@@ -814,7 +856,7 @@ CPM_API int cpm_listed_attention_tcgen05(const void* q, const void* k_cache, con
         ((uintptr_t)q & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15) || ((uintptr_t)out & 15))
         return CPM_BAD_ARGUMENT;
     const int words = (max_pages + 31) / 32;
-    const int smem = 1024 + kSparseQBytes + kSparseStages * kSparseKvBytes + (kSparseTokens + 1) * words * 4;
+    const int smem = 1024 + kSparseTileBytes + (kSparseTokens + 1) * words * 4;
     if (smem > 110 * 1024) return CPM_BAD_ARGUMENT;                  // two blocks share an SM's shared memory
     CUtensorMap map_q, map_k, map_v;
     if (!tc5::make_map_3d_bf16(&map_q, q, 128, (uint64_t)n_heads, (uint64_t)n_tokens, 128 * 2, (uint64_t)n_heads * 128 * 2, 64, 16,
