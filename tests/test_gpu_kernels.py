@@ -375,6 +375,56 @@ def test_block_list_attention_against_generic(n_heads, n_kv, d, tiles):
     assert _err(got, want) < KTOL["bfloat16"]
 
 
+def test_block_list_attention_of_random_batches():
+    """The two tile kernels of the block-list attention on random batches: one to four sequences of lengths around
+    the page and tile edges (so a tile holds tokens of up to four sequences, and unions of one, two, an odd and an
+    even number of blocks all occur), one to three key/value heads, lists of 3, 7 and 40 places with any number of
+    blocks in them, a fifth of the tokens "dense"."""
+    import random
+    ops = _ops("bfloat16")
+    rnd = random.Random(5)
+    d = 128
+    try:
+        for trial in range(16):
+            n_kv = rnd.choice([1, 2, 3])
+            n_heads = 16 * n_kv
+            lens = [rnd.choice([1, 5, 63, 64, 65, 130, 300, 777, 1500]) for _ in range(rnd.randint(1, 4))]
+            cache, slots = _paged_setup(ops, lens, n_kv, d, trial, "bfloat16")
+            lane = cache.lane(0)
+            g = torch.Generator().manual_seed(100 + trial)
+            T = sum(lens)
+            qkv = torch.randn(T, (n_heads + 2 * n_kv) * d, generator=g).bfloat16()
+            positions = torch.cat([torch.arange(n) for n in lens]).int()
+            token_seq = torch.cat([torch.full((n,), i) for i, n in enumerate(lens)]).int().cuda()
+            sl = torch.tensor(slots, dtype=torch.int32).cuda()
+            q = ops.rope_store(qkv.cuda(), n_heads, n_kv, d, positions.cuda(), token_seq, sl, lane.page_table, lane.k,
+                               lane.v, None, 1.0, 0)
+            cap = rnd.choice([3, 7, 40])
+            lists = torch.full((T, n_kv, cap), -1, dtype=torch.int32)
+            for t in range(T):
+                own = int(positions[t]) // 64
+                for h in range(n_kv):
+                    if rnd.random() < 0.2:
+                        lists[t, h, 0] = -2
+                        continue
+                    k = rnd.randint(0, min(own, cap - 1))
+                    blocks = sorted(set(rnd.sample(range(own), k) + [own]))
+                    lists[t, h, :len(blocks)] = torch.tensor(blocks, dtype=torch.int32)
+                    lists[t, h, len(blocks) + 1:] = 12345
+            lists = lists.cuda()
+            scale = 1 / math.sqrt(d)
+            want = ops.attention_generic(q, lane.k, lane.v, positions.cuda(), token_seq, sl, lane.page_table, n_kv, scale,
+                                         block_list=lists, block_size=64)
+            for tcgen05 in (True, False):
+                ops.use_tcgen05_listed = tcgen05
+                got = ops.listed_attention(q, lane.k, lane.v, positions.cuda(), token_seq, sl, lane.page_table, lists,
+                                           n_kv, scale, tiles=True)
+                ops.raise_on_kernel_error()
+                assert _err(got, want) < KTOL["bfloat16"], (trial, tcgen05, lens, n_kv, cap)
+    finally:
+        ops.use_tcgen05_listed = True
+
+
 @pytest.mark.parametrize("n_heads,n_kv,d", [(4, 2, 128), (2, 1, 128), (32, 2, 128), (16, 2, 64), (4, 2, 64)])
 def test_tcgen05_prefill_attention(n_heads, n_kv, d):
     """The tcgen05 prefill attention (head sizes 128 and 64, heads in pairs) against the plain implementation:
